@@ -1,0 +1,64 @@
+"""CPU restatement of the reference's dequantise-then-matmul GEMM check.
+
+TEST INFRASTRUCTURE ONLY (see ``oracle/__init__.py``).
+
+Follows the reference's ``tests/test_dense_gemm.py:48-74`` (``ref_gemm`` /
+``ref_gemm_w4a4``): both operands are expanded to float32 with their block
+scales, multiplied with ``torch.matmul`` in float32 and rounded to bfloat16.
+The scale decoders follow ``tests/utils/gemm_utils.py:68-71,247-254``.  The
+optional ``alpha`` is the per-tensor factor the NVFP4 kernel applies to the
+float32 accumulator before the bfloat16 rounding
+(``csrc/kernel/gemm/dense_gemm.cu:159-164``).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .quant import (
+    GROUP_SIZE,
+    decode_e2m1_packed,
+    decode_e4m3,
+    decode_ue4m3,
+    decode_ue8m0,
+    unswizzle_sf,
+)
+
+
+def _np(x) -> np.ndarray:
+    if isinstance(x, torch.Tensor):
+        x = x.detach().to("cpu")
+        if x.dtype != torch.uint8:
+            x = x.view(torch.uint8)
+        return x.numpy()
+    return np.asarray(x, dtype=np.uint8)
+
+
+def dequantize(q, sf, mode: str, rows: int | None = None, swizzled: bool = True) -> torch.Tensor:
+    """Quantised bytes + block scales -> float32 [rows, k] tensor."""
+    q = _np(q)
+    sf = _np(sf)
+    g = GROUP_SIZE[mode]
+    rows = q.shape[0] if rows is None else rows
+    vals = decode_e4m3(q) if mode == "w8a8-mxfp8" else decode_e2m1_packed(q)
+    k = vals.shape[1]
+    sf = sf.reshape(-1, k // g)
+    sf_logical = unswizzle_sf(sf, rows) if swizzled else sf[:rows]
+    scale = decode_ue4m3(sf_logical) if mode == "w4a4-nvfp4" else decode_ue8m0(sf_logical)
+    return torch.from_numpy(vals[:rows] * np.repeat(scale, g, axis=1))
+
+
+def dense_gemm_ref(a_q, b_q, sfa, sfb, mode: str = "w8a8-mxfp8", alpha: float | None = None,
+                   swizzled: bool = True, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """``bf16(alpha * (dequant(A) @ dequant(B)^T))`` in float32 on the CPU.
+
+    ``a_q`` [M, K or K/2], ``b_q`` [N, K or K/2]; ``sfa`` / ``sfb`` in SfAtom
+    order when ``swizzled`` (what the GEMM kernel consumes) else logical.
+    Pass ``out_dtype=torch.float32`` to skip the final rounding."""
+    a = dequantize(a_q, sfa, mode, swizzled=swizzled)
+    b = dequantize(b_q, sfb, mode, swizzled=swizzled)
+    acc = torch.matmul(a, b.T)
+    if alpha is not None:
+        acc = acc * float(alpha)
+    return acc.to(out_dtype)
