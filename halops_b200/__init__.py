@@ -1,0 +1,46 @@
+"""B200-native (sm_100a) block-scaled quantize -> dense GEMM path.
+
+Drop-in for the reference's ``halops.group_wise_quant`` and
+``halops.dense_gemm`` (plus ``interleave_gate_up`` and ``EpilogueOp``): same
+Python signatures, executed by hand-written CUDA/PTX kernels through a C-ABI
+shared library.  There is no CPU path and no fallback.
+"""
+
+from .gemm import EpilogueOp, dense_gemm, group_wise_quant, interleave_gate_up
+from ._native import lib_path
+
+__all__ = ["EpilogueOp", "dense_gemm", "group_wise_quant", "interleave_gate_up", "device_status",
+           "describe_tile", "lib_path"]
+__version__ = "0.1.0"
+
+
+def device_status(device=None) -> int:
+    """Synchronises the current stream of ``device`` and returns the device-side
+    status word (0 = every bounded wait completed); raises RuntimeError when a
+    kernel gave up on a wait."""
+    import ctypes
+
+    import torch
+
+    from . import _native
+
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    status = ctypes.c_uint32(0)
+    _native.call("hq_device_status", dev.index, torch.cuda.current_stream(dev).cuda_stream,
+                 ctypes.byref(status))
+    return int(status.value)
+
+
+def describe_tile(m: int, n: int, k: int, mode: str = "w8a8-mxfp8", sm_count: int = -1, device: int = -1) -> str:
+    """The tile the GEMM dispatch picks for a shape (what the reference prints
+    under ``IR_GEMM_TRACE``); raises the reference's "No dense ... tile" error
+    for an illegal shape."""
+    import ctypes
+
+    from . import _native
+
+    buf = ctypes.create_string_buffer(256)
+    rc = _native.lib().hq_describe_tile(m, n, k, _native.MODE_IDS[mode], sm_count, device, buf, len(buf))
+    if rc != 0:
+        raise RuntimeError(buf.value.decode())
+    return buf.value.decode()

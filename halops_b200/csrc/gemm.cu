@@ -1,0 +1,671 @@
+// Block-scaled dense GEMM for sm_100a: out[M,N] = bf16(alpha * A[M,K] . B[N,K]^T)
+// with MXFP8 (e4m3 + UE8M0 / 32), NVFP4 (e2m1 + UE4M3 / 16) or MXFP4 (e2m1 +
+// UE8M0 / 32) operands whose scales arrive in the 128x4 SfAtom order.
+//
+// Replaces the reference's CUTLASS/CuTe kernel (csrc/kernel/gemm/gemm_kernel.cuh:28-285,
+// mainloop_fwd.cuh:405-1007, epilogue.cuh:713-1058, tile_scheduler.cuh:523-542)
+// with hand-written PTX.  Per CTA (one per SM, persistent over output tiles):
+//   warp 0   TMA producer: A and B tiles (128-byte swizzle) by tensor map, the
+//            512-byte scale atoms by flat bulk copies, into a ring of stages
+//   warp 1   one thread issues tcgen05.cp (scales -> tensor memory) and the
+//            block-scaled tcgen05.mma (fp32 accumulators in tensor memory,
+//            two accumulator stages so the epilogue overlaps the next tile)
+//   warps 2-5 epilogue: tcgen05.ld -> * alpha -> bf16 -> swizzled staging in
+//            shared memory -> TMA store (rows >= M are dropped by the tensor
+//            map extent, so neither A nor the output is ever padded)
+// Every mbarrier wait is bounded: a role that waits longer than kTimeoutNs
+// records a code in the device status word, raises the CTA's abort flag and
+// all roles leave through the common teardown that frees tensor memory.
+
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace hq {
+namespace {
+
+constexpr int kBM = 128;           // rows of A per CTA tile
+constexpr int kBKBytes = 128;      // bytes of K per stage row: 128 e4m3 or 256 e2m1
+constexpr int kThreads = 192;      // 6 warps
+constexpr int kEpiWarps = 4;
+constexpr int kEpiChunk = 32;      // accumulator columns per tcgen05.ld / TMA store
+constexpr int kEpiBufBytes = 32 * kEpiChunk * 2;  // 32 rows x 64 bytes
+constexpr uint64_t kTimeoutNs = 2000000000ull;    // bound of every device-side wait
+constexpr int kSmemBudget = 232448;               // 227 KiB opt-in maximum per CTA
+
+// device status word: non-zero when a kernel gave up on a bounded wait
+__device__ uint32_t g_status[4];
+
+enum : uint32_t {
+    kStatusProducer = 0x01,
+    kStatusMma = 0x02,
+    kStatusEpilogue = 0x04,
+};
+
+template <int BN, int KIND>
+struct Cfg {
+    static_assert(BN == 64 || BN == 128 || BN == 256, "tile widths built");
+    static constexpr int kABytes = kBM * kBKBytes;
+    static constexpr int kBBytes = BN * kBKBytes;
+    // SfAtoms along K that one stage needs per 128 rows: K elements per stage / (4 * group)
+    static constexpr int kSfKAtoms = KIND == 0 ? 1 : (KIND == 1 ? 4 : 2);
+    static constexpr int kNAtoms = (BN + 127) / 128;
+    static constexpr int kSfaBytes = kSfKAtoms * 512;
+    static constexpr int kSfbBytes = kNAtoms * kSfaBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+    static constexpr int kEpiBufs = (KIND == 1 && BN == 256) ? 1 : 2;
+    static constexpr int kEpiBytes = kEpiWarps * kEpiBufs * kEpiBufBytes;
+    static constexpr int kBarBytes = 1024;
+    static constexpr int kStagesFit = (kSmemBudget - kEpiBytes - kBarBytes - 1024) / kStageBytes;
+    static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarBytes + 1024;
+
+    // tensor memory columns: two accumulator stages of BN columns; when
+    // BN == 256 they overlap by kOverlap columns so that the scale columns
+    // still fit in 512 (the epilogue drains the shared columns first).
+    static constexpr int kSfCols = kSfKAtoms * 4 * (1 + kNAtoms);
+    static constexpr int kOverlap = BN == 256 ? (kSfCols + 15) / 16 * 16 : 0;
+    static constexpr int kAccStride = BN - kOverlap;
+    static constexpr int kSfaCol = kAccStride + BN;
+    static constexpr int kSfbCol = kSfaCol + kSfKAtoms * 4;
+    static constexpr int kColsUsed = kSfaCol + kSfCols;
+    static constexpr int kTmemCols = kColsUsed <= 32 ? 32 : kColsUsed <= 64 ? 64 : kColsUsed <= 128 ? 128
+                                     : kColsUsed <= 256 ? 256 : 512;
+    static_assert(kColsUsed <= 512, "tensor memory budget");
+    static constexpr int kChunks = BN / kEpiChunk;
+    static constexpr int kOverlapChunks = (kOverlap + kEpiChunk - 1) / kEpiChunk;
+    static_assert(kStages >= 2, "pipeline depth");
+};
+
+struct Barriers {
+    uint64_t full[8];
+    uint64_t empty[8];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint64_t overlap_free[2];
+    uint32_t tmem_base;
+    uint32_t abort;
+};
+
+// Bounded mbarrier wait.  Returns false when the CTA is aborting.
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile uint32_t* abort,
+                                         uint32_t code) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    while (!ptx::mbar_try_wait(bar, parity)) {
+        if ((++spins & 31u) == 0u) {
+            if (*abort != 0u) return false;
+            if (ptx::globaltimer_ns() - t0 > kTimeoutNs) {
+                *abort = 1u;
+                atomicOr(&g_status[0], code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+struct TileCoord {
+    int m;
+    int n;
+};
+
+// Persistent static schedule: tile ids walk down groups of 8 row tiles, then
+// across columns, so one wave of CTAs shares a small set of A and B tiles in L2.
+__device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles_n) {
+    constexpr int kGroup = 8;
+    const int per_group = kGroup * tiles_n;
+    const int g = tile / per_group;
+    const int first_m = g * kGroup;
+    const int gsz = min(kGroup, tiles_m - first_m);
+    const int r = tile - g * per_group;
+    return {first_m + r % gsz, r / gsz};
+}
+
+template <int BN, int KIND>
+__device__ __forceinline__ uint32_t instr_desc(uint32_t sf_id) {
+    // block-scaled instruction descriptor: [4,6) SFB byte id, [7,10) A format,
+    // [10,13) B format, bit 15/16 A/B major (0 = K), [17,23) N >> 3,
+    // bit 23 scale format (1 = UE8M0, 0 = UE4M3), [24,29) M >> 4, [29,31) SFA byte id
+    constexpr uint32_t fmt = KIND == 0 ? 0u /* e4m3 */ : 1u /* e2m1 */;
+    constexpr uint32_t scale_fmt = KIND == 1 ? 0u : 1u;
+    return (sf_id << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(BN >> 3) << 17) | (scale_fmt << 23) |
+           (uint32_t(kBM >> 4) << 24) | (sf_id << 29);
+}
+
+template <int BN, int KIND>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+            const __grid_constant__ CUtensorMap tm_d, const uint8_t* __restrict__ sfa,
+            const uint8_t* __restrict__ sfb, const float* __restrict__ alpha,
+            __nv_bfloat16* __restrict__ out, int64_t ldo, int M, int N, int k_tiles, int kq_dim,
+            int tiles_m, int tiles_n, int direct_store) {
+    using C = Cfg<BN, KIND>;
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment: required by the 128-byte swizzle of the operand tiles
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* const smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+    const uint32_t a_base = smem_base;
+    const uint32_t b_base = a_base + C::kStages * C::kABytes;
+    const uint32_t sfa_base = b_base + C::kStages * C::kBBytes;
+    const uint32_t sfb_base = sfa_base + C::kStages * C::kSfaBytes;
+    const uint32_t epi_base = sfb_base + C::kStages * C::kSfbBytes;
+    const uint32_t bar_off = C::kStages * C::kStageBytes + C::kEpiBytes;
+    Barriers* const bars = reinterpret_cast<Barriers*>(smem + bar_off);
+    volatile uint32_t* const abort = &bars->abort;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&bars->full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&bars->acc_full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[s]), kEpiWarps);
+            ptx::mbar_init(ptx::smem_u32(&bars->overlap_free[s]), kEpiWarps);
+        }
+        bars->abort = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tmap(&tm_a);
+        ptx::prefetch_tmap(&tm_b);
+        ptx::prefetch_tmap(&tm_d);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<1>(ptx::smem_u32(&bars->tmem_base), C::kTmemCols);
+        ptx::tmem_relinquish<1>();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+
+    // Everything above overlaps the tail of the previous kernel under a
+    // programmatic launch; nothing below may run before its writes are visible.
+    ptx::pdl_wait();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+                const int m0 = tc.m * kBM;
+                const int n0 = tc.n * BN;
+                const uint8_t* const sfa_row = sfa + int64_t(tc.m) * kq_dim * 512;
+                const uint8_t* const sfb_row = sfb + int64_t(n0 / 128) * kq_dim * 512;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1u;
+                    ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ph ^ 1u, abort, kStatusProducer);
+                    if (!ok) break;
+                    const uint32_t full = ptx::smem_u32(&bars->full[s]);
+                    ptx::mbar_arrive_expect_tx(full, C::kStageBytes);
+                    ptx::tma_load_2d(a_base + s * C::kABytes, &tm_a, kt * kBKBytes, m0, full);
+                    ptx::tma_load_2d(b_base + s * C::kBBytes, &tm_b, kt * kBKBytes, n0, full);
+                    const int64_t koff = int64_t(kt) * C::kSfaBytes;
+                    ptx::bulk_load(sfa_base + s * C::kSfaBytes, sfa_row + koff, C::kSfaBytes, full);
+#pragma unroll
+                    for (int j = 0; j < C::kNAtoms; ++j) {
+                        ptx::bulk_load(sfb_base + s * C::kSfbBytes + j * C::kSfaBytes,
+                                       sfb_row + int64_t(j) * kq_dim * 512 + koff, C::kSfaBytes, full);
+                    }
+                }
+            }
+            // let a dependent kernel start its prologue
+            ptx::pdl_launch_dependents();
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0;
+            uint32_t t = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++t) {
+                const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+                const uint32_t as = t & 1u;
+                const uint32_t aph = (t >> 1) & 1u;
+                ok = wait_bar(ptx::smem_u32(&bars->acc_empty[as]), aph ^ 1u, abort, kStatusMma);
+                if (!ok) break;
+                if (C::kOverlap != 0 && t > 0) {
+                    // the previous tile's epilogue has drained the columns both stages share
+                    ok = wait_bar(ptx::smem_u32(&bars->overlap_free[as ^ 1u]), ((t - 1) >> 1) & 1u,
+                                  abort, kStatusMma);
+                    if (!ok) break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t acc = tmem + as * C::kAccStride;
+                // a 64-wide tile uses half of a 128-row scale atom
+                const uint32_t sfb_shift = BN == 64 ? uint32_t((tc.n * BN) % 128) / 32u : 0u;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1u;
+                    ok = wait_bar(ptx::smem_u32(&bars->full[s]), ph, abort, kStatusMma);
+                    if (!ok) break;
+                    ptx::tc_fence_after();
+                    // scales: shared memory -> tensor memory (4 columns per atom)
+#pragma unroll
+                    for (int a = 0; a < C::kSfKAtoms; ++a) {
+                        ptx::tc_copy_sf<1>(tmem + C::kSfaCol + a * 4,
+                                           ptx::smem_desc(sfa_base + s * C::kSfaBytes + a * 512, 0, 128, 0));
+#pragma unroll
+                        for (int j = 0; j < C::kNAtoms; ++j) {
+                            ptx::tc_copy_sf<1>(
+                                tmem + C::kSfbCol + (a * C::kNAtoms + j) * 4,
+                                ptx::smem_desc(sfb_base + s * C::kSfbBytes + (j * C::kSfKAtoms + a) * 512, 0,
+                                               128, 0));
+                        }
+                    }
+                    const uint64_t adesc = ptx::smem_desc(a_base + s * C::kABytes, 16, 1024, 2);
+                    const uint64_t bdesc = ptx::smem_desc(b_base + s * C::kBBytes, 16, 1024, 2);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        // 32 bytes of K per instruction: K = 32 (e4m3) or 64 (e2m1)
+                        uint32_t atom, sf_id;
+                        if constexpr (KIND == 0) {
+                            atom = 0;
+                            sf_id = k;
+                        } else if constexpr (KIND == 1) {
+                            atom = k;
+                            sf_id = 0;
+                        } else {
+                            atom = k >> 1;
+                            sf_id = (k & 1) * 2;
+                        }
+                        ptx::tc_mma_block_scaled<1, KIND>(
+                            acc, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2),
+                            instr_desc<BN, KIND>(sf_id), tmem + C::kSfaCol + atom * 4,
+                            tmem + C::kSfbCol + atom * C::kNAtoms * 4 + sfb_shift,
+                            (kt > 0 || k > 0) ? 1u : 0u);
+                    }
+                    // stage s may be refilled once these MMAs have read it
+                    ptx::tc_commit(ptx::smem_u32(&bars->empty[s]));
+                }
+                if (ok) ptx::tc_commit(ptx::smem_u32(&bars->acc_full[as]));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int ew = warp - 2;                  // staging buffer owner
+        const uint32_t lane_base = (warp & 3) * 32;  // tensor-memory lanes this warp may read
+        const float scale = (KIND == 1 && alpha != nullptr) ? __ldg(alpha) : 1.0f;
+        uint32_t t = 0;
+        uint32_t stores = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++t) {
+            const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+            const int m0 = tc.m * kBM;
+            const int n0 = tc.n * BN;
+            const uint32_t as = t & 1u;
+            const uint32_t aph = (t >> 1) & 1u;
+            ok = wait_bar(ptx::smem_u32(&bars->acc_full[as]), aph, abort, kStatusEpilogue);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const uint32_t acc = tmem + as * C::kAccStride + (lane_base << 16);
+#pragma unroll 1
+            for (int ci = 0; ci < C::kChunks; ++ci) {
+                // stage 0 shares its highest columns with stage 1, stage 1 its lowest with stage 0
+                const int c = (C::kOverlap != 0 && as == 0) ? C::kChunks - 1 - ci : ci;
+                uint32_t r[32];
+                ptx::tc_load_32x32(acc + c * kEpiChunk, r);
+                ptx::tc_wait_ld();
+                if (C::kOverlap != 0 && ci == C::kOverlapChunks - 1) {
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->overlap_free[as]));
+                }
+                if (ci == C::kChunks - 1) {
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[as]));
+                }
+                uint32_t p[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const __nv_bfloat162 v = __float22bfloat162_rn(make_float2(
+                        __uint_as_float(r[2 * i]) * scale, __uint_as_float(r[2 * i + 1]) * scale));
+                    p[i] = *reinterpret_cast<const uint32_t*>(&v);
+                }
+                const int row = m0 + int(lane_base) + lane;
+                const int col = n0 + c * kEpiChunk;
+                if (direct_store) {
+                    if (row < M) {
+                        uint4* dst = reinterpret_cast<uint4*>(out + int64_t(row) * ldo + col);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            dst[j] = make_uint4(p[4 * j], p[4 * j + 1], p[4 * j + 2], p[4 * j + 3]);
+                        }
+                    }
+                } else {
+                    const uint32_t buf =
+                        epi_base + (ew * C::kEpiBufs + (stores % C::kEpiBufs)) * kEpiBufBytes;
+                    // the TMA store that last read this buffer must be done with it
+                    if (lane == 0) ptx::bulk_wait_read<C::kEpiBufs - 1>();
+                    __syncwarp();
+                    // 32 rows x 64 bytes, 64-byte swizzle: 16-byte chunk j of row r
+                    // sits at chunk j ^ ((r >> 1) & 3)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t dst = buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                                     "r"(p[4 * j]), "r"(p[4 * j + 1]), "r"(p[4 * j + 2]),
+                                     "r"(p[4 * j + 3])
+                                     : "memory");
+                    }
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_store_2d(&tm_d, buf, col, m0 + int(lane_base));
+                        ptx::bulk_commit();
+                    }
+                    ++stores;
+                }
+            }
+        }
+        if (lane == 0) ptx::bulk_wait<0>();
+    }
+
+    if (*abort != 0u) {
+        // bounded grace period for copies / MMAs still in flight before the
+        // shared and tensor memory they target is released
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc<1>(tmem, C::kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------- host
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            p = nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// rank-2 row-major tensor map: `inner` elements per row, `rows` rows, `pitch` bytes between rows
+bool make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base, uint64_t inner,
+                  uint64_t rows, uint64_t pitch, uint32_t box_inner, uint32_t box_rows,
+                  CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {pitch};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct GemmArgs {
+    const void* a;
+    const void* b;
+    const uint8_t* sfa;
+    const uint8_t* sfb;
+    const float* alpha;
+    __nv_bfloat16* out;
+    int64_t ldo;
+    int m, n;
+    int64_t k_bytes;
+    int kq_dim;
+    int sm_count;
+    bool pdl;
+    bool direct_store;
+    cudaStream_t stream;
+};
+
+template <int BN, int KIND>
+int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
+    using C = Cfg<BN, KIND>;
+    static std::once_flag once[16];
+    int dev = 0;
+    HQ_CUDA_TRY(cudaGetDevice(&dev));
+    cudaError_t attr_err = cudaSuccess;
+    std::call_once(once[dev & 15], [&] {
+        attr_err = cudaFuncSetAttribute(gemm_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        C::kSmemBytes);
+    });
+    HQ_CUDA_TRY(attr_err);
+
+    CUtensorMap tm_a, tm_b, tm_d;
+    const bool maps_ok =
+        make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.a, uint64_t(g.k_bytes), uint64_t(g.m),
+                     uint64_t(g.k_bytes), kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B) &&
+        make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes), uint64_t(g.n),
+                     uint64_t(g.k_bytes), kBKBytes, BN, CU_TENSOR_MAP_SWIZZLE_128B) &&
+        make_tmap_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out, uint64_t(g.n), uint64_t(g.m),
+                     uint64_t(g.ldo) * 2, kEpiChunk, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (!maps_ok) {
+        return fail(err, errlen, HQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the GEMM operands");
+    }
+    const int tiles_m = (g.m + kBM - 1) / kBM;
+    const int tiles_n = g.n / BN;
+    const int grid = min(g.sm_count, tiles_m * tiles_n);
+    const int k_tiles = int(g.k_bytes / kBKBytes);
+    HQ_CUDA_TRY(launch(gemm_kernel<BN, KIND>, dim3(grid), dim3(kThreads), size_t(C::kSmemBytes), g.stream,
+                       g.pdl, 1, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.out, g.ldo, g.m, g.n, k_tiles,
+                       g.kq_dim, tiles_m, tiles_n, g.direct_store ? 1 : 0));
+    return HQ_OK;
+}
+
+const char* mode_name(int mode) {
+    switch (mode) {
+        case HQ_MODE_W8A8_MXFP8:
+            return "w8a8-mxfp8";
+        case HQ_MODE_W4A4_MXFP4:
+            return "w4a4-mxfp4";
+        default:
+            return "w4a4-nvfp4";
+    }
+}
+
+// Shape legality follows the reference's "some compiled tile fits" rule
+// (csrc/kernel/gemm/gemm_dispatch.cuh:65-100 over the tiles of gemm_tile.cuh:371-395):
+// MXFP8 needs K % 128 == 0 and N % 64 == 0, the FP4 modes K % 256 == 0 and
+// N % 128 == 0; any M >= 1.  Returns the tile width, 0 when nothing fits.
+int pick_tile_n(int64_t m, int64_t n, int64_t k, int mode, int sm_count) {
+    const bool fp8 = mode == HQ_MODE_W8A8_MXFP8;
+    if (m < 1 || n < 1 || k < 1) return 0;
+    if (fp8 ? (k % 128 != 0 || n % 64 != 0) : (k % 256 != 0 || n % 128 != 0)) return 0;
+    const int64_t tiles_m = (m + kBM - 1) / kBM;
+    // widest tile that divides N and still gives every SM a tile; failing
+    // that, the narrowest that divides N (most CTAs streaming the weight)
+    const int widths[3] = {256, 128, 64};
+    int narrowest = 0;
+    for (int w : widths) {
+        if (n % w != 0 || (w == 64 && !fp8)) continue;
+        if (tiles_m * (n / w) >= sm_count) return w;
+        narrowest = w;
+    }
+    return narrowest;
+}
+
+std::mutex g_sm_mutex;
+int g_sm_cache[64];
+
+}  // namespace
+}  // namespace hq
+
+extern "C" int hq_sm_count(int device) {
+    if (device < 0 || device >= 64) {
+        if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+    }
+    std::lock_guard<std::mutex> lock(hq::g_sm_mutex);
+    if (hq::g_sm_cache[device] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+        hq::g_sm_cache[device] = n;
+    }
+    return hq::g_sm_cache[device];
+}
+
+extern "C" int hq_describe_tile(int64_t m, int64_t n, int64_t k, int mode, int sm_count, int device,
+                                char* buf, size_t buflen) {
+    if (hq_group_size(mode) == 0) return hq::fail(buf, buflen, HQ_ERR_INVALID, "Unsupported mode: %d", mode);
+    const int sm = sm_count > 0 ? sm_count : hq_sm_count(device);
+    const int bn = hq::pick_tile_n(m, n, k, mode, sm > 0 ? sm : 148);
+    if (bn == 0) {
+        return hq::fail(buf, buflen, HQ_ERR_INVALID,
+                        "No dense %s tile for M=%lld (grid M=%lld), N=%lld, K=%lld", hq::mode_name(mode),
+                        (long long)(m < 128 ? m : hq_sf_rows(m)), (long long)(m < 128 ? m : hq_sf_rows(m)), (long long)n,
+                        (long long)k);
+    }
+    if (buf != nullptr && buflen > 0) {
+        snprintf(buf, buflen, "[gemm] mode=dense kind=%s m=%lld n=%lld k=%lld sm=%d -> %dx%d/%d pair=0",
+                 hq::mode_name(mode), (long long)m, (long long)n, (long long)k, sm, hq::kBM, bn,
+                 mode == HQ_MODE_W8A8_MXFP8 ? 128 : 256);
+    }
+    return HQ_OK;
+}
+
+extern "C" int hq_dense_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* out,
+                             const float* alpha, int64_t m, int64_t n, int64_t k, int64_t sfa_bytes,
+                             int64_t sfb_bytes, int64_t ldo, int mode, int epilogue, int sm_count,
+                             int use_pdl, int device, void* stream, char* err, size_t errlen) {
+    using hq::fail;
+    const int group = hq_group_size(mode);
+    if (group == 0) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "Unsupported mode: %d. Expected 'w8a8-mxfp8', 'w4a4-mxfp4' or 'w4a4-nvfp4'.", mode);
+    }
+    if (epilogue != HQ_EPILOGUE_IDENTITY) {
+        return fail(err, errlen, HQ_ERR_UNSUPPORTED, "Unsupported epilogue %d for %s", epilogue,
+                    hq::mode_name(mode));
+    }
+    if (m < 0 || n < 0 || k < 0 || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) {
+        return fail(err, errlen, HQ_ERR_INVALID, "input must be a 2D tensor of shape [M, K]");
+    }
+    if (mode == HQ_MODE_W4A4_MXFP4 && alpha != nullptr) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "'w4a4-mxfp4' does not take alpha; the global scaling factor is only used by "
+                    "'w4a4-nvfp4'.");
+    }
+    if (mode == HQ_MODE_W4A4_NVFP4 && alpha == nullptr) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "W4A4-nvfp4 mode requires alpha input (per-batch scaling).");
+    }
+    if (m == 0 || n == 0) return HQ_OK;
+
+    // shape legality first: it needs no device
+    if (hq::pick_tile_n(m, n, k, mode, 148) == 0) {
+        return fail(err, errlen, HQ_ERR_INVALID, "No dense %s tile for M=%lld (grid M=%lld), N=%lld, K=%lld",
+                    hq::mode_name(mode), (long long)(m < 128 ? m : hq_sf_rows(m)),
+                    (long long)(m < 128 ? m : hq_sf_rows(m)), (long long)n, (long long)k);
+    }
+    const int64_t sf_k = k / group;
+    const int64_t need_a = hq_sf_rows(m) * sf_k;
+    const int64_t need_b = hq_sf_rows(n) * sf_k;
+    if (sfa_bytes < need_a) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "sfa must hold whole 128-row SfAtoms: expected at least %lld elements (%lld x %lld) "
+                    "for M=%lld, got %lld",
+                    (long long)need_a, (long long)hq_sf_rows(m), (long long)sf_k, (long long)m,
+                    (long long)sfa_bytes);
+    }
+    if (sfb_bytes < need_b) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "sfb must hold whole 128-row SfAtoms: expected at least %lld elements (%lld x %lld) "
+                    "for N=%lld, got %lld",
+                    (long long)need_b, (long long)hq_sf_rows(n), (long long)sf_k, (long long)n,
+                    (long long)sfb_bytes);
+    }
+    const hq::DeviceGuard guard(device);
+    if (!guard.ok()) return fail(err, errlen, HQ_ERR_CUDA, "cannot select CUDA device %d", device);
+    const int sm_all = hq_sm_count(device);
+    const int sm = sm_count > 0 ? (sm_count < sm_all || sm_all == 0 ? sm_count : sm_all) : sm_all;
+    if (sm <= 0) return fail(err, errlen, HQ_ERR_CUDA, "cannot query the SM count of device %d", device);
+    const int bn = hq::pick_tile_n(m, n, k, mode, sm);
+    if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || out == nullptr) {
+        return fail(err, errlen, HQ_ERR_INVALID, "null pointer argument");
+    }
+    if (!hq::aligned(a, 16) || !hq::aligned(b, 16) || !hq::aligned(sfa, 16) || !hq::aligned(sfb, 16) ||
+        !hq::aligned(out, 16) || ldo < n || ldo % 8 != 0) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "operands, scales and output must be 16-byte aligned and the output row stride a "
+                    "multiple of 8 elements");
+    }
+
+    hq::GemmArgs g;
+    g.a = a;
+    g.b = b;
+    g.sfa = static_cast<const uint8_t*>(sfa);
+    g.sfb = static_cast<const uint8_t*>(sfb);
+    g.alpha = alpha;
+    g.out = static_cast<__nv_bfloat16*>(out);
+    g.ldo = ldo;
+    g.m = int(m);
+    g.n = int(n);
+    g.k_bytes = mode == HQ_MODE_W8A8_MXFP8 ? k : k / 2;
+    g.kq_dim = int(sf_k / 4);
+    g.sm_count = sm;
+    g.pdl = use_pdl != 0;
+    static const bool direct = [] {
+        const char* e = getenv("HALOPS_B200_EPILOGUE");
+        return e != nullptr && strcmp(e, "direct") == 0;
+    }();
+    g.direct_store = direct;
+    g.stream = static_cast<cudaStream_t>(stream);
+
+#define HQ_DISPATCH(KIND)                                                \
+    switch (bn) {                                                        \
+        case 256:                                                        \
+            return hq::launch_tile<256, KIND>(g, err, errlen);           \
+        case 128:                                                        \
+            return hq::launch_tile<128, KIND>(g, err, errlen);           \
+        default:                                                         \
+            return hq::launch_tile<64, KIND>(g, err, errlen);            \
+    }
+    if (mode == HQ_MODE_W8A8_MXFP8) {
+        HQ_DISPATCH(0)
+    } else if (mode == HQ_MODE_W4A4_NVFP4) {
+        HQ_DISPATCH(1)
+    } else {
+        HQ_DISPATCH(2)
+    }
+#undef HQ_DISPATCH
+}
+
+extern "C" int hq_device_status(int device, void* stream, uint32_t* status, char* err, size_t errlen) {
+    const hq::DeviceGuard guard(device);
+    if (!guard.ok()) return hq::fail(err, errlen, HQ_ERR_CUDA, "cannot select CUDA device %d", device);
+    HQ_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    uint32_t host[4] = {0, 0, 0, 0};
+    HQ_CUDA_TRY(cudaMemcpyFromSymbol(host, hq::g_status, sizeof(host)));
+    if (host[0] != 0) {
+        const uint32_t zero[4] = {0, 0, 0, 0};
+        HQ_CUDA_TRY(cudaMemcpyToSymbol(hq::g_status, zero, sizeof(zero)));
+    }
+    if (status != nullptr) *status = host[0];
+    if (host[0] != 0) {
+        return hq::fail(err, errlen, HQ_ERR_DEVICE,
+                        "a GEMM role gave up on a bounded wait (status 0x%x: 1 producer, 2 MMA, 4 epilogue)",
+                        host[0]);
+    }
+    return HQ_OK;
+}
+
+extern "C" const char* hq_version(void) { return "halops_b200 0.1 (sm_100a)"; }

@@ -1,0 +1,382 @@
+// Group-wise block-scale quantizer: bf16/fp16 [m, k] -> MXFP8 / MXFP4 / NVFP4
+// codes plus UE8M0 / UE4M3 scales, emitted directly in the 128x4 SfAtom order
+// the block-scaled tensor-core instructions consume.
+//
+// Same results, bit for bit, as the reference kernel
+// (csrc/kernel/gemm/group_wise_quant.cu:123-231, csrc/common/mx_quant.cuh:104-150)
+// as modelled by its own tests (tests/test_group_wise_quant.py:40-213), but a
+// different decomposition: the reference gives one thread one whole group
+// (lane-strided 16-byte loads); here a warp streams 2 KiB-contiguous row
+// segments with fully coalesced 16-byte loads, 4 (or 2, or 1) lanes share a
+// group and reduce its amax with warp shuffles, and the scale exponent is
+// derived from the amax bit pattern with integer arithmetic instead of
+// log2f/exp2f, so the result does not depend on fast-math code generation.
+//
+// HBM-bound: algorithmic bytes per element are 2 (read) + 1 + 1/32 (MXFP8),
+// 2 + 1/2 + 1/32 (MXFP4), 2 + 1/2 + 1/16 (NVFP4).
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace hq {
+namespace {
+
+constexpr int kWarpsPerCta = 8;
+constexpr int kThreads = kWarpsPerCta * 32;
+constexpr int kColsPerWarp = 1024;  // elements of one row a warp handles
+constexpr float kE4m3Max = 448.0f;
+constexpr float kE2m1Max = 6.0f;
+constexpr float kAmaxFloor = 1e-10f;  // reference: mx_quant.cuh:50
+
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]);
+
+template <>
+__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& v,
+                                                       float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+template <>
+__device__ __forceinline__ void unpack8<__half>(const uint4& v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        f[2 * i] = p.x;
+        f[2 * i + 1] = p.y;
+    }
+}
+
+// UE8M0 byte of ceil(log2(amax / D)) + 127 with the reference kernel's
+// observed behaviour that an exact power of two below 1 comes out one higher
+// (tests/test_group_wise_quant.py:40-53).  D = 1.75 * 2^8 (448) or 1.5 * 2^2
+// (6): with B the biased exponent and M the mantissa field of amax,
+//   amax / D = (1.M / 1.kk) * 2^(B - 127 - S)
+// lies strictly inside a binade unless M equals D's mantissa, so
+//   e = B - S - 1 + [M >= D.M] + 1, minus one when the quotient is an exact
+// power of two that is >= 1.  Exact for every amax that comes from a bf16 or
+// fp16 value and for the floor constant.
+template <uint32_t kMant, int kShift>
+__device__ __forceinline__ uint32_t ue8m0_of_amax(float amax) {
+    const uint32_t u = __float_as_uint(amax);
+    int e = int((u + (0x00800000u - kMant)) >> 23) - kShift;
+    const bool exact_ge_one =
+        (u & 0x007fffffu) == kMant && (u >> 23) >= uint32_t(127 + kShift);
+    e -= exact_ge_one ? 1 : 0;
+    return uint32_t(min(max(e, 0), 254));
+}
+
+// 2^(127 - e); e == 254 gives 0, which is what the reference's flush-to-zero
+// exp2f(-127) returns.
+__device__ __forceinline__ float inv_pow2(uint32_t e) {
+    return __uint_as_float((254u - e) << 23);
+}
+
+__device__ __forceinline__ float clamp_sym(float x, float lim) {
+    return fminf(fmaxf(x, -lim), lim);  // NaN -> -lim, as in the reference
+}
+
+// Two e2m1 codes (x in the low nibble), nearest with ties away from zero; a
+// negative value that rounds to zero keeps its sign bit, -0.0 does not.
+// cvt rounds ties to even, so the midpoints that would go to the smaller
+// (even) code - 0.25, 1.25, 2.5, 5 - are first moved one ulp outwards.
+__device__ __forceinline__ uint32_t e2m1x2(float x, float y) {
+    const auto away = [](float v) {
+        v += 0.0f;  // -0.0 -> +0.0
+        const uint32_t b = __float_as_uint(v);
+        const uint32_t a = b & 0x7fffffffu;
+        const bool tie = ((a - 0x3fa00000u) & 0xfe7fffffu) == 0u || a == 0x3e800000u;
+        return __uint_as_float(b + (tie ? 1u : 0u));
+    };
+    return __nv_cvt_float2_to_fp4x2(make_float2(away(x), away(y)), __NV_E2M1,
+                                    cudaRoundNearest);
+}
+
+__device__ __forceinline__ uint32_t e4m3x2(float x, float y) {
+    return __nv_cvt_float2_to_fp8x2(make_float2(x, y), __NV_SATFINITE, __NV_E4M3);
+}
+
+__device__ __forceinline__ int64_t sf_atom_offset(int64_t row, int kb, int kb_dim) {
+    return ((row >> 7) * (kb_dim >> 2) + (kb >> 2)) * 512 + (row & 31) * 16 +
+           ((row >> 5) & 3) * 4 + (kb & 3);
+}
+
+// kEpl elements per lane and piece: 8 for the 32-element groups (4 lanes per
+// group), 16 for NVFP4 (one lane per group).
+template <typename T, int kMode, bool kSwizzle>
+__global__ void __launch_bounds__(kThreads)
+group_wise_quant_kernel(const T* __restrict__ input, int64_t ld,
+                        uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf,
+                        int64_t m, int64_t rows_total, int k, int kb_dim) {
+    constexpr bool kNv = kMode == HQ_MODE_W4A4_NVFP4;
+    constexpr bool kFp4 = kMode != HQ_MODE_W8A8_MXFP8;
+    constexpr int kEpl = kNv ? 16 : 8;
+    constexpr int kPieces = kColsPerWarp / (32 * kEpl);  // 4 or 2
+    constexpr int kGroup = kNv ? 16 : 32;
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int64_t row = int64_t(blockIdx.x) * kWarpsPerCta + warp;
+    const int col0 = blockIdx.y * kColsPerWarp;
+
+    // The first global access is below: with a programmatic launch the index
+    // math above overlaps the tail of the producing kernel.
+    pdl_wait();
+    pdl_launch_dependents();
+
+    if (row >= rows_total) return;
+
+    if (row >= m) {
+        // padding rows of the last SfAtom (swizzled layout only): zero scales
+        if constexpr (kSwizzle) {
+#pragma unroll
+            for (int p = 0; p < kPieces; ++p) {
+                const int col = col0 + (p * 32 + lane) * kEpl;
+                const int kb = col / kGroup;
+                const bool lead = kNv ? (lane & 3) == 0 : (lane & 15) == 0;
+                if (col < k && lead) {
+                    *reinterpret_cast<uint32_t*>(out_sf + sf_atom_offset(row, kb, kb_dim)) = 0u;
+                }
+            }
+        }
+        return;
+    }
+
+    const T* const in_row = input + row * ld;
+    uint4 raw[kPieces][kEpl / 8];
+#pragma unroll
+    for (int p = 0; p < kPieces; ++p) {
+        const int col = col0 + (p * 32 + lane) * kEpl;
+#pragma unroll
+        for (int h = 0; h < kEpl / 8; ++h) {
+            raw[p][h] = col < k ? ld_stream(in_row + col + h * 8) : make_uint4(0, 0, 0, 0);
+        }
+    }
+
+#pragma unroll
+    for (int p = 0; p < kPieces; ++p) {
+        const int col = col0 + (p * 32 + lane) * kEpl;
+        const bool active = col < k;
+        float v[kEpl];
+#pragma unroll
+        for (int h = 0; h < kEpl / 8; ++h) {
+            float f[8];
+            unpack8<T>(raw[p][h], f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[h * 8 + i] = f[i];
+        }
+        float amax = kAmaxFloor;
+#pragma unroll
+        for (int i = 0; i < kEpl; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        if constexpr (!kNv) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        }
+
+        uint32_t sf_byte;
+        float inv;
+        if constexpr (kMode == HQ_MODE_W8A8_MXFP8) {
+            sf_byte = ue8m0_of_amax<0x00600000u, 8>(amax);
+            inv = inv_pow2(sf_byte);
+        } else if constexpr (kMode == HQ_MODE_W4A4_MXFP4) {
+            sf_byte = ue8m0_of_amax<0x00400000u, 2>(amax);
+            inv = inv_pow2(sf_byte);
+        } else {
+            const float s = fminf(fmaxf(__fdiv_rn(amax, kE2m1Max), 0.0f), kE4m3Max);
+            sf_byte = __nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3);
+            // UE4M3 may round a tiny scale to 0: smallest positive code (2^-9)
+            if (sf_byte == 0u) sf_byte = 1u;
+            const float dec = __half2float(__half(__nv_cvt_fp8_to_halfraw(
+                static_cast<__nv_fp8_storage_t>(sf_byte), __NV_E4M3)));
+            inv = __frcp_rn(dec);
+        }
+
+        if constexpr (!kFp4) {
+            uint32_t w[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const uint32_t lo = e4m3x2(clamp_sym(__fmul_rn(v[4 * i], inv), kE4m3Max),
+                                           clamp_sym(__fmul_rn(v[4 * i + 1], inv), kE4m3Max));
+                const uint32_t hi = e4m3x2(clamp_sym(__fmul_rn(v[4 * i + 2], inv), kE4m3Max),
+                                           clamp_sym(__fmul_rn(v[4 * i + 3], inv), kE4m3Max));
+                w[i] = lo | (hi << 16);
+            }
+            if (active) {
+                *reinterpret_cast<uint2*>(out_q + row * int64_t(k) + col) = make_uint2(w[0], w[1]);
+            }
+        } else {
+            uint32_t w[kEpl / 8];
+#pragma unroll
+            for (int h = 0; h < kEpl / 8; ++h) {
+                uint32_t acc = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float a = clamp_sym(__fmul_rn(v[h * 8 + 2 * i], inv), kE2m1Max);
+                    const float b = clamp_sym(__fmul_rn(v[h * 8 + 2 * i + 1], inv), kE2m1Max);
+                    acc |= (e2m1x2(a, b) & 0xffu) << (8 * i);
+                }
+                w[h] = acc;
+            }
+            if (active) {
+                uint8_t* dst = out_q + row * int64_t(k >> 1) + (col >> 1);
+                if constexpr (kNv) {
+                    *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[kEpl / 8 - 1]);
+                } else {
+                    *reinterpret_cast<uint32_t*>(dst) = w[0];
+                }
+            }
+        }
+
+        const int kb = col / kGroup;
+        if constexpr (kSwizzle) {
+            // the four scale bytes of one SfAtom word sit in lanes L, L+s, L+2s, L+3s
+            constexpr int s = kNv ? 1 : 4;
+            uint32_t word = sf_byte;
+            word |= __shfl_down_sync(0xffffffffu, word, s) << 8;
+            word |= __shfl_down_sync(0xffffffffu, word, 2 * s) << 16;
+            if (active && (lane & (4 * s - 1)) == 0) {
+                *reinterpret_cast<uint32_t*>(out_sf + sf_atom_offset(row, kb, kb_dim)) = word;
+            }
+        } else {
+            const bool lead = kNv ? true : (lane & 3) == 0;
+            if (active && lead) out_sf[row * int64_t(kb_dim) + kb] = uint8_t(sf_byte);
+        }
+    }
+}
+
+template <typename T, int kMode>
+cudaError_t launch_mode(const T* in, int64_t ld, uint8_t* q, uint8_t* sf, int64_t m,
+                        int k, bool swizzle, bool pdl, cudaStream_t stream) {
+    const int kb_dim = k / (kMode == HQ_MODE_W4A4_NVFP4 ? 16 : 32);
+    const int64_t rows_total = swizzle ? hq_sf_rows(m) : m;
+    const dim3 grid(unsigned((rows_total + kWarpsPerCta - 1) / kWarpsPerCta),
+                    unsigned((k + kColsPerWarp - 1) / kColsPerWarp));
+    if (swizzle) {
+        return launch(group_wise_quant_kernel<T, kMode, true>, grid, dim3(kThreads), 0,
+                      stream, pdl, 1, in, ld, q, sf, m, rows_total, k, kb_dim);
+    }
+    return launch(group_wise_quant_kernel<T, kMode, false>, grid, dim3(kThreads), 0,
+                  stream, pdl, 1, in, ld, q, sf, m, rows_total, k, kb_dim);
+}
+
+template <typename T>
+cudaError_t launch_dtype(const void* in, int64_t ld, void* q, void* sf, int64_t m, int k,
+                         int mode, bool swizzle, bool pdl, cudaStream_t stream) {
+    const T* p = static_cast<const T*>(in);
+    uint8_t* pq = static_cast<uint8_t*>(q);
+    uint8_t* psf = static_cast<uint8_t*>(sf);
+    switch (mode) {
+        case HQ_MODE_W8A8_MXFP8:
+            return launch_mode<T, HQ_MODE_W8A8_MXFP8>(p, ld, pq, psf, m, k, swizzle, pdl, stream);
+        case HQ_MODE_W4A4_MXFP4:
+            return launch_mode<T, HQ_MODE_W4A4_MXFP4>(p, ld, pq, psf, m, k, swizzle, pdl, stream);
+        default:
+            return launch_mode<T, HQ_MODE_W4A4_NVFP4>(p, ld, pq, psf, m, k, swizzle, pdl, stream);
+    }
+}
+
+}  // namespace
+}  // namespace hq
+
+extern "C" int hq_parse_mode(const char* mode) {
+    if (mode == nullptr) return -1;
+    if (strcmp(mode, "w8a8-mxfp8") == 0) return HQ_MODE_W8A8_MXFP8;
+    if (strcmp(mode, "w4a4-mxfp4") == 0) return HQ_MODE_W4A4_MXFP4;
+    if (strcmp(mode, "w4a4-nvfp4") == 0) return HQ_MODE_W4A4_NVFP4;
+    return -1;
+}
+
+extern "C" int hq_group_size(int mode) {
+    switch (mode) {
+        case HQ_MODE_W8A8_MXFP8:
+        case HQ_MODE_W4A4_MXFP4:
+            return 32;
+        case HQ_MODE_W4A4_NVFP4:
+            return 16;
+        default:
+            return 0;
+    }
+}
+
+extern "C" int64_t hq_sf_rows(int64_t m) { return (m + 127) / 128 * 128; }
+
+extern "C" int hq_group_wise_quant(const void* input, int64_t ld_elems, int in_dtype,
+                                   int64_t m, int64_t k, int mode, int use_swizzle,
+                                   int use_pdl, void* out_q, void* out_sf, int device,
+                                   void* stream, char* err, size_t errlen) {
+    using hq::fail;
+    const int group = hq_group_size(mode);
+    if (group == 0) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "Unsupported quantization mode: %d. Expected 'w8a8-mxfp8', "
+                    "'w4a4-mxfp4' or 'w4a4-nvfp4'.", mode);
+    }
+    if (in_dtype != HQ_DTYPE_BF16 && in_dtype != HQ_DTYPE_FP16) {
+        return fail(err, errlen, HQ_ERR_INVALID, "input dtype must be bfloat16 or float16");
+    }
+    if (m < 0 || k < 0 || k > INT32_MAX) {
+        return fail(err, errlen, HQ_ERR_INVALID, "input must be a 2D tensor of shape [m, k]");
+    }
+    if (k % group != 0) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "k must be divisible by the quantization group size (%d), got k=%lld",
+                    group, static_cast<long long>(k));
+    }
+    const int64_t kb_dim = k / group;
+    if (use_swizzle && kb_dim % 4 != 0) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "scale kb_dim must be divisible by 4 for CUTLASS SfAtom layout, got %lld",
+                    static_cast<long long>(kb_dim));
+    }
+    if (m == 0 || k == 0) return HQ_OK;
+    if (input == nullptr || out_q == nullptr || out_sf == nullptr) {
+        return fail(err, errlen, HQ_ERR_INVALID, "null pointer argument");
+    }
+    if (ld_elems < k || (ld_elems * 2) % 16 != 0 || !hq::aligned(input, 16)) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "input rows must be contiguous and 16-byte aligned");
+    }
+    if (!hq::aligned(out_q, 16) || !hq::aligned(out_sf, use_swizzle ? 16 : 1)) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "output_quant / output_sf must be 16-byte aligned");
+    }
+    if ((m + 7) / 8 > INT32_MAX) {
+        return fail(err, errlen, HQ_ERR_INVALID, "m is too large for one launch");
+    }
+    const hq::DeviceGuard guard(device);
+    if (!guard.ok()) return fail(err, errlen, HQ_ERR_CUDA, "cannot select CUDA device %d", device);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const cudaError_t e =
+        in_dtype == HQ_DTYPE_BF16
+            ? hq::launch_dtype<__nv_bfloat16>(input, ld_elems, out_q, out_sf, m, int(k), mode,
+                                              use_swizzle != 0, use_pdl != 0, s)
+            : hq::launch_dtype<__half>(input, ld_elems, out_q, out_sf, m, int(k), mode,
+                                       use_swizzle != 0, use_pdl != 0, s);
+    HQ_CUDA_TRY(e);
+    return HQ_OK;
+}

@@ -1,0 +1,4 @@
+from .dense_gemm import EpilogueOp, dense_gemm, interleave_gate_up
+from .group_wise_quant import group_wise_quant
+
+__all__ = ["EpilogueOp", "dense_gemm", "group_wise_quant", "interleave_gate_up"]

@@ -1,0 +1,163 @@
+"""``dense_gemm``: same signature, defaults and error texts as the reference's
+``halops.dense_gemm`` (``halops/gemm/dense_gemm.py:44-135``; host checks of
+``csrc/kernel/gemm/dense_gemm.cu:23-189``), executed by this package's
+tcgen05 kernel through the C ABI.  Built: the Identity epilogue without bias
+for ``w8a8-mxfp8``, ``w4a4-nvfp4`` and ``w4a4-mxfp4``."""
+
+from __future__ import annotations
+
+import enum
+from typing import Optional
+
+import torch
+
+from .. import _native
+
+__all__ = ["dense_gemm", "interleave_gate_up", "EpilogueOp"]
+
+_GLU_INTERLEAVE = 16
+
+
+class EpilogueOp(enum.IntEnum):
+    """Values of the reference enum (``csrc/kernel/gemm/epilogue_op.h:21-28``)."""
+
+    Identity = 0
+    Quant = 1
+    GateMulQuant = 2
+    Sigmoid = 3
+    SituQuant = 4
+    SigmoidGateMulQuant = 5
+
+
+def interleave_gate_up(t: torch.Tensor) -> torch.Tensor:
+    """Reorder ``[gate; up]`` rows into alternating blocks of 16 rows (gate rows
+    ``16i..16i+15``, then up rows ``16i..16i+15``), the row order the
+    reference's SituQuant epilogue expects (``halops/gemm/dense_gemm.py:30-41``)."""
+    gate, up = t.view(2, -1, _GLU_INTERLEAVE, *t.shape[1:]).unbind(0)
+    return torch.stack([gate, up], 1).flatten(0, 2)
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def dense_gemm(
+    input: torch.Tensor,
+    weight: torch.Tensor,
+    sfa: torch.Tensor,
+    sfb: torch.Tensor,
+    output: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    alpha: Optional[torch.Tensor] = None,
+    sm_count: int = -1,
+    mode: str = "w8a8-mxfp8",
+    use_pdl: bool = True,
+    epilogue: EpilogueOp = EpilogueOp.Identity,
+    output_sf: Optional[torch.Tensor] = None,
+    situ_beta: float = 4.0,
+    situ_linear_beta: Optional[float] = 25.0,
+) -> None:
+    """``output = bf16(alpha * (input @ weight^T))`` on the sm_100a tensor cores.
+
+    Args:
+        input: [M, K] float8_e4m3fn, or [M, K/2] uint8 packed e2m1 (w4a4 modes).
+        weight: [N, K] / [N, K/2], same encoding.
+        sfa / sfb: uint8 block scales in SfAtom order covering whole 128-row
+            atoms, exactly what ``group_wise_quant`` returns.
+        output: [M, N] bfloat16, written in place.
+        alpha: float32 [1]; required for ``w4a4-nvfp4``, rejected for
+            ``w4a4-mxfp4``, ignored for ``w8a8-mxfp8``.
+        sm_count: SMs to use (-1: all).
+        mode: ``"w8a8-mxfp8"``, ``"w4a4-mxfp4"`` or ``"w4a4-nvfp4"``.
+        use_pdl: launch with programmatic stream serialisation.
+        bias, epilogue (other than Identity), output_sf, situ_*: accepted for
+            signature compatibility; not built, a RuntimeError says so.
+    """
+    _check(
+        mode in _native.MODE_IDS,
+        f"Unsupported mode: {mode}. Expected 'w8a8-mxfp8', 'w4a4-mxfp4' or 'w4a4-nvfp4'.",
+    )
+    _check(input.dim() == 2, "input must be a 2D tensor of shape [M, K]")
+    _check(weight.dim() == 2, "weight must be a 2D tensor of shape [N, K]")
+    _check(output.dim() == 2, "output must be a 2D tensor of shape [M, N]")
+    epilogue = EpilogueOp(int(epilogue))
+    m, n = input.size(0), weight.size(0)
+    out_n = n // 2 if epilogue == EpilogueOp.SituQuant else n
+    _check(
+        output.size(0) == m and output.size(1) == out_n,
+        f"output shape must be [{m}, {out_n}], got [{output.size(0)}, {output.size(1)}]",
+    )
+    m_sf = (m + 127) // 128 * 128
+    fp8 = mode == "w8a8-mxfp8"
+    if fp8:
+        k = weight.size(1)
+        _check(input.size(1) == k, f"input K must match weight K, got input K={input.size(1)}, weight K={k}")
+        _check(sfb.dtype == torch.uint8,
+               "sfb must be the uint8 SfAtom weight scale that group_wise_quant returns")
+        sf_k = k // 32
+        _check(
+            sfa.is_contiguous() and sfa.numel() >= m_sf * sf_k,
+            f"sfa must hold whole 128-row SfAtoms: expected at least {m_sf * sf_k} elements "
+            f"({m_sf} x {sf_k}) for M={m}, got {sfa.numel()}",
+        )
+        if bias is not None and epilogue != EpilogueOp.SituQuant:
+            _check(
+                m % 256 == 0,
+                "the bias tile has no per-row store predicate yet, so M must be a multiple of 256 "
+                f"when bias is given, got {m}",
+            )
+    else:
+        k = weight.size(1) * 2
+        _check(
+            input.size(1) == weight.size(1),
+            f"packed input K/2 must match packed weight K/2, got input K/2={input.size(1)}, "
+            f"weight K/2={weight.size(1)}",
+        )
+        _check(bias is None, "W4A4 mode does not support bias yet.")
+        mxfp4 = mode == "w4a4-mxfp4"
+        _check(
+            not mxfp4 or alpha is None,
+            "'w4a4-mxfp4' does not take alpha; the global scaling factor is only used by 'w4a4-nvfp4'.",
+        )
+        sf_k = k // (32 if mxfp4 else 16)
+        _check(
+            sfa.size(-1) == sf_k and sfb.size(-1) == sf_k,
+            "W4A4 scale-factor shape does not match mode "
+            + ("'w4a4-mxfp4' (UE8M0 per 32)" if mxfp4 else "'w4a4-nvfp4' (UE4M3 per 16)")
+            + f" requires SF K = {sf_k}, got sfa K={sfa.size(-1)} and sfb K={sfb.size(-1)}.",
+        )
+        _check(
+            sfa.is_contiguous() and sfa.numel() >= m_sf * sf_k,
+            f"sfa must hold whole 128-row SfAtoms: expected at least {m_sf * sf_k} elements "
+            f"({m_sf} x {sf_k}) for M={m}, got {sfa.numel()}",
+        )
+        if not mxfp4:
+            _check(alpha is not None, "W4A4-nvfp4 mode requires alpha input (per-batch scaling).")
+    _check(
+        epilogue == EpilogueOp.Identity,
+        f"Unsupported epilogue {int(epilogue)} for {mode} (only EpilogueOp.Identity is built)",
+    )
+    _check(bias is None, "the bias epilogue is not built in this library")
+    _check(output.dtype == torch.bfloat16, "output must be a bfloat16 tensor")
+    _check(input.is_contiguous() and weight.is_contiguous() and sfb.is_contiguous(),
+           "input, weight and sfb must be contiguous")
+    _check(output.stride(1) == 1, "output rows must be contiguous")
+    if m > 0 and n > 0:
+        # shape legality ("No dense ... tile") is reported before anything touches a device
+        _native.call("hq_describe_tile", m, n, k, _native.MODE_IDS[mode], 148, -1)
+    alpha_ptr = None
+    if alpha is not None and not fp8:
+        _check(alpha.is_cuda and alpha.dtype == torch.float32 and alpha.numel() >= 1,
+               "alpha must be a float32 CUDA tensor with shape [1]")
+        alpha_ptr = alpha.data_ptr()
+    for name, t in (("input", input), ("weight", weight), ("sfa", sfa), ("sfb", sfb), ("output", output)):
+        _check(t.is_cuda, f"{name} must be a CUDA tensor (this library has no CPU path)")
+    dev = input.device.index
+    stream = torch.cuda.current_stream(input.device).cuda_stream
+    _native.call(
+        "hq_dense_gemm",
+        input.data_ptr(), weight.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), output.data_ptr(), alpha_ptr,
+        m, n, k, sfa.numel(), sfb.numel(), output.stride(0) if m > 0 else max(n, 8),
+        _native.MODE_IDS[mode], int(epilogue), int(sm_count), int(bool(use_pdl)), dev, stream,
+    )

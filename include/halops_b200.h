@@ -1,0 +1,134 @@
+/*
+ * C ABI of the B200-native block-scaled quantize -> dense GEMM path.
+ *
+ * Plain pointers and sizes only: every entry point takes device pointers that
+ * the caller owns, the CUDA device ordinal they live on and the stream to
+ * launch on, never synchronises, and returns 0 on success or a non-zero
+ * HQ_ERR_* code with a NUL-terminated message in `err` (when `err` is not
+ * NULL and `errlen` > 0).  The message texts follow the reference's
+ * TORCH_CHECK texts so that a binding can raise them unchanged.
+ *
+ * Each declaration cites the reference interface it replaces (paths relative
+ * to the reference project).
+ */
+#ifndef HALOPS_B200_H_
+#define HALOPS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Quantisation recipe; same order as the reference's QuantMode
+ * (csrc/kernel/gemm/group_wise_quant.cu:36-40). */
+enum {
+    HQ_MODE_W8A8_MXFP8 = 0, /* e4m3 values, UE8M0 scale per 32 */
+    HQ_MODE_W4A4_MXFP4 = 1, /* packed e2m1 values, UE8M0 scale per 32 */
+    HQ_MODE_W4A4_NVFP4 = 2  /* packed e2m1 values, UE4M3 scale per 16 */
+};
+
+/* Input element type of the quantizer. */
+enum { HQ_DTYPE_BF16 = 0, HQ_DTYPE_FP16 = 1 };
+
+/* Epilogue selector; values of the reference's EpilogueOp
+ * (csrc/kernel/gemm/epilogue_op.h:21-28).  Only Identity is implemented. */
+enum {
+    HQ_EPILOGUE_IDENTITY = 0,
+    HQ_EPILOGUE_QUANT = 1,
+    HQ_EPILOGUE_GATE_MUL_QUANT = 2,
+    HQ_EPILOGUE_SIGMOID = 3,
+    HQ_EPILOGUE_SITU_QUANT = 4,
+    HQ_EPILOGUE_SIGMOID_GATE_MUL_QUANT = 5
+};
+
+enum {
+    HQ_OK = 0,
+    HQ_ERR_INVALID = 1,     /* argument rejected; nothing was launched */
+    HQ_ERR_CUDA = 2,        /* a CUDA runtime / driver call failed */
+    HQ_ERR_UNSUPPORTED = 3, /* legal in the reference, not built here */
+    HQ_ERR_DEVICE = 4       /* a kernel gave up on a bounded wait (see hq_device_status) */
+};
+
+/* Maps "w8a8-mxfp8" / "w4a4-mxfp4" / "w4a4-nvfp4" to HQ_MODE_*, -1 otherwise.
+ * Replaces ParseQuantMode (csrc/kernel/gemm/group_wise_quant.cu:49-61) and the
+ * mode check of DenseGemm (csrc/kernel/gemm/dense_gemm.cu:33-36). */
+int hq_parse_mode(const char* mode);
+
+/* Group size (32 or 16) of a mode, 0 for an unknown mode.
+ * Replaces GroupSize (csrc/kernel/gemm/group_wise_quant.cu:44-46). */
+int hq_group_size(int mode);
+
+/* Rows of a swizzled scale tensor: m rounded up to whole 128-row SfAtoms.
+ * Replaces AlignSfM (csrc/kernel/gemm/gemm_utils.h:56-60). */
+int64_t hq_sf_rows(int64_t m);
+
+/*
+ * Group-wise quantisation of a row-major [m, k] bf16/fp16 matrix along k.
+ * Replaces halops::GroupWiseQuant (csrc/kernel/gemm/group_wise_quant.cu:297-375,
+ * bound at csrc/common/cpp_extensions.cc:300-303) minus the tensor allocation,
+ * which stays with the caller:
+ *   input   row-major, `ld_elems` elements between rows, rows 16-byte aligned
+ *   out_q   [m, k] e4m3 bytes (mxfp8) or [m, k/2] packed e2m1 (even index in
+ *           the low nibble), contiguous
+ *   out_sf  swizzle != 0: hq_sf_rows(m) * k/g bytes in SfAtom order (128 rows
+ *           x 4 K-blocks per 512-byte atom; padding rows written as zero);
+ *           swizzle == 0: [m, k/g] row-major bytes
+ * use_pdl != 0 launches with programmatic stream serialisation.
+ */
+int hq_group_wise_quant(const void* input, int64_t ld_elems, int in_dtype,
+                        int64_t m, int64_t k, int mode, int use_swizzle,
+                        int use_pdl, void* out_q, void* out_sf, int device,
+                        void* stream, char* err, size_t errlen);
+
+/*
+ * out[M, N] = bf16(alpha * (A . B^T)) with block-scaled operands.
+ * Replaces halops::DenseGemm (csrc/kernel/gemm/dense_gemm.cu:23-189, bound at
+ * csrc/common/cpp_extensions.cc:280-286) for EpilogueOp::Identity without bias:
+ *   a     [M, K] e4m3 or [M, K/2] packed e2m1, row-major contiguous
+ *   b     [N, K] / [N, K/2], same encoding
+ *   sfa   SfAtom-swizzled scales of A, at least hq_sf_rows(M) * K/g bytes
+ *   sfb   SfAtom-swizzled scales of B, at least hq_sf_rows(N) * K/g bytes
+ *   out   [M, N] bf16, `ldo` elements between rows (ldo % 8 == 0)
+ *   alpha device pointer to one float: required for nvfp4, must be NULL for
+ *         mxfp4, ignored for mxfp8 (csrc/kernel/gemm/dense_gemm.cu:126-164)
+ *   sm_count <= 0 uses every SM of the device
+ * Rows of A past M are never read into the result and rows of out past M are
+ * never written.
+ */
+int hq_dense_gemm(const void* a, const void* b, const void* sfa,
+                  const void* sfb, void* out, const float* alpha, int64_t m,
+                  int64_t n, int64_t k, int64_t sfa_bytes, int64_t sfb_bytes,
+                  int64_t ldo, int mode, int epilogue, int sm_count,
+                  int use_pdl, int device, void* stream, char* err,
+                  size_t errlen);
+
+/* Number of SMs of `device`, cached per device.
+ * Replaces GetSmCount (csrc/kernel/gemm/gemm_utils.h:29-37), whose cache is
+ * keyed by nothing and so returns the first device's count on every device. */
+int hq_sm_count(int device);
+
+/*
+ * Reads (and clears) the device-side status word of `device` after
+ * synchronising `stream`: 0 when no kernel of this library gave up on a
+ * bounded wait since the last call, else a code whose low byte names the
+ * role that timed out.  The reference's waits are unbounded
+ * (csrc/common/ptx.cuh:131-139); it has no counterpart of this call.
+ */
+int hq_device_status(int device, void* stream, uint32_t* status, char* err,
+                     size_t errlen);
+
+/* Human-readable description of the tile the GEMM dispatch picks for a shape
+ * (what the reference prints under IR_GEMM_TRACE,
+ * csrc/kernel/gemm/gemm_dispatch.cuh:389-416).  Returns 0 and fills `buf`, or
+ * HQ_ERR_INVALID with the reference's "No dense ... tile" message. */
+int hq_describe_tile(int64_t m, int64_t n, int64_t k, int mode, int sm_count,
+                     int device, char* buf, size_t buflen);
+
+const char* hq_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HALOPS_B200_H_ */

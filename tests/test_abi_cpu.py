@@ -1,0 +1,183 @@
+"""CPU-only checks of the drop-in boundary: the C-ABI library builds, loads and
+exports every symbol the header declares, and the host-side validation raises
+the reference's error texts before anything touches a device."""
+
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def native():
+    from halops_b200 import build
+
+    build.build()
+    from halops_b200 import _native
+
+    _native.lib()
+    return _native
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "halops_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hq_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(native):
+    names = _declared_functions()
+    assert "hq_group_wise_quant" in names and "hq_dense_gemm" in names
+    handle = ctypes.CDLL(native.lib_path())
+    for name in names:
+        assert getattr(handle, name) is not None
+    assert sorted(native.SIGNATURES) == names, "ctypes table and header disagree"
+    assert b"sm_100a" in native.lib().hq_version()
+
+
+def test_no_torch_types_in_the_header():
+    text = open(os.path.join(ROOT, "include", "halops_b200.h")).read()
+    assert "torch" not in text.replace("TORCH_CHECK", "") and "at::" not in text
+
+
+def test_mode_helpers(native):
+    lib = native.lib()
+    assert lib.hq_parse_mode(b"w8a8-mxfp8") == 0
+    assert lib.hq_parse_mode(b"w4a4-mxfp4") == 1
+    assert lib.hq_parse_mode(b"w4a4-nvfp4") == 2
+    assert lib.hq_parse_mode(b"nvfp4") == -1
+    assert [lib.hq_group_size(i) for i in range(4)] == [32, 32, 16, 0]
+    assert [lib.hq_sf_rows(m) for m in (0, 1, 128, 129, 1000)] == [0, 128, 128, 256, 1024]
+
+
+def _gemm_rc(native, m, n, k, mode, alpha=None, epilogue=0):
+    err = ctypes.create_string_buffer(512)
+    rc = native.lib().hq_dense_gemm(None, None, None, None, None, alpha, m, n, k, 1 << 40, 1 << 40, n,
+                                    mode, epilogue, -1, 0, 0, None, err, len(err))
+    return rc, err.value.decode()
+
+
+@pytest.mark.parametrize("mode, m, n, k, text", [
+    (0, 128, 256, 96, "No dense w8a8-mxfp8 tile for M=128 (grid M=128), N=256, K=96"),
+    (0, 128, 255, 128, "No dense w8a8-mxfp8 tile for M=128 (grid M=128), N=255, K=128"),
+    (2, 128, 256, 48, "No dense w4a4-nvfp4 tile for M=128 (grid M=128), N=256, K=48"),
+    (0, 200, 100, 128, "No dense w8a8-mxfp8 tile for M=256 (grid M=256), N=100, K=128"),
+])
+def test_shape_legality_messages(native, mode, m, n, k, text):
+    """Texts pinned by the reference's tests/test_dense_gemm.py:398-492."""
+    alpha = ctypes.cast(16, ctypes.c_void_p) if mode == 2 else None
+    rc, msg = _gemm_rc(native, m, n, k, mode, alpha)
+    assert rc == 1 and text in msg
+
+
+def test_gemm_argument_rules(native):
+    rc, msg = _gemm_rc(native, 128, 256, 512, 1, alpha=ctypes.cast(16, ctypes.c_void_p))
+    assert rc == 1 and "does not take alpha" in msg
+    rc, msg = _gemm_rc(native, 128, 256, 512, 2, alpha=None)
+    assert rc == 1 and "requires alpha" in msg
+    rc, msg = _gemm_rc(native, 128, 256, 512, 0, epilogue=3)
+    assert rc == 3 and "Unsupported epilogue" in msg
+    rc, msg = _gemm_rc(native, 128, 256, 512, 7)
+    assert rc == 1 and "Unsupported mode" in msg
+    assert _gemm_rc(native, 0, 256, 512, 0)[0] == 0  # empty problem: nothing to do
+
+
+def test_quant_argument_rules(native):
+    err = ctypes.create_string_buffer(512)
+    f = native.lib().hq_group_wise_quant
+    assert f(None, 96, 0, 128, 96, 0, 1, 0, None, None, 0, None, err, len(err)) == 1
+    assert b"scale kb_dim must be divisible by 4" in err.value
+    assert f(None, 100, 0, 128, 100, 0, 0, 0, None, None, 0, None, err, len(err)) == 1
+    assert b"k must be divisible by the quantization group size (32)" in err.value
+    assert f(None, 1024, 0, 128, 1024, 9, 1, 0, None, None, 0, None, err, len(err)) == 1
+    assert b"Unsupported quantization mode" in err.value
+    assert f(None, 1024, 5, 128, 1024, 0, 1, 0, None, None, 0, None, err, len(err)) == 1
+    assert b"bfloat16 or float16" in err.value
+    assert f(None, 1024, 0, 0, 1024, 0, 1, 0, None, None, 0, None, err, len(err)) == 0  # m = 0
+
+
+def test_python_wrapper_errors_without_a_device():
+    import halops_b200 as hq
+
+    x = torch.zeros([128, 1024], dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match=re.escape("Unsupported quantization mode")):
+        hq.group_wise_quant(x, mode="w4a4-fp6")
+    with pytest.raises(RuntimeError, match=re.escape("scale kb_dim must be divisible by 4")):
+        hq.group_wise_quant(torch.zeros([128, 96], dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        hq.group_wise_quant(x)
+
+    def empties(m, n, k, mode, x_shape=None, out_shape=None):
+        if mode == "w8a8-mxfp8":
+            a = torch.empty(x_shape or [m, k], dtype=torch.float8_e4m3fn)
+            w = torch.empty([n, k], dtype=torch.float8_e4m3fn)
+            sfa, sfb = torch.empty([m, k // 32], dtype=torch.uint8), torch.empty([n, k // 32], dtype=torch.uint8)
+            alpha = None
+        else:
+            a = torch.empty(x_shape or [m, k // 2], dtype=torch.uint8)
+            w = torch.empty([n, k // 2], dtype=torch.uint8)
+            g = 16 if mode == "w4a4-nvfp4" else 32
+            sfa, sfb = torch.empty([m, k // g], dtype=torch.uint8), torch.empty([n, k // g], dtype=torch.uint8)
+            alpha = torch.ones([1]) if mode == "w4a4-nvfp4" else None
+        return a, w, sfa, sfb, torch.empty(out_shape or [m, n], dtype=torch.bfloat16), alpha
+
+    cases = [
+        ("w8a8-mxfp8", 128, 256, 96, None, None, "No dense w8a8-mxfp8 tile for M=128 (grid M=128), N=256, K=96"),
+        ("w8a8-mxfp8", 128, 255, 128, None, None, "No dense w8a8-mxfp8 tile for M=128 (grid M=128), N=255, K=128"),
+        ("w4a4-nvfp4", 128, 256, 48, None, None, "No dense w4a4-nvfp4 tile for M=128 (grid M=128), N=256, K=48"),
+        ("w8a8-mxfp8", 128, 256, 128, [128, 1, 128], None, "input must be a 2D tensor"),
+        ("w8a8-mxfp8", 128, 256, 128, None, [128, 256, 1], "output must be a 2D tensor"),
+    ]
+    for mode, m, n, k, xs, os_, text in cases:
+        a, w, sfa, sfb, out, alpha = empties(m, n, k, mode, xs, os_)
+        with pytest.raises(RuntimeError, match=re.escape(text)):
+            hq.dense_gemm(a, w, sfa, sfb, out, None, alpha, -1, mode)
+
+    a, w, sfa, sfb, out, _ = empties(128, 256, 512, "w4a4-mxfp4")
+    with pytest.raises(RuntimeError, match=re.escape("does not take alpha")):
+        hq.dense_gemm(a, w, sfa, sfb, out, None, torch.ones([1]), -1, "w4a4-mxfp4")
+    a, w, _, _, out, _ = empties(128, 256, 512, "w4a4-mxfp4")
+    bad = torch.empty([128, 32], dtype=torch.uint8), torch.empty([256, 32], dtype=torch.uint8)
+    with pytest.raises(RuntimeError, match=re.escape("scale-factor shape does not match mode")):
+        hq.dense_gemm(a, w, bad[0], bad[1], out, None, None, -1, "w4a4-mxfp4")
+    a, w, sfa, sfb, out, _ = empties(200, 1024, 1024, "w8a8-mxfp8")
+    with pytest.raises(RuntimeError, match=re.escape("multiple of 256")):
+        hq.dense_gemm(a, w, torch.empty([256, 32], dtype=torch.uint8), sfb, out, torch.zeros([1024], dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="Unsupported mode"):
+        hq.dense_gemm(a, w, sfa, sfb, out, mode="nvfp4")
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        a, w, sfa, sfb, out, _ = empties(128, 256, 512, "w8a8-mxfp8")
+        hq.dense_gemm(a, w, sfa, sfb, out)
+
+
+def test_enum_and_interleave():
+    import halops_b200 as hq
+
+    assert [int(e) for e in hq.EpilogueOp] == [0, 1, 2, 3, 4, 5]
+    assert hq.EpilogueOp.SituQuant == 4
+    t = torch.arange(64).reshape(64, 1)
+    r = hq.interleave_gate_up(t).reshape(-1)
+    assert r[:16].tolist() == list(range(16)) and r[16:32].tolist() == list(range(32, 48))
+    assert r[32:48].tolist() == list(range(16, 32))
+
+
+def test_describe_tile(native):
+    import halops_b200 as hq
+
+    assert "128x256/128" in hq.describe_tile(8192, 8192, 8192, sm_count=148)
+    assert "128x64/128" in hq.describe_tile(8, 7168, 2048, sm_count=148)
+    with pytest.raises(RuntimeError, match="No dense"):
+        hq.describe_tile(128, 96, 128, sm_count=148)
+
+
+def test_product_never_imports_the_oracle():
+    """The library must not route through the CPU oracle."""
+    pkg = os.path.join(ROOT, "halops_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                assert "oracle" not in open(os.path.join(dirpath, f)).read(), f

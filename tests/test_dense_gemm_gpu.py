@@ -1,0 +1,263 @@
+"""GPU parity tests of ``dense_gemm`` against the CPU dequantise-then-matmul
+oracle.  Mirrors the reference's ``tests/test_dense_gemm.py`` (shapes, unaligned
+M, out-of-bounds sentinels, determinism, PDL, quantize -> GEMM chain) and adds
+the benchmark configurations.  Calls go through the Python wrapper and
+therefore the C ABI.
+
+Tolerances: the reference's ``rtol 2e-2 / atol 2e-3`` (MXFP8) and ``5e-2 / 5e-2``
+(FP4) element-wise, plus max|out - ref| / max|ref| <= 1e-2 against the fp32
+oracle."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+W8A8_TOL = dict(rtol=2e-2, atol=2e-3)
+W4A4_TOL = dict(rtol=5e-2, atol=5e-2)
+MAX_REL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def hq():
+    import halops_b200
+
+    return halops_b200
+
+
+def _rand(m, k, seed, kind="normal"):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn([m, k], generator=g)
+    if kind == "weight":
+        x = x * 0.02
+    elif kind == "student_t":
+        chi2 = torch.randn([3, m, k], generator=g).pow(2).sum(0)
+        x = x / torch.sqrt(chi2 / 3)
+    return x.to(torch.bfloat16)
+
+
+def _quantize(hq, a, b, mode):
+    aq, sfa = hq.group_wise_quant(a.cuda(), mode=mode)
+    bq, sfb = hq.group_wise_quant(b.cuda(), mode=mode)
+    return aq, bq, sfa, sfb
+
+
+def _gemm(hq, aq, bq, sfa, sfb, mode, alpha=None, use_pdl=False, sm_count=-1):
+    out = torch.zeros([aq.shape[0], bq.shape[0]], dtype=torch.bfloat16, device="cuda")
+    al = None
+    if mode == "w4a4-nvfp4":
+        al = torch.full([1], 1.0 if alpha is None else alpha, dtype=torch.float32, device="cuda")
+    hq.dense_gemm(aq, bq, sfa, sfb, out, None, al, sm_count, mode, use_pdl)
+    assert hq.device_status() == 0
+    return out
+
+
+def _check(out, aq, bq, sfa, sfb, mode, alpha=None, rows=None):
+    """Compare with the oracle; ``rows`` restricts the check to a row sample."""
+    a_sel = aq if rows is None else aq[rows]
+    a_deq = oracle.dequantize(aq, sfa, mode)
+    if rows is not None:
+        a_deq = a_deq[rows]
+    b_deq = oracle.dequantize(bq, sfb, mode)
+    ref = a_deq @ b_deq.T
+    if alpha is not None:
+        ref = ref * alpha
+    got = (out if rows is None else out[rows]).float().cpu()
+    tol = W8A8_TOL if mode == "w8a8-mxfp8" else W4A4_TOL
+    torch.testing.assert_close(got, ref.to(torch.bfloat16).float(), **tol)
+    rel = (got - ref).abs().max().item() / max(ref.abs().max().item(), 1e-30)
+    assert rel <= MAX_REL, f"max relative error {rel}"
+    del a_sel
+    return rel
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (128, 256, 256), (64, 128, 256), (128, 128, 128),
+                                   (256, 512, 1024), (64, 7168, 3584), (4096, 7168, 3584)],
+                         ids=lambda v: str(v))
+def test_mxfp8_shapes(hq, m, n, k):
+    """Reference shapes (tests/test_dense_gemm.py:186-212) plus config 1 (128x256x512)."""
+    a, b = _rand(m, k, 1), _rand(n, k, 2)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, "w8a8-mxfp8")
+    out = _gemm(hq, aq, bq, sfa, sfb, "w8a8-mxfp8")
+    _check(out, aq, bq, sfa, sfb, "w8a8-mxfp8")
+
+
+@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4", "w4a4-mxfp4"])
+def test_golden_fixture(hq, golden_dir, mode):
+    """Operands quantised by the reference's Python helpers (weights with
+    32x32 / 16x16 block scales), output produced by the reference's ref_gemm."""
+    d = np.load(os.path.join(golden_dir, f"gemm_{mode}.npz"))
+    x = torch.from_numpy(d["x"]).cuda()
+    w = torch.from_numpy(d["w"]).cuda()
+    if mode == "w8a8-mxfp8":
+        x, w = x.view(torch.float8_e4m3fn), w.view(torch.float8_e4m3fn)
+    sfa, sfb = torch.from_numpy(d["sfa"]).cuda(), torch.from_numpy(d["sfb"]).cuda()
+    out = _gemm(hq, x, w, sfa, sfb, mode)
+    ref = torch.from_numpy(d["out_bits"].view(np.int16)).view(torch.bfloat16).float()
+    tol = W8A8_TOL if mode == "w8a8-mxfp8" else W4A4_TOL
+    torch.testing.assert_close(out.float().cpu(), ref, **tol)
+
+
+@pytest.mark.parametrize("mode, m, n, k", [
+    ("w8a8-mxfp8", 129, 1024, 1024), ("w8a8-mxfp8", 200, 1024, 1024), ("w8a8-mxfp8", 300, 1024, 1024),
+    ("w8a8-mxfp8", 449, 1024, 1024), ("w8a8-mxfp8", 200, 8192, 4096), ("w8a8-mxfp8", 1000, 8192, 4096),
+    ("w8a8-mxfp8", 1, 1024, 1024), ("w8a8-mxfp8", 17, 192, 384),
+    ("w4a4-nvfp4", 129, 1024, 1024), ("w4a4-nvfp4", 200, 1024, 1024), ("w4a4-nvfp4", 300, 1024, 1024),
+    ("w4a4-mxfp4", 129, 1024, 1024), ("w4a4-mxfp4", 200, 1024, 1024), ("w4a4-mxfp4", 300, 1024, 1024)],
+    ids=lambda v: str(v))
+def test_unaligned_m(hq, mode, m, n, k):
+    """Neither the activation nor the output is padded to 128 rows."""
+    a, b = _rand(m, k, 3), _rand(n, k, 4)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, mode)
+    out = _gemm(hq, aq, bq, sfa, sfb, mode)
+    _check(out, aq, bq, sfa, sfb, mode, alpha=1.0 if mode == "w4a4-nvfp4" else None)
+
+
+@pytest.mark.parametrize("m", [1, 8, 32, 64, 128])
+@pytest.mark.parametrize("n,k", [(7168, 2048), (24576, 1536)])
+def test_decode_shapes(hq, m, n, k):
+    """Config 3: heavy-tailed Student-t activations, N(0, 0.02) weights."""
+    a, b = _rand(m, k, 5, "student_t"), _rand(n, k, 6, "weight")
+    aq, bq, sfa, sfb = _quantize(hq, a, b, "w8a8-mxfp8")
+    out = _gemm(hq, aq, bq, sfa, sfb, "w8a8-mxfp8")
+    _check(out, aq, bq, sfa, sfb, "w8a8-mxfp8")
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (256, 384, 768), (4096, 7168, 3584)], ids=lambda v: str(v))
+@pytest.mark.parametrize("mode", ["w4a4-nvfp4", "w4a4-mxfp4"])
+def test_fp4_shapes(hq, mode, m, n, k):
+    a, b = _rand(m, k, 7), _rand(n, k, 8)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, mode)
+    out = _gemm(hq, aq, bq, sfa, sfb, mode)
+    _check(out, aq, bq, sfa, sfb, mode, alpha=1.0 if mode == "w4a4-nvfp4" else None)
+
+
+def test_nvfp4_alpha_is_applied(hq):
+    a, b = _rand(256, 1024, 9), _rand(512, 1024, 10)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, "w4a4-nvfp4")
+    out = _gemm(hq, aq, bq, sfa, sfb, "w4a4-nvfp4", alpha=0.37)
+    _check(out, aq, bq, sfa, sfb, "w4a4-nvfp4", alpha=0.37)
+
+
+def test_config4_nvfp4_full_size(hq):
+    """Config 4: M=4096, N=14336, K=4096, checked on a 256-row sample."""
+    m, n, k = 4096, 14336, 4096
+    g = torch.Generator(device="cuda").manual_seed(4)
+    a = torch.randn([m, k], generator=g, device="cuda").to(torch.bfloat16)
+    b = torch.randn([n, k], generator=g, device="cuda").to(torch.bfloat16)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, "w4a4-nvfp4")
+    out = _gemm(hq, aq, bq, sfa, sfb, "w4a4-nvfp4")
+    _check(out, aq, bq, sfa, sfb, "w4a4-nvfp4", alpha=1.0, rows=torch.arange(0, m, 16))
+
+
+def test_config2_large_square_sample_and_linearity(hq):
+    """Config 2: M=N=K=8192, A ~ N(0,1), B ~ N(0,0.02).  A 256-row sample is
+    checked against the oracle; the whole output is checked through a
+    size-independent property: scaling one operand's block scales by 2 (adding 1
+    to every UE8M0 byte) doubles the output exactly."""
+    m = n = k = 8192
+    g = torch.Generator(device="cuda").manual_seed(2)
+    a = torch.randn([m, k], generator=g, device="cuda").to(torch.bfloat16)
+    b = (torch.randn([n, k], generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, "w8a8-mxfp8")
+    out = _gemm(hq, aq, bq, sfa, sfb, "w8a8-mxfp8")
+    _check(out, aq, bq, sfa, sfb, "w8a8-mxfp8", rows=torch.arange(0, m, 32))
+    out2 = _gemm(hq, aq, bq, sfa, sfb + 1, "w8a8-mxfp8")
+    assert torch.equal(out2.float(), out.float() * 2)
+
+
+@pytest.mark.parametrize("m,n,k", [(1344, 16384, 1024), (100, 7168, 512)])
+def test_no_out_of_bounds_write(hq, m, n, k):
+    """The output is a view of a larger sentinel-filled buffer; bytes past the
+    view stay untouched (reference tests/test_dense_gemm.py:308-329)."""
+    a, b = _rand(m, k, 11), _rand(n, k, 12)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, "w8a8-mxfp8")
+    guard, sentinel = 128, 0x5A
+    buf = torch.full([(m + guard) * n * 2], sentinel, dtype=torch.uint8, device="cuda")
+    out = buf[: m * n * 2].view(torch.bfloat16).view(m, n)
+    hq.dense_gemm(aq, bq, sfa, sfb, out, None, None, -1, "w8a8-mxfp8", True)
+    torch.cuda.synchronize()
+    assert (buf[m * n * 2:] == sentinel).all()
+    _check(out, aq, bq, sfa, sfb, "w8a8-mxfp8")
+
+
+def test_strided_output(hq):
+    m, n, k = 192, 256, 512
+    a, b = _rand(m, k, 13), _rand(n, k, 14)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, "w8a8-mxfp8")
+    wide = torch.full([m, 3 * n], 7.0, dtype=torch.bfloat16, device="cuda")
+    out = wide[:, n:2 * n]
+    hq.dense_gemm(aq, bq, sfa, sfb, out, None, None, -1, "w8a8-mxfp8")
+    torch.cuda.synchronize()
+    assert (wide[:, :n] == 7.0).all() and (wide[:, 2 * n:] == 7.0).all()
+    _check(out.contiguous(), aq, bq, sfa, sfb, "w8a8-mxfp8")
+
+
+@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4", "w4a4-mxfp4"])
+def test_determinism_pdl_and_sm_count(hq, mode):
+    """Bitwise identical across runs, with and without PDL, and for any SM count."""
+    a, b = _rand(1024, 2048, 15), _rand(2048, 2048, 16)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, mode)
+    base = _gemm(hq, aq, bq, sfa, sfb, mode)
+    assert torch.equal(base, _gemm(hq, aq, bq, sfa, sfb, mode))
+    assert torch.equal(base, _gemm(hq, aq, bq, sfa, sfb, mode, use_pdl=True))
+    assert torch.equal(base, _gemm(hq, aq, bq, sfa, sfb, mode, sm_count=37))
+    _check(base, aq, bq, sfa, sfb, mode, alpha=1.0 if mode == "w4a4-nvfp4" else None)
+
+
+@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-mxfp4", "w4a4-nvfp4"])
+def test_pdl_chain_after_group_wise_quant(hq, mode):
+    """quantize -> GEMM with PDL on both kernels and no synchronisation in
+    between equals the plain chain (reference tests/test_dense_gemm.py:679-706)."""
+    m, n, k = 512, 1024, 1024
+    a, b = _rand(m, k, 17).cuda(), _rand(n, k, 18).cuda()
+    alpha = torch.ones([1], dtype=torch.float32, device="cuda") if mode == "w4a4-nvfp4" else None
+    x, sfa = hq.group_wise_quant(a, mode=mode, use_pdl=False)
+    w, sfb = hq.group_wise_quant(b, mode=mode, use_pdl=False)
+    ref = torch.empty([m, n], dtype=torch.bfloat16, device="cuda")
+    hq.dense_gemm(x, w, sfa, sfb, ref, None, alpha, -1, mode, False)
+    for _ in range(8):
+        x, sfa = hq.group_wise_quant(a, mode=mode, use_pdl=True)
+        w, sfb = hq.group_wise_quant(b, mode=mode, use_pdl=True)
+        out = torch.empty([m, n], dtype=torch.bfloat16, device="cuda")
+        hq.dense_gemm(x, w, sfa, sfb, out, None, alpha, -1, mode, True)
+        assert torch.equal(out, ref)
+    assert hq.device_status() == 0
+
+
+def test_end_to_end_unaligned(hq):
+    """The user flow with no manual pad or slice (reference :591-611)."""
+    m, n, k = 300, 1024, 2048
+    a, b = _rand(m, k, 19), _rand(n, k, 20)
+    x, sfa = hq.group_wise_quant(a.cuda())
+    w, sfb = hq.group_wise_quant(b.cuda())
+    assert list(x.shape) == [m, k] and list(sfa.shape) == [384, k // 32]
+    out = torch.empty([m, n], dtype=torch.bfloat16, device="cuda")
+    hq.dense_gemm(x, w, sfa, sfb, out, None, None, -1, "w8a8-mxfp8")
+    _check(out, x, w, sfa, sfb, "w8a8-mxfp8")
+    # and close to the unquantised product
+    ref = a.float() @ b.float().T
+    rel = (out.float().cpu() - ref).norm() / ref.norm()
+    assert rel < 0.05
+
+
+def test_errors_on_device(hq):
+    dev = "cuda"
+    x = torch.empty([128, 128], dtype=torch.float8_e4m3fn, device=dev)
+    w = torch.empty([256, 128], dtype=torch.float8_e4m3fn, device=dev)
+    sfa = torch.empty([128, 4], dtype=torch.uint8, device=dev)
+    sfb = torch.empty([256, 4], dtype=torch.uint8, device=dev)
+    out = torch.empty([128, 256], dtype=torch.bfloat16, device=dev)
+    with pytest.raises(RuntimeError, match="sfa must hold whole 128-row SfAtoms"):
+        hq.dense_gemm(x, w, sfa[:64], sfb, out)
+    with pytest.raises(RuntimeError, match="sfb must hold whole 128-row SfAtoms"):
+        hq.dense_gemm(x, w, sfa, sfb[:128], out)
+    with pytest.raises(RuntimeError, match="Unsupported epilogue"):
+        hq.dense_gemm(x, w, sfa, sfb, out, epilogue=hq.EpilogueOp.Sigmoid)
+    with pytest.raises(RuntimeError, match="multiple of 256"):
+        hq.dense_gemm(x, w, sfa, sfb, out, torch.zeros([256], dtype=torch.bfloat16, device=dev))
