@@ -1,0 +1,357 @@
+"""Benchmark of the block-scaled quantize -> dense GEMM path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = group_wise_quant(A) + group_wise_quant(B) + dense_gemm, MXFP8, on
+the large square configuration M = N = K = 8192 (A ~ N(0,1), B ~ N(0,0.02),
+seeded synthetic data, which is also what the reference's own benchmark uses).
+With N > 1 ranks (torchrun, one per GPU) every rank owns one 8192-column shard
+of a weight that is N x 8192 columns wide (column-parallel, no data-path
+collective): weak scaling.  Prints ONE JSON line on rank 0.
+
+``--impl reference`` times the reference's CPU path of the same step (torch
+quantise + float32 dequantise-then-matmul, all host threads) on a bounded
+sample of the workload and extrapolates it to the whole step.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M = N_LOCAL = K = 8192
+MODE = "w8a8-mxfp8"
+NOMINAL_FP8_TFLOPS = 4500.0
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16": p["bf16_tflops"], "bf16_sustained": p["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken during the timed region."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        clocks, maxes, power, reasons = [], [], [], set()
+        for line in self.file.read().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                clocks.append(float(f[1]))
+                maxes.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        if clocks:
+            clocks.sort()
+            out.update(sm_mhz=clocks[len(clocks) // 2], sm_max_mhz=max(maxes), reasons=sorted(reasons),
+                       samples=len(clocks), power_w_max=max(power))
+        return out
+
+
+def _dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# ----------------------------------------------------------------------------- CPU arm
+
+
+def cpu_reference_step(sample_m: int, sample_n: int, threads: int):
+    """One bounded sample of the step on the host: quantise an [sample_m, K]
+    block of A and an [sample_n, K] block of B, dequantise both and multiply
+    them in float32.  Returns the measured times of the three parts."""
+    from oracle.cpu_path import dequant_mxfp8_torch, quant_mxfp8_torch
+
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(2027)
+    a = torch.randn([sample_m, K], generator=g).to(torch.bfloat16)
+    b = (torch.randn([sample_n, K], generator=g) * 0.02).to(torch.bfloat16)
+    t0 = time.perf_counter()
+    aq, sfa = quant_mxfp8_torch(a)
+    bq, sfb = quant_mxfp8_torch(b)
+    t1 = time.perf_counter()
+    ad, bd = dequant_mxfp8_torch(aq, sfa), dequant_mxfp8_torch(bq, sfb)
+    t2 = time.perf_counter()
+    out = torch.matmul(ad, bd.T).to(torch.bfloat16)
+    t3 = time.perf_counter()
+    return t1 - t0, t2 - t1, t3 - t2, float(out[0, 0])
+
+
+def cpu_baseline(steps: int, warmup: int, sample_m: int = 512, sample_n: int = 2048):
+    """Times the sample `steps` times and extrapolates to the whole step:
+    quantise and dequantise scale with the elements, the matmul with the flops."""
+    threads = os.cpu_count() or 1
+    for _ in range(warmup):
+        cpu_reference_step(sample_m, sample_n, threads)
+    tq = td = tm = 0.0
+    t_begin = time.perf_counter()
+    for _ in range(steps):
+        q, d, mm, _ = cpu_reference_step(sample_m, sample_n, threads)
+        tq += q
+        td += d
+        tm += mm
+    wall = time.perf_counter() - t_begin
+    elem_ratio = (M + N_LOCAL) * K / ((sample_m + sample_n) * K)
+    flop_ratio = (2.0 * M * N_LOCAL * K) / (2.0 * sample_m * sample_n * K)
+    full = (tq + td) / steps * elem_ratio + tm / steps * flop_ratio
+    tflops = 2.0 * M * N_LOCAL * K / full / 1e12
+    sample = (f"{sample_m}x{K} block of A and {sample_n}x{K} block of B quantised (torch, MXFP8), "
+              f"dequantised and multiplied in float32; quantise and dequantise times scaled by elements "
+              f"and the matmul time by flops to the full {M}x{N_LOCAL}x{K} step")
+    return {"value": tflops, "unit": "TFLOPS", "cores": threads, "kind": "port", "sample": sample,
+            "ms_per_sample_step": 1e3 * wall / steps}
+
+
+def run_reference(args):
+    rank, world, _ = _dist_env()
+    if rank != 0:
+        return
+    base = cpu_baseline(max(args.steps, 1), args.warmup)
+    line = {
+        "impl": "reference", "metric": "mxfp8_dense_gemm_tflops_quant_incl", "value": base["value"],
+        "unit": "TFLOPS", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": base["ms_per_sample_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"C2 MXFP8 dense GEMM M=N=K={M}, quant(A)+quant(B)+GEMM per step",
+                   "arm": "reference CPU path (torch quantise + float32 dequantise-then-matmul), rank 0 only"},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+
+def run_ours(args):
+    import halops_b200 as hq
+
+    rank, world, local = _dist_env()
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    peaks = _peaks()
+    g = torch.Generator(device=dev).manual_seed(2026 + 1)
+    a = torch.randn([M, K], generator=g, device=dev).to(torch.bfloat16)
+    # rank r owns columns [r * N_LOCAL, (r + 1) * N_LOCAL) of the global weight
+    gw = torch.Generator(device=dev).manual_seed(4052 + rank)
+    b = (torch.randn([N_LOCAL, K], generator=gw, device=dev) * 0.02).to(torch.bfloat16)
+    out = torch.empty([M, N_LOCAL], dtype=torch.bfloat16, device=dev)
+    aq = torch.empty([M, K], dtype=torch.float8_e4m3fn, device=dev)
+    bq = torch.empty([N_LOCAL, K], dtype=torch.float8_e4m3fn, device=dev)
+    sfa = torch.empty([M, K // 32], dtype=torch.uint8, device=dev)
+    sfb = torch.empty([N_LOCAL, K // 32], dtype=torch.uint8, device=dev)
+
+    def step():
+        hq.group_wise_quant(a, MODE, True, True, aq, sfa)
+        hq.group_wise_quant(b, MODE, True, True, bq, sfb)
+        hq.dense_gemm(aq, bq, sfa, sfb, out, None, None, -1, MODE, True)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    assert hq.device_status(dev) == 0
+
+    # ---- timed region: K steps, device time by CUDA events on the launching stream
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    steps = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for i in range(steps):
+        ev[i][0].record()
+        hq.group_wise_quant(a, MODE, True, True, aq, sfa)
+        hq.group_wise_quant(b, MODE, True, True, bq, sfb)
+        ev[i][1].record()
+        hq.dense_gemm(aq, bq, sfa, sfb, out, None, None, -1, MODE, True)
+        ev[i][2].record()
+    stop.record()
+    barrier()
+    total_ms = start.elapsed_time(stop)
+    quant_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / steps
+    gemm_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / steps
+    clocks = sampler.stop() if rank == 0 else None
+    assert hq.device_status(dev) == 0
+
+    # ---- GEMM alone and quantizer alone (explains the headline; same buffers, > L2 working set)
+    def timed(fn, reps):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fn()
+        torch.cuda.synchronize()
+        s.record()
+        for _ in range(reps):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / reps
+
+    gemm_only_ms = timed(lambda: hq.dense_gemm(aq, bq, sfa, sfb, out, None, None, -1, MODE, False), max(steps, 5))
+    quant_only_ms = timed(lambda: hq.group_wise_quant(a, MODE, True, False, aq, sfa), max(steps, 5))
+
+    # ---- end to end through the public API with host buffers
+    a_host = a.cpu().pin_memory()
+    b_host = b.cpu().pin_memory()
+    out_host = torch.empty([M, N_LOCAL], dtype=torch.bfloat16).pin_memory()
+    a_dev, b_dev = torch.empty_like(a), torch.empty_like(b)
+
+    def e2e_step():
+        a_dev.copy_(a_host, non_blocking=True)
+        b_dev.copy_(b_host, non_blocking=True)
+        xq, xs = hq.group_wise_quant(a_dev, MODE, True, True, aq, sfa)
+        wq, ws = hq.group_wise_quant(b_dev, MODE, True, True, bq, sfb)
+        hq.dense_gemm(xq, wq, xs, ws, out, None, None, -1, MODE, True)
+        out_host.copy_(out, non_blocking=True)
+
+    e2e_steps = max(3, min(steps, 10))
+    e2e_step()
+    barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e.record()
+    barrier()
+    e2e_ms = s.elapsed_time(e) / e2e_steps
+
+    # ---- max over ranks
+    times = torch.tensor([total_ms, gemm_ms, quant_ms, gemm_only_ms, quant_only_ms, e2e_ms], device=dev,
+                         dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, gemm_ms, quant_ms, gemm_only_ms, quant_only_ms, e2e_ms = times.tolist()
+
+    flops_rank = 2.0 * M * N_LOCAL * K
+    ms_per_step = total_ms / steps
+    value = world * flops_rank / (ms_per_step * 1e-3) / 1e12
+    gemm_tflops = flops_rank / (gemm_ms * 1e-3) / 1e12
+    timed_seconds = total_ms * 1e-3
+    fp8_peak = 2.0 * (peaks["bf16"] if timed_seconds < 1.0 else peaks["bf16_sustained"])
+    quant_bytes = M * K * (2 + 1 + 1 / 32)
+
+    if rank == 0:
+        base = cpu_baseline(steps=2, warmup=1) if world == 1 and not args.no_cpu_baseline else None
+        line = {
+            "metric": "mxfp8_dense_gemm_tflops_quant_incl", "value": value, "unit": "TFLOPS", "n_gpus": world,
+            "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32 accumulate -> bf16",
+            "data": "synthetic",
+            "config": {
+                "workload": f"C2 MXFP8 dense GEMM M=N=K={M} per GPU: group_wise_quant(A) + group_wise_quant(B) + "
+                            "dense_gemm per step; N>1: column-parallel, one 8192-column weight shard per rank",
+                "cache": "inputs larger than L2 (A and B bf16 128 MiB each, e4m3 64 MiB each, output 128 MiB)",
+                "tile": hq.describe_tile(M, N_LOCAL, K, MODE, device=local),
+            },
+            "gemm_only": {"tflops_in_step": gemm_tflops, "ms_in_step": gemm_ms,
+                          "tflops_alone": flops_rank / (gemm_only_ms * 1e-3) / 1e12, "ms_alone": gemm_only_ms,
+                          "frac_of_nominal_fp8": gemm_tflops / NOMINAL_FP8_TFLOPS},
+            "quant": {"ms_both_in_step": quant_ms, "ms_one_operand_alone": quant_only_ms,
+                      "gbs_alone": quant_bytes / (quant_only_ms * 1e-3) / 1e9,
+                      "frac_of_hbm": quant_bytes / (quant_only_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                      "bytes_per_element": 3.03125},
+            "roofline": {"kernel": "gemm_kernel<256, mxfp8>", "bound": "tensor", "achieved": gemm_tflops,
+                         "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak, "traffic": None,
+                         "peak_source": f"2 x {peaks['source']} cuBLAS bf16 "
+                                        f"({'burst' if timed_seconds < 1.0 else 'sustained'}) as the dense fp8 peak"},
+            "e2e": {"value": world * flops_rank / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
+                    "h2d_bytes_per_step": 2 * M * K * 2, "d2h_bytes_per_step": M * N_LOCAL * 2,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": 3 * steps,
+            "clocks": clocks,
+        }
+        if base is not None:
+            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -119,3 +119,22 @@ def test_quant_edge_cases():
     x = torch.tensor([[float("nan")] + [1.0] * 31, [float("inf")] + [2.0] * 31], dtype=torch.bfloat16)
     q, sf = oracle.quant_group_wise(x, "w8a8-mxfp8", use_swizzle=False)
     assert q[0, 0] == 0xFE and q[1, 0] == 0xFE and sf[1, 0] == 254 and q[1, 1] == 0
+
+
+def test_torch_cpu_path_equals_numpy_oracle(golden_dir):
+    """The multi-threaded torch port timed by the benchmark produces the same
+    bytes as the numpy oracle (and so as the reference model)."""
+    from oracle.cpu_path import gemm_mxfp8_torch, quant_mxfp8_torch
+
+    d = np.load(os.path.join(golden_dir, "quant_w8a8-mxfp8.npz"))
+    x = _bf16(d["x_bits"])
+    q, sf = quant_mxfp8_torch(x)
+    assert np.array_equal(q.view(torch.uint8).numpy(), d["q"])
+    assert np.array_equal(sf.numpy(), d["sf_logical"])
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn([64, 256], generator=g).to(torch.bfloat16)
+    b = torch.randn([96, 256], generator=g).to(torch.bfloat16)
+    aq, sfa = quant_mxfp8_torch(a)
+    bq, sfb = quant_mxfp8_torch(b)
+    want = oracle.dense_gemm_ref(aq, bq, sfa.numpy(), sfb.numpy(), "w8a8-mxfp8", swizzled=False)
+    assert torch.equal(gemm_mxfp8_torch(aq, sfa, bq, sfb), want)
