@@ -62,7 +62,7 @@ class ClockSampler:
             self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+                 "-lms", "20"], stdout=self.file, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
@@ -258,6 +258,14 @@ def run_ours(args):
         torch.cuda.synchronize()
         return s.elapsed_time(e) / reps
 
+    if args.kernels_only:
+        # profiling aid: only the timed steps above run (keeps a profiler's launch list short)
+        if rank == 0:
+            print(json.dumps({"kernels_only": True, "ms_per_step": total_ms / steps, "gemm_ms": gemm_ms,
+                              "quant_ms": quant_ms}), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
     gemm_only_ms = timed(lambda: hq.dense_gemm(aq, bq, sfa, sfb, out, None, None, -1, MODE, False), max(steps, 5))
     quant_only_ms = timed(lambda: hq.group_wise_quant(a, MODE, True, False, aq, sfa), max(steps, 5))
 
@@ -342,10 +350,12 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="run only warm-up and the timed steps (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

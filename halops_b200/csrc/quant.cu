@@ -84,6 +84,7 @@ __device__ __forceinline__ void unpack8<__half>(const uint4& v, float (&f)[8]) {
 template <uint32_t kMant, int kShift>
 __device__ __forceinline__ uint32_t ue8m0_of_amax(float amax) {
     const uint32_t u = __float_as_uint(amax);
+    if (u >= 0x7f800000u) return 254u;  // an infinite amax saturates (fmaxf never returns NaN here)
     int e = int((u + (0x00800000u - kMant)) >> 23) - kShift;
     const bool exact_ge_one =
         (u & 0x007fffffu) == kMant && (u >> 23) >= uint32_t(127 + kShift);

@@ -1,0 +1,124 @@
+"""Column-parallel (N-sharded) dense GEMM over the GPUs of one box.
+
+The reference has no multi-GPU dense GEMM; this is the sharded mode of the
+benchmark's largest configuration (M=16384, N=57344, K=8192 over 1/2/4/8 GPUs).
+Output columns are independent, so rank r owns weight rows
+``[r * N/w, (r + 1) * N/w)`` and computes ``out[:, r * N/w : (r + 1) * N/w]``
+with no data-path collective.  ``N/w`` must be a multiple of 128 so that every
+shard starts on an SfAtom boundary: the atoms of the swizzled scale tensor are
+ordered by 128-row tile first, so a shard's scales are one contiguous byte
+range of the global ``sfb`` (no re-swizzle).  An optional all-gather over NCCL
+assembles the full ``[M, N]`` output on every rank.
+
+One process per GPU (``torch.distributed``); the kernels run on each rank's
+current stream.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+
+from . import _native
+from .gemm import dense_gemm, group_wise_quant
+
+__all__ = ["shard_bounds", "shard_quantized_weight", "ColumnParallelDenseGemm"]
+
+
+def shard_bounds(n: int, world: int, rank: int) -> Tuple[int, int]:
+    """(first weight row, number of rows) of ``rank``'s shard."""
+    if world < 1 or not 0 <= rank < world:
+        raise RuntimeError(f"invalid rank {rank} for world size {world}")
+    if n % world != 0 or (n // world) % 128 != 0:
+        raise RuntimeError(
+            f"N={n} cannot be sharded over {world} ranks: every shard must be a multiple of 128 "
+            "rows so that it starts on a scale-atom boundary")
+    rows = n // world
+    return rank * rows, rows
+
+
+def shard_quantized_weight(wq: torch.Tensor, sfb: torch.Tensor, mode: str, world: int, rank: int):
+    """Views of ``rank``'s rows of a quantised weight ``[N, K or K/2]`` and of
+    the matching contiguous byte range of its swizzled scales."""
+    n = wq.size(0)
+    start, rows = shard_bounds(n, world, rank)
+    k = wq.size(1) * (1 if mode == "w8a8-mxfp8" else 2)
+    kb_dim = k // _native.GROUP_SIZE[mode]
+    flat = sfb.reshape(-1)
+    sf = flat[start * kb_dim:(start + rows) * kb_dim].view(rows, kb_dim)
+    return wq[start:start + rows], sf
+
+
+class ColumnParallelDenseGemm:
+    """``y = x @ W^T`` with ``W`` sharded by rows (output columns) over a process group.
+
+    Args:
+        weight: this rank's ``[N/w, K]`` bf16/fp16 weight shard (quantised here once),
+            or a tuple ``(wq, sfb)`` of an already quantised shard.
+        mode: quantisation recipe of both operands.
+        group: process group (default: the world group); ``None`` world of 1 needs no
+            initialised process group.
+        gemm_fn / quant_fn: the kernels to call (defaults: this package's); tests of the
+            host-side logic on CPU ranks inject stand-ins.
+    """
+
+    def __init__(self, weight, mode: str = "w8a8-mxfp8", group=None,
+                 gemm_fn: Optional[Callable] = None, quant_fn: Optional[Callable] = None):
+        import torch.distributed as dist
+
+        self.mode = mode
+        self._dist = dist if dist.is_available() and dist.is_initialized() else None
+        self.group = group
+        self.world = self._dist.get_world_size(group) if self._dist else 1
+        self.rank = self._dist.get_rank(group) if self._dist else 0
+        self._gemm = gemm_fn or dense_gemm
+        self._quant = quant_fn or group_wise_quant
+        if isinstance(weight, tuple):
+            self.wq, self.sfb = weight
+        else:
+            self.wq, self.sfb = self._quant(weight, mode=mode)
+        self.n_local = self.wq.size(0)
+        if self.n_local % 128 != 0:
+            raise RuntimeError("a weight shard must have a multiple of 128 rows")
+        self.alpha = None
+        self._staging = None
+
+    def set_alpha(self, alpha: torch.Tensor) -> None:
+        """Per-tensor float32 ``[1]`` factor of the NVFP4 recipe."""
+        self.alpha = alpha
+
+    def local(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """This rank's ``[M, N/w]`` column block from bf16/fp16 activations."""
+        xq, sfa = self._quant(x, mode=self.mode)
+        return self.local_quantized(xq, sfa, out)
+
+    def local_quantized(self, xq, sfa, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        m = xq.size(0)
+        if out is None:
+            out = torch.empty([m, self.n_local], dtype=torch.bfloat16, device=xq.device)
+        self._gemm(xq, self.wq, sfa, self.sfb, out, None, self.alpha, -1, self.mode)
+        return out
+
+    def gather(self, out_local: torch.Tensor) -> torch.Tensor:
+        """All-gather of the column blocks: returns ``[world, M, N/w]`` (block r is
+        rank r's columns) without a re-tiling pass; ``as_matrix`` gives ``[M, N]``."""
+        if self.world == 1:
+            return out_local.unsqueeze(0)
+        m = out_local.size(0)
+        shape = [self.world, m, self.n_local]
+        if self._staging is None or list(self._staging.shape) != shape or self._staging.device != out_local.device:
+            self._staging = torch.empty(shape, dtype=out_local.dtype, device=out_local.device)
+        self._dist.all_gather_into_tensor(self._staging.view(self.world * m, self.n_local),
+                                          out_local.contiguous(), group=self.group)
+        return self._staging
+
+    @staticmethod
+    def as_matrix(gathered: torch.Tensor) -> torch.Tensor:
+        """``[world, M, N/w]`` -> ``[M, N]`` (one copy)."""
+        w, m, nl = gathered.shape
+        return gathered.permute(1, 0, 2).reshape(m, w * nl)
+
+    def __call__(self, x: torch.Tensor, gather: bool = False) -> torch.Tensor:
+        out = self.local(x)
+        return self.as_matrix(self.gather(out)) if gather else out
