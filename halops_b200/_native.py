@@ -7,7 +7,8 @@ import ctypes
 import os
 import threading
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libhalops_b200.so")
+_LIB_PATH = os.environ.get("HALOPS_B200_LIB") or os.path.join(
+    os.path.dirname(os.path.abspath(__file__)), "lib", "libhalops_b200.so")
 _lock = threading.Lock()
 _lib = None
 

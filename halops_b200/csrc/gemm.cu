@@ -39,6 +39,19 @@ constexpr int kSmemBudget = 232448;               // 227 KiB opt-in maximum per 
 // device status word: non-zero when a kernel gave up on a bounded wait
 __device__ uint32_t g_status[4];
 
+#ifdef HQ_TRACE
+// development aid: %globaltimer stamps of the first k-iterations of cluster 0
+__device__ unsigned long long g_trace[3 * 512 * 2];
+#define HQ_STAMP(role, it, slot)                                                      \
+    do {                                                                              \
+        if (cluster_id == 0 && (it) < 512u) g_trace[((role)*512 + (it)) * 2 + (slot)] = ptx::globaltimer_ns(); \
+    } while (0)
+#else
+#define HQ_STAMP(role, it, slot) \
+    do {                         \
+    } while (0)
+#endif
+
 enum : uint32_t {
     kStatusProducer = 0x01,
     kStatusMma = 0x02,
@@ -386,6 +399,323 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     }
 }
 
+// ---------------------------------------------------------------------------- 2-CTA tiles
+//
+// Pair kernel: a cluster of two CTAs computes one 256 x BN tile with
+// tcgen05.mma.cta_group::2 (M = 256).  CTA r of the pair owns rows
+// [128 r, 128 r + 128) of the A tile, rows [r BN/2, (r + 1) BN/2) of the B tile and the
+// matching half of the accumulator; both CTAs hold the scales of all BN columns.
+// Every CTA loads its own halves with plain (non-broadcast) TMA copies in the
+// cta_group::2 form, which lets the bytes be counted on the leader's (rank 0)
+// barrier; only the leader issues tcgen05.cp / tcgen05.mma, and it releases a stage
+// or publishes an accumulator with one tcgen05.commit per CTA.  The epilogue warps of
+// both CTAs report to the leader's barriers.  Per CTA this halves the B traffic from
+// L2 and leaves room for 6 stages instead of 4.
+
+template <int BN, int KIND>
+struct Cfg2 {
+    static_assert(BN == 128 || BN == 256, "pair tile widths built");
+    static constexpr int kABytes = kBM * kBKBytes;
+    static constexpr int kBBytes = (BN / 2) * kBKBytes;
+    static constexpr int kSfKAtoms = KIND == 0 ? 1 : (KIND == 1 ? 4 : 2);
+    static constexpr int kNAtoms = BN / 128;
+    static constexpr int kSfaBytes = kSfKAtoms * 512;
+    static constexpr int kSfbBytes = kNAtoms * kSfaBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+    static constexpr int kEpiBufs = 2;
+    static constexpr int kEpiBytes = kEpiWarps * kEpiBufs * kEpiBufBytes;
+    static constexpr int kBarBytes = 1024;
+    static constexpr int kStagesFit = (kSmemBudget - kEpiBytes - kBarBytes - 1024) / kStageBytes;
+    static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarBytes + 1024;
+    // Scale columns of one k-iteration and how many such sets rotate in tensor
+    // memory.  With two sets the tcgen05.cp for iteration i + 1 is issued ahead of
+    // the MMAs of iteration i, so that a late stage shows up one iteration before
+    // its MMAs are due.  (Measured: the copies cost the tensor pipe about 30 ns
+    // each whether or not they depend on their neighbours.)
+    static constexpr int kSfCols = kSfKAtoms * 4 * (1 + kNAtoms);
+    static constexpr int kSfSets = KIND == 0 ? 2 : 1;
+    static constexpr int kSfRegion = kSfCols * kSfSets;
+    static constexpr int kOverlap = BN == 256 ? (kSfRegion + 15) / 16 * 16 : 0;
+    static constexpr int kAccStride = BN - kOverlap;
+    static constexpr int kSfCol0 = kAccStride + BN;
+    static constexpr int kColsUsed = kSfCol0 + kSfRegion;
+    static constexpr int kTmemCols = kColsUsed <= 256 ? 256 : 512;
+    static_assert(kColsUsed <= 512, "tensor memory budget");
+    static constexpr int kChunks = BN / kEpiChunk;
+    static constexpr int kOverlapChunks = (kOverlap + kEpiChunk - 1) / kEpiChunk;
+    static_assert(kStages >= 2, "pipeline depth");
+};
+
+template <int BN, int KIND>
+__device__ __forceinline__ uint32_t instr_desc_pair(uint32_t sf_id) {
+    constexpr uint32_t fmt = KIND == 0 ? 0u : 1u;
+    constexpr uint32_t scale_fmt = KIND == 1 ? 0u : 1u;
+    return (sf_id << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(BN >> 3) << 17) | (scale_fmt << 23) |
+           (uint32_t(256 >> 4) << 24) | (sf_id << 29);
+}
+
+template <int BN, int KIND>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ CUtensorMap tm_d, const __grid_constant__ CUtensorMap tm_sfa,
+                 const __grid_constant__ CUtensorMap tm_sfb, const float* __restrict__ alpha, int k_tiles,
+                 int kq_dim, int tiles_m, int tiles_n) {
+    using C = Cfg2<BN, KIND>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* const smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+    const uint32_t a_base = smem_base;
+    const uint32_t b_base = a_base + C::kStages * C::kABytes;
+    const uint32_t sfa_base = b_base + C::kStages * C::kBBytes;
+    const uint32_t sfb_base = sfa_base + C::kStages * C::kSfaBytes;
+    const uint32_t epi_base = sfb_base + C::kStages * C::kSfbBytes;
+    const uint32_t bar_off = C::kStages * C::kStageBytes + C::kEpiBytes;
+    Barriers* const bars = reinterpret_cast<Barriers*>(smem + bar_off);
+    volatile uint32_t* const abort = &bars->abort;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = ptx::cluster_ctarank();  // 0 = leader
+    const bool leader = rank == 0;
+    const int cluster_id = blockIdx.x >> 1;
+    const int num_clusters = gridDim.x >> 1;
+    const int num_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            // the leader's copy collects the bytes of both CTAs after one
+            // expect_tx arrival of the leader's producer
+            ptx::mbar_init(ptx::smem_u32(&bars->full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);  // one tcgen05.commit
+        }
+        for (int s = 0; s < 2; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&bars->acc_full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[s]), 2 * kEpiWarps);  // leader's copy is used
+            ptx::mbar_init(ptx::smem_u32(&bars->overlap_free[s]), 2 * kEpiWarps);
+        }
+        bars->abort = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tmap(&tm_a);
+        ptx::prefetch_tmap(&tm_b);
+        ptx::prefetch_tmap(&tm_d);
+        ptx::prefetch_tmap(&tm_sfa);
+        ptx::prefetch_tmap(&tm_sfb);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<2>(ptx::smem_u32(&bars->tmem_base), C::kTmemCols);
+        ptx::tmem_relinquish<2>();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    // barriers of both CTAs are initialised before anyone signals across the pair
+    ptx::cluster_sync();
+    ptx::tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+
+    ptx::pdl_wait();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+                const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+                const int m0 = tc.m * 256 + int(rank) * kBM;
+                const int n0 = tc.n * BN;
+                const int sfa_atom_row = (tc.m * 2 + int(rank)) * kq_dim;
+                const int sfb_atom_row = (n0 / 128) * kq_dim;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1u;
+                    HQ_STAMP(rank, it, 0);
+                    ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ph ^ 1u, abort, kStatusProducer);
+                    if (!ok) break;
+                    HQ_STAMP(rank, it, 1);
+                    // Bytes of both CTAs are counted on the leader's barrier; only the
+                    // leader registers them (the count may go negative in between).
+                    const uint32_t full = ptx::mapa_cluster(ptx::smem_u32(&bars->full[s]), 0);
+                    if (leader) ptx::mbar_arrive_expect_tx(ptx::smem_u32(&bars->full[s]), 2 * C::kStageBytes);
+                    ptx::tma_load_2d_pair(a_base + s * C::kABytes, &tm_a, kt * kBKBytes, m0, full);
+                    ptx::tma_load_2d_pair(b_base + s * C::kBBytes, &tm_b, kt * kBKBytes,
+                                          n0 + int(rank) * (BN / 2), full);
+                    // scale atoms are rows of 128 32-bit words
+                    ptx::tma_load_2d_pair(sfa_base + s * C::kSfaBytes, &tm_sfa, 0,
+                                          sfa_atom_row + kt * C::kSfKAtoms, full);
+#pragma unroll
+                    for (int j = 0; j < C::kNAtoms; ++j) {
+                        ptx::tma_load_2d_pair(sfb_base + s * C::kSfbBytes + j * C::kSfaBytes, &tm_sfb, 0,
+                                              sfb_atom_row + j * kq_dim + kt * C::kSfKAtoms, full);
+                    }
+                }
+            }
+            ptx::pdl_launch_dependents();
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader only)
+        if (leader && lane == 0) {
+            const int my_tiles = cluster_id < num_tiles ? (num_tiles - cluster_id + num_clusters - 1) / num_clusters : 0;
+            const uint32_t total_its = uint32_t(my_tiles) * uint32_t(k_tiles);
+            // scales of k-iteration `j` (stage j % kStages) -> tensor-memory set j % kSfSets
+            auto copy_scales = [&](uint32_t j) -> bool {
+                const uint32_t s = j % C::kStages;
+                if (!wait_bar(ptx::smem_u32(&bars->full[s]), (j / C::kStages) & 1u, abort, kStatusMma)) return false;
+                ptx::tc_fence_after();
+                const uint32_t set = tmem + C::kSfCol0 + (j % C::kSfSets) * C::kSfCols;
+#pragma unroll
+                for (int a = 0; a < C::kSfKAtoms; ++a) {
+                    ptx::tc_copy_sf<2>(set + a * 4,
+                                       ptx::smem_desc(sfa_base + s * C::kSfaBytes + a * 512, 0, 128, 0));
+#pragma unroll
+                    for (int j2 = 0; j2 < C::kNAtoms; ++j2) {
+                        ptx::tc_copy_sf<2>(
+                            set + C::kSfKAtoms * 4 + (a * C::kNAtoms + j2) * 4,
+                            ptx::smem_desc(sfb_base + s * C::kSfbBytes + (j2 * C::kSfKAtoms + a) * 512, 0, 128, 0));
+                    }
+                }
+                return true;
+            };
+            uint32_t it = 0;
+            uint32_t t = 0;
+            bool ok = total_its == 0 || copy_scales(0);
+            for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++t) {
+                const uint32_t as = t & 1u;
+                const uint32_t aph = (t >> 1) & 1u;
+                ok = wait_bar(ptx::smem_u32(&bars->acc_empty[as]), aph ^ 1u, abort, kStatusMma);
+                if (!ok) break;
+                if (C::kOverlap != 0 && t > 0) {
+                    ok = wait_bar(ptx::smem_u32(&bars->overlap_free[as ^ 1u]), ((t - 1) >> 1) & 1u, abort,
+                                  kStatusMma);
+                    if (!ok) break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t acc = tmem + as * C::kAccStride;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % C::kStages;
+                    HQ_STAMP(2, it, 0);
+                    // scales of the next k-iteration go ahead of this iteration's MMAs
+                    if (C::kSfSets > 1) {
+                        if (it + 1 < total_its) ok = copy_scales(it + 1);
+                    } else if (it > 0) {
+                        ok = copy_scales(it);
+                    }
+                    if (!ok) break;
+                    HQ_STAMP(2, it, 1);
+                    const uint32_t set = tmem + C::kSfCol0 + (it % C::kSfSets) * C::kSfCols;
+                    const uint64_t adesc = ptx::smem_desc(a_base + s * C::kABytes, 16, 1024, 2);
+                    const uint64_t bdesc = ptx::smem_desc(b_base + s * C::kBBytes, 16, 1024, 2);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        uint32_t atom, sf_id;
+                        if constexpr (KIND == 0) {
+                            atom = 0;
+                            sf_id = k;
+                        } else if constexpr (KIND == 1) {
+                            atom = k;
+                            sf_id = 0;
+                        } else {
+                            atom = k >> 1;
+                            sf_id = (k & 1) * 2;
+                        }
+                        ptx::tc_mma_block_scaled<2, KIND>(
+                            acc, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2),
+                            instr_desc_pair<BN, KIND>(sf_id), set + atom * 4,
+                            set + C::kSfKAtoms * 4 + atom * C::kNAtoms * 4, (kt > 0 || k > 0) ? 1u : 0u);
+                    }
+                    // both producers may refill stage s once these MMAs have read it
+                    const uint32_t empty = ptx::smem_u32(&bars->empty[s]);
+                    ptx::tc_commit_pair(ptx::mapa_cluster(empty, 0));
+                    ptx::tc_commit_pair(ptx::mapa_cluster(empty, 1));
+                }
+                if (ok) {
+                    const uint32_t accf = ptx::smem_u32(&bars->acc_full[as]);
+                    ptx::tc_commit_pair(ptx::mapa_cluster(accf, 0));
+                    ptx::tc_commit_pair(ptx::mapa_cluster(accf, 1));
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (both CTAs)
+        const int ew = warp - 2;
+        const uint32_t lane_base = (warp & 3) * 32;
+        const float scale = (KIND == 1 && alpha != nullptr) ? __ldg(alpha) : 1.0f;
+        uint32_t t = 0;
+        uint32_t stores = 0;
+        bool ok = true;
+        for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++t) {
+            const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+            const int m0 = tc.m * 256 + int(rank) * kBM;
+            const int n0 = tc.n * BN;
+            const uint32_t as = t & 1u;
+            const uint32_t aph = (t >> 1) & 1u;
+            ok = wait_bar(ptx::smem_u32(&bars->acc_full[as]), aph, abort, kStatusEpilogue);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const uint32_t acc = tmem + as * C::kAccStride + (lane_base << 16);
+#pragma unroll 1
+            for (int ci = 0; ci < C::kChunks; ++ci) {
+                const int c = (C::kOverlap != 0 && as == 0) ? C::kChunks - 1 - ci : ci;
+                uint32_t r[32];
+                ptx::tc_load_32x32(acc + c * kEpiChunk, r);
+                ptx::tc_wait_ld();
+                if (C::kOverlap != 0 && ci == C::kOverlapChunks - 1) {
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::mbar_arrive_cluster_addr(ptx::mapa_cluster(ptx::smem_u32(&bars->overlap_free[as]), 0));
+                    }
+                }
+                if (ci == C::kChunks - 1) {
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::mbar_arrive_cluster_addr(ptx::mapa_cluster(ptx::smem_u32(&bars->acc_empty[as]), 0));
+                    }
+                }
+                uint32_t p[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const __nv_bfloat162 v = __float22bfloat162_rn(make_float2(
+                        __uint_as_float(r[2 * i]) * scale, __uint_as_float(r[2 * i + 1]) * scale));
+                    p[i] = *reinterpret_cast<const uint32_t*>(&v);
+                }
+                const uint32_t buf = epi_base + (ew * C::kEpiBufs + (stores % C::kEpiBufs)) * kEpiBufBytes;
+                if (lane == 0) ptx::bulk_wait_read<C::kEpiBufs - 1>();
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t dst = buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(p[4 * j]),
+                                 "r"(p[4 * j + 1]), "r"(p[4 * j + 2]), "r"(p[4 * j + 3])
+                                 : "memory");
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::tma_store_2d(&tm_d, buf, n0 + c * kEpiChunk, m0 + int(lane_base));
+                    ptx::bulk_commit();
+                }
+                ++stores;
+            }
+        }
+        if (lane == 0) ptx::bulk_wait<0>();
+    }
+
+    if (*abort != 0u) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    // neither CTA may leave while the other can still signal its barriers or
+    // while MMAs of the pair read its shared memory
+    ptx::cluster_sync();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc<2>(tmem, C::kTmemCols);
+    }
+}
+
 // ---------------------------------------------------------------------------- host
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -472,6 +802,68 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     return HQ_OK;
 }
 
+template <int BN, int KIND>
+int launch_pair(const GemmArgs& g, char* err, size_t errlen) {
+    using C = Cfg2<BN, KIND>;
+    static std::once_flag once[16];
+    int dev = 0;
+    HQ_CUDA_TRY(cudaGetDevice(&dev));
+    cudaError_t attr_err = cudaSuccess;
+    std::call_once(once[dev & 15], [&] {
+        attr_err = cudaFuncSetAttribute(gemm_pair_kernel<BN, KIND>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    });
+    HQ_CUDA_TRY(attr_err);
+
+    const uint64_t atoms_a = uint64_t((g.m + 127) / 128) * uint64_t(g.kq_dim);
+    const uint64_t atoms_b = uint64_t((g.n + 127) / 128) * uint64_t(g.kq_dim);
+    CUtensorMap tm_a, tm_b, tm_d, tm_sfa, tm_sfb;
+    const bool maps_ok =
+        make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.a, uint64_t(g.k_bytes), uint64_t(g.m),
+                     uint64_t(g.k_bytes), kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B) &&
+        make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes), uint64_t(g.n),
+                     uint64_t(g.k_bytes), kBKBytes, BN / 2, CU_TENSOR_MAP_SWIZZLE_128B) &&
+        make_tmap_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out, uint64_t(g.n), uint64_t(g.m),
+                     uint64_t(g.ldo) * 2, kEpiChunk, 32, CU_TENSOR_MAP_SWIZZLE_64B) &&
+        // scale atoms as rows of 128 32-bit words
+        make_tmap_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_UINT32, g.sfa, 128, atoms_a, 512, 128, C::kSfKAtoms,
+                     CU_TENSOR_MAP_SWIZZLE_NONE) &&
+        make_tmap_2d(&tm_sfb, CU_TENSOR_MAP_DATA_TYPE_UINT32, g.sfb, 128, atoms_b, 512, 128, C::kSfKAtoms,
+                     CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (!maps_ok) {
+        return fail(err, errlen, HQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the GEMM operands");
+    }
+    const int tiles_m = (g.m + 255) / 256;
+    const int tiles_n = g.n / BN;
+    // persistent grid: no more clusters than can be resident at once
+    static int max_clusters[16];
+    if (max_clusters[dev & 15] == 0) {
+        cudaLaunchConfig_t occ = {};
+        occ.gridDim = dim3(2 * 74);
+        occ.blockDim = dim3(kThreads);
+        occ.dynamicSmemBytes = size_t(C::kSmemBytes);
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        occ.attrs = at;
+        occ.numAttrs = 1;
+        int n = 0;
+        HQ_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<BN, KIND>, &occ));
+        max_clusters[dev & 15] = n > 0 ? n : 1;
+        if (getenv("HALOPS_B200_TRACE") != nullptr) {
+            fprintf(stderr, "[gemm] pair tile %d: max active clusters %d\n", BN, n);
+        }
+    }
+    const int clusters = min(min(g.sm_count / 2, max_clusters[dev & 15]), tiles_m * tiles_n);
+    const int k_tiles = int(g.k_bytes / kBKBytes);
+    HQ_CUDA_TRY(launch(gemm_pair_kernel<BN, KIND>, dim3(2 * clusters), dim3(kThreads), size_t(C::kSmemBytes),
+                       g.stream, g.pdl, 2, tm_a, tm_b, tm_d, tm_sfa, tm_sfb, g.alpha, k_tiles, g.kq_dim, tiles_m,
+                       tiles_n));
+    return HQ_OK;
+}
+
 const char* mode_name(int mode) {
     switch (mode) {
         case HQ_MODE_W8A8_MXFP8:
@@ -483,25 +875,49 @@ const char* mode_name(int mode) {
     }
 }
 
+struct TilePick {
+    int bn;     // tile width, 0 = no tile fits
+    bool pair;  // 256-row tile on a pair of CTAs
+};
+
 // Shape legality follows the reference's "some compiled tile fits" rule
 // (csrc/kernel/gemm/gemm_dispatch.cuh:65-100 over the tiles of gemm_tile.cuh:371-395):
 // MXFP8 needs K % 128 == 0 and N % 64 == 0, the FP4 modes K % 256 == 0 and
-// N % 128 == 0; any M >= 1.  Returns the tile width, 0 when nothing fits.
-int pick_tile_n(int64_t m, int64_t n, int64_t k, int mode, int sm_count) {
+// N % 128 == 0; any M >= 1.  Among the legal tiles: the largest that still
+// gives every SM (or SM pair) a tile; failing that, the narrowest single-CTA
+// tile that divides N (most CTAs streaming the weight).  HALOPS_B200_TILE
+// (pair256 | pair128 | 256 | 128 | 64) overrides the choice when it is legal.
+TilePick pick_tile(int64_t m, int64_t n, int64_t k, int mode, int sm_count) {
     const bool fp8 = mode == HQ_MODE_W8A8_MXFP8;
-    if (m < 1 || n < 1 || k < 1) return 0;
-    if (fp8 ? (k % 128 != 0 || n % 64 != 0) : (k % 256 != 0 || n % 128 != 0)) return 0;
+    if (m < 1 || n < 1 || k < 1) return {0, false};
+    if (fp8 ? (k % 128 != 0 || n % 64 != 0) : (k % 256 != 0 || n % 128 != 0)) return {0, false};
     const int64_t tiles_m = (m + kBM - 1) / kBM;
-    // widest tile that divides N and still gives every SM a tile; failing
-    // that, the narrowest that divides N (most CTAs streaming the weight)
-    const int widths[3] = {256, 128, 64};
-    int narrowest = 0;
-    for (int w : widths) {
-        if (n % w != 0 || (w == 64 && !fp8)) continue;
-        if (tiles_m * (n / w) >= sm_count) return w;
-        narrowest = w;
+    const int64_t tiles_m2 = (m + 255) / 256;
+    const char* forced = getenv("HALOPS_B200_TILE");
+    if (forced != nullptr && forced[0] != '\0') {
+        const bool pair = strncmp(forced, "pair", 4) == 0;
+        const int w = atoi(pair ? forced + 4 : forced);
+        const bool legal = (w == 256 || w == 128 || (w == 64 && fp8 && !pair)) && n % w == 0;
+        if (legal) return {w, pair};
     }
-    return narrowest;
+    struct Cand {
+        int bn;
+        bool pair;
+    };
+    // measured on B200 (M=N=K=8192 MXFP8): 128x256 single-CTA 404 us, 256x256 pair 475 us,
+    // 128x128 620 us, 256x128 pair 807 us
+    const Cand order[4] = {{256, false}, {256, true}, {128, false}, {64, false}};
+    int narrowest = 0;
+    for (const Cand& c : order) {
+        if (n % c.bn != 0 || (c.bn == 64 && !fp8)) continue;
+        if (c.pair) {
+            if (m > kBM && tiles_m2 * (n / c.bn) >= sm_count / 2) return {c.bn, true};
+        } else {
+            if (tiles_m * (n / c.bn) >= sm_count) return {c.bn, false};
+            narrowest = c.bn;
+        }
+    }
+    return {narrowest, false};
 }
 
 std::mutex g_sm_mutex;
@@ -527,17 +943,17 @@ extern "C" int hq_describe_tile(int64_t m, int64_t n, int64_t k, int mode, int s
                                 char* buf, size_t buflen) {
     if (hq_group_size(mode) == 0) return hq::fail(buf, buflen, HQ_ERR_INVALID, "Unsupported mode: %d", mode);
     const int sm = sm_count > 0 ? sm_count : hq_sm_count(device);
-    const int bn = hq::pick_tile_n(m, n, k, mode, sm > 0 ? sm : 148);
-    if (bn == 0) {
+    const hq::TilePick pick = hq::pick_tile(m, n, k, mode, sm > 0 ? sm : 148);
+    if (pick.bn == 0) {
         return hq::fail(buf, buflen, HQ_ERR_INVALID,
                         "No dense %s tile for M=%lld (grid M=%lld), N=%lld, K=%lld", hq::mode_name(mode),
                         (long long)(m < 128 ? m : hq_sf_rows(m)), (long long)(m < 128 ? m : hq_sf_rows(m)), (long long)n,
                         (long long)k);
     }
     if (buf != nullptr && buflen > 0) {
-        snprintf(buf, buflen, "[gemm] mode=dense kind=%s m=%lld n=%lld k=%lld sm=%d -> %dx%d/%d pair=0",
-                 hq::mode_name(mode), (long long)m, (long long)n, (long long)k, sm, hq::kBM, bn,
-                 mode == HQ_MODE_W8A8_MXFP8 ? 128 : 256);
+        snprintf(buf, buflen, "[gemm] mode=dense kind=%s m=%lld n=%lld k=%lld sm=%d -> %dx%d/%d pair=%d",
+                 hq::mode_name(mode), (long long)m, (long long)n, (long long)k, sm, pick.pair ? 256 : hq::kBM,
+                 pick.bn, mode == HQ_MODE_W8A8_MXFP8 ? 128 : 256, pick.pair ? 1 : 0);
     }
     return HQ_OK;
 }
@@ -571,7 +987,7 @@ extern "C" int hq_dense_gemm(const void* a, const void* b, const void* sfa, cons
     if (m == 0 || n == 0) return HQ_OK;
 
     // shape legality first: it needs no device
-    if (hq::pick_tile_n(m, n, k, mode, 148) == 0) {
+    if (hq::pick_tile(m, n, k, mode, 148).bn == 0) {
         return fail(err, errlen, HQ_ERR_INVALID, "No dense %s tile for M=%lld (grid M=%lld), N=%lld, K=%lld",
                     hq::mode_name(mode), (long long)(m < 128 ? m : hq_sf_rows(m)),
                     (long long)(m < 128 ? m : hq_sf_rows(m)), (long long)n, (long long)k);
@@ -598,7 +1014,7 @@ extern "C" int hq_dense_gemm(const void* a, const void* b, const void* sfa, cons
     const int sm_all = hq_sm_count(device);
     const int sm = sm_count > 0 ? (sm_count < sm_all || sm_all == 0 ? sm_count : sm_all) : sm_all;
     if (sm <= 0) return fail(err, errlen, HQ_ERR_CUDA, "cannot query the SM count of device %d", device);
-    const int bn = hq::pick_tile_n(m, n, k, mode, sm);
+    const hq::TilePick pick = hq::pick_tile(m, n, k, mode, sm);
     if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || out == nullptr) {
         return fail(err, errlen, HQ_ERR_INVALID, "null pointer argument");
     }
@@ -630,14 +1046,18 @@ extern "C" int hq_dense_gemm(const void* a, const void* b, const void* sfa, cons
     g.direct_store = direct;
     g.stream = static_cast<cudaStream_t>(stream);
 
-#define HQ_DISPATCH(KIND)                                                \
-    switch (bn) {                                                        \
-        case 256:                                                        \
-            return hq::launch_tile<256, KIND>(g, err, errlen);           \
-        case 128:                                                        \
-            return hq::launch_tile<128, KIND>(g, err, errlen);           \
-        default:                                                         \
-            return hq::launch_tile<64, KIND>(g, err, errlen);            \
+#define HQ_DISPATCH(KIND)                                                            \
+    if (pick.pair) {                                                                 \
+        return pick.bn == 256 ? hq::launch_pair<256, KIND>(g, err, errlen)           \
+                              : hq::launch_pair<128, KIND>(g, err, errlen);          \
+    }                                                                                \
+    switch (pick.bn) {                                                               \
+        case 256:                                                                    \
+            return hq::launch_tile<256, KIND>(g, err, errlen);                       \
+        case 128:                                                                    \
+            return hq::launch_tile<128, KIND>(g, err, errlen);                       \
+        default:                                                                     \
+            return hq::launch_tile<64, KIND>(g, err, errlen);                        \
     }
     if (mode == HQ_MODE_W8A8_MXFP8) {
         HQ_DISPATCH(0)
@@ -667,5 +1087,11 @@ extern "C" int hq_device_status(int device, void* stream, uint32_t* status, char
     }
     return HQ_OK;
 }
+
+#ifdef HQ_TRACE
+extern "C" int hq_debug_trace(unsigned long long* host, int n) {
+    return cudaMemcpyFromSymbol(host, hq::g_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 extern "C" const char* hq_version(void) { return "halops_b200 0.1 (sm_100a)"; }

@@ -16,7 +16,7 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
 
@@ -59,6 +59,33 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta) 
         "}" ::"r"(bar),
         "r"(cta)
         : "memory");
+}
+
+// Registers `bytes` expected bytes and one arrival on a barrier given by its
+// shared::cluster address (it may belong to the other CTA of the pair).
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t bar_cluster, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(
+                     bar_cluster),
+                 "r"(bytes)
+                 : "memory");
+}
+// One arrival on a barrier given by its shared::cluster address.
+__device__ __forceinline__ void mbar_arrive_cluster_addr(uint32_t bar_cluster) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster)
+                 : "memory");
+}
+
+// ---- cluster -------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Full barrier over all threads of all CTAs of the cluster (every warp must call it converged).
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // ---- proxies / fences --------------------------------------------------------

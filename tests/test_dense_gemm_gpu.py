@@ -261,3 +261,25 @@ def test_errors_on_device(hq):
         hq.dense_gemm(x, w, sfa, sfb, out, epilogue=hq.EpilogueOp.Sigmoid)
     with pytest.raises(RuntimeError, match="multiple of 256"):
         hq.dense_gemm(x, w, sfa, sfb, out, torch.zeros([256], dtype=torch.bfloat16, device=dev))
+
+
+@pytest.mark.parametrize("tile", ["pair256", "pair128", "256", "128", "64"])
+@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4", "w4a4-mxfp4"])
+@pytest.mark.parametrize("m,n,k", [(512, 1024, 1024), (300, 512, 768), (2304, 2048, 512)], ids=lambda v: str(v))
+def test_every_tile_shape(hq, monkeypatch, tile, mode, m, n, k):
+    """Every compiled tile - single-CTA 128x{64,128,256} and the 2-CTA pair tiles
+    256x{128,256} - gives the same result, whatever the dispatch would pick."""
+    if tile == "64" and mode != "w8a8-mxfp8":
+        pytest.skip("64-wide tiles exist for MXFP8 only")
+    if mode != "w8a8-mxfp8" and k % 256:
+        pytest.skip("FP4 modes need K % 256 == 0")
+    a, b = _rand(m, k, 21), _rand(n, k, 22)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, mode)
+    base = _gemm(hq, aq, bq, sfa, sfb, mode)
+    monkeypatch.setenv("HALOPS_B200_TILE", tile)
+    want = ("256x" if tile.startswith("pair") else "128x") + tile.replace("pair", "")
+    assert want in hq.describe_tile(m, n, k, mode)
+    out = _gemm(hq, aq, bq, sfa, sfb, mode)
+    monkeypatch.delenv("HALOPS_B200_TILE")
+    assert torch.equal(out, base), "tiles disagree bitwise"
+    _check(out, aq, bq, sfa, sfb, mode, alpha=1.0 if mode == "w4a4-nvfp4" else None)
