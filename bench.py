@@ -347,6 +347,84 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------- shape sweep
+
+
+SWEEP = (
+    # (label, mode, M, N, K, A distribution, B scale)
+    [("C1", "w8a8-mxfp8", 128, 256, 512, "normal", 1.0),
+     ("C2", "w8a8-mxfp8", 8192, 8192, 8192, "normal", 0.02)]
+    + [(f"C3 m={m}", "w8a8-mxfp8", m, n, k, "student_t", 0.02)
+       for (n, k) in ((7168, 2048), (24576, 1536)) for m in (1, 8, 32, 64, 128)]
+    + [("C4", "w4a4-nvfp4", 4096, 14336, 4096, "normal", 1.0),
+       ("C5 shard of 8", "w8a8-mxfp8", 16384, 7168, 8192, "normal", 0.02),
+       ("ref CI 8192x4096x4096", "w8a8-mxfp8", 8192, 4096, 4096, "normal", 1.0),
+       ("ref CI 8192x4096x4096", "w4a4-nvfp4", 8192, 4096, 4096, "normal", 1.0),
+       ("ref CI 128x256x512", "w4a4-nvfp4", 128, 256, 512, "normal", 1.0),
+       ("ref README 1024x4096x8192", "w8a8-mxfp8", 1024, 4096, 8192, "normal", 1.0)]
+)
+
+
+def run_sweep(args):
+    """GEMM-only and quantizer-only medians for every BASELINE configuration and the
+    reference's published shapes, measured the way the reference's benchmark does
+    (cold L2: a 256 MiB buffer is zeroed before every timed call; 10 warm-up, 30 timed).
+    One JSON object per line; not the driver's contract line."""
+    import halops_b200 as hq
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = _peaks()
+    flush = torch.empty([256 << 20], dtype=torch.uint8, device=dev)
+
+    def median_us(fn, warm=10, reps=30):
+        for _ in range(warm):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e) * 1e3)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    for label, mode, m, n, k, dist, bscale in SWEEP:
+        g = torch.Generator(device=dev).manual_seed(2026)
+        a = torch.randn([m, k], generator=g, device=dev)
+        if dist == "student_t":
+            a = a / torch.sqrt(torch.randn([3, m, k], generator=g, device=dev).pow(2).sum(0) / 3)
+        a = a.to(torch.bfloat16)
+        b = (torch.randn([n, k], generator=g, device=dev) * bscale).to(torch.bfloat16)
+        aq, sfa = hq.group_wise_quant(a, mode=mode)
+        bq, sfb = hq.group_wise_quant(b, mode=mode)
+        out = torch.empty([m, n], dtype=torch.bfloat16, device=dev)
+        alpha = torch.ones([1], dtype=torch.float32, device=dev) if mode == "w4a4-nvfp4" else None
+        gemm_us = median_us(lambda: hq.dense_gemm(aq, bq, sfa, sfb, out, None, alpha, -1, mode, False))
+        qa_us = median_us(lambda: hq.group_wise_quant(a, mode=mode, use_pdl=False))
+        qb_us = median_us(lambda: hq.group_wise_quant(b, mode=mode, use_pdl=False))
+        assert hq.device_status(dev) == 0
+        fp8 = mode == "w8a8-mxfp8"
+        group = 32 if fp8 else 16
+        bpe = 1.0 if fp8 else 0.5
+        gemm_bytes = bpe * (m * k + n * k) + ((m + 127) // 128 * 128 + n) * k / group + 2.0 * m * n
+        q_bpe = 2 + bpe + 1.0 / group
+        flops = 2.0 * m * n * k
+        print(json.dumps({
+            "config": label, "mode": mode, "m": m, "n": n, "k": k,
+            "tile": hq.describe_tile(m, n, k, mode).split("-> ")[1],
+            "gemm_us": round(gemm_us, 2), "gemm_tflops": round(flops / gemm_us / 1e6, 1),
+            "gemm_gbs": round(gemm_bytes / gemm_us / 1e3, 1),
+            "gemm_frac_of_hbm": round(gemm_bytes / gemm_us / 1e3 / peaks["hbm_gbs"], 3),
+            "quant_a_us": round(qa_us, 2), "quant_b_us": round(qb_us, 2),
+            "quant_b_gbs": round(n * k * q_bpe / qb_us / 1e3, 1),
+            "quant_incl_tflops": round(flops / (gemm_us + qa_us + qb_us) / 1e6, 1),
+        }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -356,8 +434,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernels-only", action="store_true",
                     help="run only warm-up and the timed steps (for profiler captures)")
+    ap.add_argument("--sweep", action="store_true",
+                    help="time every BASELINE configuration (GEMM only / quantizer only, cold L2) instead")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.sweep:
+        run_sweep(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -156,7 +156,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const __grid_constant__ CUtensorMap tm_d, const uint8_t* __restrict__ sfa,
             const uint8_t* __restrict__ sfb, const float* __restrict__ alpha,
             __nv_bfloat16* __restrict__ out, int64_t ldo, int M, int N, int k_tiles, int kq_dim,
-            int tiles_m, int tiles_n, int direct_store) {
+            int tiles_m, int tiles_n, int a_rows, int direct_store) {
     using C = Cfg<BN, KIND>;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle of the operand tiles
@@ -221,7 +221,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ph ^ 1u, abort, kStatusProducer);
                     if (!ok) break;
                     const uint32_t full = ptx::smem_u32(&bars->full[s]);
-                    ptx::mbar_arrive_expect_tx(full, C::kStageBytes);
+                    // a short activation loads only its own rows (the A box is a_rows tall)
+                    ptx::mbar_arrive_expect_tx(full, C::kStageBytes - (kBM - a_rows) * kBKBytes);
                     ptx::tma_load_2d(a_base + s * C::kABytes, &tm_a, kt * kBKBytes, m0, full);
                     ptx::tma_load_2d(b_base + s * C::kBBytes, &tm_b, kt * kBKBytes, n0, full);
                     const int64_t koff = int64_t(kt) * C::kSfaBytes;
@@ -349,6 +350,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
                 const int row = m0 + int(lane_base) + lane;
                 const int col = n0 + c * kEpiChunk;
+                if (m0 + int(lane_base) >= M) continue;  // this warp's 32 rows are all padding
                 if (direct_store) {
                     if (row < M) {
                         uint4* dst = reinterpret_cast<uint4*>(out + int64_t(row) * ldo + col);
@@ -383,7 +385,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
             }
         }
-        if (lane == 0) ptx::bulk_wait<0>();
+        if (lane == 0) ptx::bulk_wait_read<0>();
     }
 
     if (*abort != 0u) {
@@ -699,7 +701,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 ++stores;
             }
         }
-        if (lane == 0) ptx::bulk_wait<0>();
+        if (lane == 0) ptx::bulk_wait_read<0>();
     }
 
     if (*abort != 0u) {
@@ -782,9 +784,13 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     HQ_CUDA_TRY(attr_err);
 
     CUtensorMap tm_a, tm_b, tm_d;
+    // M < 128: the A box holds only the rows that exist (rounded up to the 8-row
+    // swizzle period); the other rows of the shared-memory tile keep stale bytes,
+    // which only feed accumulator rows that are never stored
+    const int a_rows = g.m >= kBM ? kBM : (g.m + 7) / 8 * 8;
     const bool maps_ok =
         make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.a, uint64_t(g.k_bytes), uint64_t(g.m),
-                     uint64_t(g.k_bytes), kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B) &&
+                     uint64_t(g.k_bytes), kBKBytes, uint32_t(a_rows), CU_TENSOR_MAP_SWIZZLE_128B) &&
         make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes), uint64_t(g.n),
                      uint64_t(g.k_bytes), kBKBytes, BN, CU_TENSOR_MAP_SWIZZLE_128B) &&
         make_tmap_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out, uint64_t(g.n), uint64_t(g.m),
@@ -798,7 +804,7 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     const int k_tiles = int(g.k_bytes / kBKBytes);
     HQ_CUDA_TRY(launch(gemm_kernel<BN, KIND>, dim3(grid), dim3(kThreads), size_t(C::kSmemBytes), g.stream,
                        g.pdl, 1, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.out, g.ldo, g.m, g.n, k_tiles,
-                       g.kq_dim, tiles_m, tiles_n, g.direct_store ? 1 : 0));
+                       g.kq_dim, tiles_m, tiles_n, a_rows, g.direct_store ? 1 : 0));
     return HQ_OK;
 }
 
@@ -899,6 +905,23 @@ TilePick pick_tile(int64_t m, int64_t n, int64_t k, int mode, int sm_count) {
         const int w = atoi(pair ? forced + 4 : forced);
         const bool legal = (w == 256 || w == 128 || (w == 64 && fp8 && !pair)) && n % w == 0;
         if (legal) return {w, pair};
+    }
+    if (tiles_m == 1) {
+        // One row of tiles: the weight streams through once, so what counts is the
+        // largest share of weight rows any CTA has to stream (tiles per CTA x width,
+        // plus a fixed cost per tile of about 16 rows' worth); ties go to the wider tile.
+        int best = 0;
+        int64_t best_cost = 0;
+        for (int w : {256, 128, 64}) {
+            if (n % w != 0 || (w == 64 && !fp8)) continue;
+            const int64_t tiles = n / w;
+            const int64_t cost = ((tiles + sm_count - 1) / sm_count) * (w + 16);
+            if (best == 0 || cost < best_cost) {
+                best = w;
+                best_cost = cost;
+            }
+        }
+        return {best, false};
     }
     struct Cand {
         int bn;
