@@ -47,29 +47,56 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
     return v;
 }
 
+// Pair-wise operations on a 32-bit word holding two T (x in the low half).
 template <typename T>
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]);
+struct Pair;
 
 template <>
-__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& v,
-                                                       float (&f)[8]) {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        f[2 * i] = __uint_as_float(w[i] << 16);
-        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+struct Pair<__nv_bfloat16> {
+    static constexpr uint32_t kNegInf2 = 0xff80ff80u;
+    static __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) {
+        uint32_t r;
+        asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));  // a NaN operand is ignored
+        return r;
     }
+    static __device__ __forceinline__ float lo(uint32_t w) { return __uint_as_float(w << 16); }
+    static __device__ __forceinline__ float hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+};
+
+template <>
+struct Pair<__half> {
+    static constexpr uint32_t kNegInf2 = 0xfc00fc00u;
+    static __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) {
+        uint32_t r;
+        asm("max.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
+    static __device__ __forceinline__ float lo(uint32_t w) {
+        return __half2float(__ushort_as_half(static_cast<unsigned short>(w & 0xffffu)));
+    }
+    static __device__ __forceinline__ float hi(uint32_t w) {
+        return __half2float(__ushort_as_half(static_cast<unsigned short>(w >> 16)));
+    }
+};
+
+// (a * s, b * s) as one packed instruction
+__device__ __forceinline__ float2 mul2(float a, float b, float s) {
+    float2 r;
+    asm("{\n\t"
+        ".reg .b64 t, u;\n\t"
+        "mov.b64 t, {%2, %3};\n\t"
+        "mov.b64 u, {%4, %4};\n\t"
+        "mul.rn.f32x2 t, t, u;\n\t"
+        "mov.b64 {%0, %1}, t;\n\t"
+        "}"
+        : "=f"(r.x), "=f"(r.y)
+        : "f"(a), "f"(b), "f"(s));
+    return r;
 }
-
-template <>
-__device__ __forceinline__ void unpack8<__half>(const uint4& v, float (&f)[8]) {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 p = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-        f[2 * i] = p.x;
-        f[2 * i + 1] = p.y;
-    }
+// -0.0 -> +0.0, everything else unchanged.  (Written as two scalar adds: the
+// packed add.rn.f32x2 with a zero operand does not survive ptxas.)
+__device__ __forceinline__ float2 add_zero2(float2 v) {
+    return make_float2(__fadd_rn(v.x, 0.0f), __fadd_rn(v.y, 0.0f));
 }
 
 // UE8M0 byte of ceil(log2(amax / D)) + 127 with the reference kernel's
@@ -103,101 +130,81 @@ __device__ __forceinline__ float clamp_sym(float x, float lim) {
 }
 
 // Two e2m1 codes (x in the low nibble), nearest with ties away from zero; a
-// negative value that rounds to zero keeps its sign bit, -0.0 does not.
-// cvt rounds ties to even, so the midpoints that would go to the smaller
-// (even) code - 0.25, 1.25, 2.5, 5 - are first moved one ulp outwards.
-__device__ __forceinline__ uint32_t e2m1x2(float x, float y) {
-    const auto away = [](float v) {
-        v += 0.0f;  // -0.0 -> +0.0
-        const uint32_t b = __float_as_uint(v);
+// negative value that rounds to zero keeps its sign bit, -0.0 does not (the
+// caller has added +0.0).  cvt rounds ties to even, so the midpoints that would
+// go to the smaller (even) code - 0.25, 1.25, 2.5, 5 - are first moved one ulp
+// outwards.
+__device__ __forceinline__ uint32_t e2m1x2_half_away(float2 v) {
+    const auto away = [](float x) {
+        const uint32_t b = __float_as_uint(x);
         const uint32_t a = b & 0x7fffffffu;
         const bool tie = ((a - 0x3fa00000u) & 0xfe7fffffu) == 0u || a == 0x3e800000u;
         return __uint_as_float(b + (tie ? 1u : 0u));
     };
-    return __nv_cvt_float2_to_fp4x2(make_float2(away(x), away(y)), __NV_E2M1,
-                                    cudaRoundNearest);
+    return __nv_cvt_float2_to_fp4x2(make_float2(away(v.x), away(v.y)), __NV_E2M1, cudaRoundNearest);
+}
+// Same for values that are exact products of a 16-bit float and a power of two
+// and have already been scaled by 1 + 2^-23: such a value is never within an
+// ulp below a midpoint, so plain round-to-nearest-even gives ties away.
+__device__ __forceinline__ uint32_t e2m1x2_rne(float2 v) {
+    return __nv_cvt_float2_to_fp4x2(v, __NV_E2M1, cudaRoundNearest);
 }
 
 __device__ __forceinline__ uint32_t e4m3x2(float x, float y) {
     return __nv_cvt_float2_to_fp8x2(make_float2(x, y), __NV_SATFINITE, __NV_E4M3);
 }
 
-__device__ __forceinline__ int64_t sf_atom_offset(int64_t row, int kb, int kb_dim) {
-    return ((row >> 7) * (kb_dim >> 2) + (kb >> 2)) * 512 + (row & 31) * 16 +
-           ((row >> 5) & 3) * 4 + (kb & 3);
-}
-
-// kEpl elements per lane and piece: 8 for the 32-element groups (4 lanes per
-// group), 16 for NVFP4 (one lane per group).
-template <typename T, int kMode, bool kSwizzle>
-__global__ void __launch_bounds__(kThreads)
-group_wise_quant_kernel(const T* __restrict__ input, int64_t ld,
-                        uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf,
-                        int64_t m, int64_t rows_total, int k, int kb_dim) {
+// One warp quantizes kColsPerWarp consecutive elements of one row.  A lane
+// handles kEpl elements per piece: 8 for the 32-element groups (4 lanes per
+// group), 16 for NVFP4 (one lane per group).  Every address is a per-lane base
+// computed once plus a compile-time offset per piece.  kFull: the whole
+// segment lies inside the row, no column predicates.
+template <typename T, int kMode, bool kSwizzle, bool kFull>
+__device__ __forceinline__ void quantize_segment(const T* __restrict__ in_row,
+                                                 uint8_t* __restrict__ q_row,
+                                                 uint8_t* __restrict__ sf_lane, int col0, int k,
+                                                 int lane) {
     constexpr bool kNv = kMode == HQ_MODE_W4A4_NVFP4;
     constexpr bool kFp4 = kMode != HQ_MODE_W8A8_MXFP8;
     constexpr int kEpl = kNv ? 16 : 8;
     constexpr int kPieces = kColsPerWarp / (32 * kEpl);  // 4 or 2
     constexpr int kGroup = kNv ? 16 : 32;
+    constexpr int kWords = kEpl / 2;
+    using P = Pair<T>;
 
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    const int64_t row = int64_t(blockIdx.x) * kWarpsPerCta + warp;
-    const int col0 = blockIdx.y * kColsPerWarp;
-
-    // The first global access is below: with a programmatic launch the index
-    // math above overlaps the tail of the producing kernel.
-    pdl_wait();
-    pdl_launch_dependents();
-
-    if (row >= rows_total) return;
-
-    if (row >= m) {
-        // padding rows of the last SfAtom (swizzled layout only): zero scales
-        if constexpr (kSwizzle) {
-#pragma unroll
-            for (int p = 0; p < kPieces; ++p) {
-                const int col = col0 + (p * 32 + lane) * kEpl;
-                const int kb = col / kGroup;
-                const bool lead = kNv ? (lane & 3) == 0 : (lane & 15) == 0;
-                if (col < k && lead) {
-                    *reinterpret_cast<uint32_t*>(out_sf + sf_atom_offset(row, kb, kb_dim)) = 0u;
-                }
-            }
-        }
-        return;
-    }
-
-    const T* const in_row = input + row * ld;
+    const uint4* const src = reinterpret_cast<const uint4*>(in_row + col0 + lane * kEpl);
+    const int lane_col = col0 + lane * kEpl;
     uint4 raw[kPieces][kEpl / 8];
 #pragma unroll
     for (int p = 0; p < kPieces; ++p) {
-        const int col = col0 + (p * 32 + lane) * kEpl;
 #pragma unroll
         for (int h = 0; h < kEpl / 8; ++h) {
-            raw[p][h] = col < k ? ld_stream(in_row + col + h * 8) : make_uint4(0, 0, 0, 0);
+            const bool active = kFull || lane_col + p * 32 * kEpl < k;
+            raw[p][h] = active ? ld_stream(src + p * 4 * kEpl + h) : make_uint4(0, 0, 0, 0);
         }
     }
 
 #pragma unroll
     for (int p = 0; p < kPieces; ++p) {
-        const int col = col0 + (p * 32 + lane) * kEpl;
-        const bool active = col < k;
-        float v[kEpl];
+        const bool active = kFull || lane_col + p * 32 * kEpl < k;
+        uint32_t w[kWords];
 #pragma unroll
         for (int h = 0; h < kEpl / 8; ++h) {
-            float f[8];
-            unpack8<T>(raw[p][h], f);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[h * 8 + i] = f[i];
+            w[4 * h + 0] = raw[p][h].x;
+            w[4 * h + 1] = raw[p][h].y;
+            w[4 * h + 2] = raw[p][h].z;
+            w[4 * h + 3] = raw[p][h].w;
         }
-        float amax = kAmaxFloor;
+        // group amax on the packed 16-bit values (NaN operands are ignored, as fmaxf does)
+        uint32_t mx = w[0] & 0x7fff7fffu;
 #pragma unroll
-        for (int i = 0; i < kEpl; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        for (int i = 1; i < kWords; ++i) mx = P::max2(mx, w[i] & 0x7fff7fffu);
+        mx = P::max2(mx, __byte_perm(mx, 0, 0x1032));
         if constexpr (!kNv) {
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            mx = P::max2(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = P::max2(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         }
+        const float amax = fmaxf(P::lo(mx), kAmaxFloor);
 
         uint32_t sf_byte;
         float inv;
@@ -217,56 +224,135 @@ group_wise_quant_kernel(const T* __restrict__ input, int64_t ld,
             inv = __frcp_rn(dec);
         }
 
-        if constexpr (!kFp4) {
-            uint32_t w[2];
+        // The reference clamps every scaled value with fminf(fmaxf(x, -MAX), MAX), which
+        // also turns NaN into -MAX.  Finite values never exceed MAX after scaling (or
+        // saturate in the conversion), so only the NaN rule needs work: NaN is replaced
+        // by -inf in the packed input, which scales to -inf and saturates to -MAX.  A
+        // group that holds an infinity has inv == 0 (inf * 0 = NaN) and takes the
+        // literal clamp.
+        uint32_t codes[kWords];
+        if (inv != 0.0f) {
+            const float mult = kMode == HQ_MODE_W4A4_MXFP4 ? inv * (1.0f + 1.1920929e-7f) : inv;
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const uint32_t lo = e4m3x2(clamp_sym(__fmul_rn(v[4 * i], inv), kE4m3Max),
-                                           clamp_sym(__fmul_rn(v[4 * i + 1], inv), kE4m3Max));
-                const uint32_t hi = e4m3x2(clamp_sym(__fmul_rn(v[4 * i + 2], inv), kE4m3Max),
-                                           clamp_sym(__fmul_rn(v[4 * i + 3], inv), kE4m3Max));
-                w[i] = lo | (hi << 16);
-            }
-            if (active) {
-                *reinterpret_cast<uint2*>(out_q + row * int64_t(k) + col) = make_uint2(w[0], w[1]);
+            for (int i = 0; i < kWords; ++i) {
+                const uint32_t g = P::max2(w[i], P::kNegInf2);
+                const float2 x = mul2(P::lo(g), P::hi(g), mult);
+                if constexpr (kMode == HQ_MODE_W8A8_MXFP8) {
+                    codes[i] = e4m3x2(x.x, x.y);
+                } else if constexpr (kMode == HQ_MODE_W4A4_MXFP4) {
+                    codes[i] = e2m1x2_rne(add_zero2(x)) & 0xffu;
+                } else {
+                    codes[i] = e2m1x2_half_away(add_zero2(x)) & 0xffu;
+                }
             }
         } else {
-            uint32_t w[kEpl / 8];
+            const float lim = kFp4 ? kE2m1Max : kE4m3Max;
 #pragma unroll
-            for (int h = 0; h < kEpl / 8; ++h) {
-                uint32_t acc = 0;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float a = clamp_sym(__fmul_rn(v[h * 8 + 2 * i], inv), kE2m1Max);
-                    const float b = clamp_sym(__fmul_rn(v[h * 8 + 2 * i + 1], inv), kE2m1Max);
-                    acc |= (e2m1x2(a, b) & 0xffu) << (8 * i);
-                }
-                w[h] = acc;
-            }
-            if (active) {
-                uint8_t* dst = out_q + row * int64_t(k >> 1) + (col >> 1);
-                if constexpr (kNv) {
-                    *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[kEpl / 8 - 1]);
+            for (int i = 0; i < kWords; ++i) {
+                const float a = clamp_sym(__fmul_rn(P::lo(w[i]), inv), lim);
+                const float b = clamp_sym(__fmul_rn(P::hi(w[i]), inv), lim);
+                if constexpr (!kFp4) {
+                    codes[i] = e4m3x2(a, b);
                 } else {
-                    *reinterpret_cast<uint32_t*>(dst) = w[0];
+                    codes[i] = e2m1x2_half_away(add_zero2(make_float2(a, b))) & 0xffu;
                 }
             }
         }
 
-        const int kb = col / kGroup;
+        if constexpr (!kFp4) {
+            // 4 x (2 codes in 16 bits) -> 2 words; 8 bytes per lane and piece
+            const uint32_t q0 = __byte_perm(codes[0], codes[1], 0x5410);
+            const uint32_t q1 = __byte_perm(codes[2], codes[3], 0x5410);
+            if (active) {
+                reinterpret_cast<uint2*>(q_row + col0 + lane * 8)[p * 32] = make_uint2(q0, q1);
+            }
+        } else {
+            // one byte per pair -> one word per 8 elements
+            uint32_t q[kWords / 4];
+#pragma unroll
+            for (int h = 0; h < kWords / 4; ++h) {
+                q[h] = codes[4 * h] | (codes[4 * h + 1] << 8) | (codes[4 * h + 2] << 16) |
+                       (codes[4 * h + 3] << 24);
+            }
+            if (active) {
+                uint8_t* const dst = q_row + (col0 >> 1) + lane * (kEpl / 2);
+                if constexpr (kNv) {
+                    reinterpret_cast<uint2*>(dst)[p * 32] = make_uint2(q[0], q[kWords / 4 - 1]);
+                } else {
+                    reinterpret_cast<uint32_t*>(dst)[p * 32] = q[0];
+                }
+            }
+        }
+
         if constexpr (kSwizzle) {
-            // the four scale bytes of one SfAtom word sit in lanes L, L+s, L+2s, L+3s
+            // the four scale bytes of one SfAtom word sit in lanes L, L+s, L+2s, L+3s;
+            // consecutive words of a row are 512 bytes apart
             constexpr int s = kNv ? 1 : 4;
             uint32_t word = sf_byte;
             word |= __shfl_down_sync(0xffffffffu, word, s) << 8;
             word |= __shfl_down_sync(0xffffffffu, word, 2 * s) << 16;
             if (active && (lane & (4 * s - 1)) == 0) {
-                *reinterpret_cast<uint32_t*>(out_sf + sf_atom_offset(row, kb, kb_dim)) = word;
+                *reinterpret_cast<uint32_t*>(sf_lane + p * (8 * kEpl / kGroup) * 512) = word;
             }
         } else {
             const bool lead = kNv ? true : (lane & 3) == 0;
-            if (active && lead) out_sf[row * int64_t(kb_dim) + kb] = uint8_t(sf_byte);
+            if (active && lead) sf_lane[p * (32 * kEpl / kGroup)] = uint8_t(sf_byte);
         }
+    }
+}
+
+template <typename T, int kMode, bool kSwizzle>
+__global__ void __launch_bounds__(kThreads)
+group_wise_quant_kernel(const T* __restrict__ input, int64_t ld,
+                        uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf,
+                        int64_t m, int64_t rows_total, int k, int kb_dim) {
+    constexpr bool kNv = kMode == HQ_MODE_W4A4_NVFP4;
+    constexpr bool kFp4 = kMode != HQ_MODE_W8A8_MXFP8;
+    constexpr int kEpl = kNv ? 16 : 8;
+    constexpr int kPieces = kColsPerWarp / (32 * kEpl);
+    constexpr int kGroup = kNv ? 16 : 32;
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int64_t row = int64_t(blockIdx.x) * kWarpsPerCta + warp;
+    const int col0 = blockIdx.y * kColsPerWarp;
+
+    // per-lane base of this lane's scale bytes for piece 0
+    uint8_t* sf_lane;
+    if constexpr (kSwizzle) {
+        sf_lane = out_sf + ((row >> 7) * (kb_dim >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 +
+                  int64_t((col0 + lane * kEpl) / (4 * kGroup)) * 512;
+    } else {
+        sf_lane = out_sf + row * int64_t(kb_dim) + (col0 + lane * kEpl) / kGroup;
+    }
+
+    // The first global access is below: with a programmatic launch the index
+    // math above overlaps the tail of the producing kernel.
+    pdl_wait();
+    pdl_launch_dependents();
+
+    if (row >= rows_total) return;
+
+    if (row >= m) {
+        // padding rows of the last SfAtom (swizzled layout only): zero scales
+        if constexpr (kSwizzle) {
+            const bool lead = kNv ? (lane & 3) == 0 : (lane & 15) == 0;
+#pragma unroll
+            for (int p = 0; p < kPieces; ++p) {
+                if (lead && col0 + (p * 32 + lane) * kEpl < k) {
+                    *reinterpret_cast<uint32_t*>(sf_lane + p * (8 * kEpl / kGroup) * 512) = 0u;
+                }
+            }
+        }
+        return;
+    }
+
+    const T* const in_row = input + row * ld;
+    uint8_t* const q_row = out_q + row * int64_t(kFp4 ? (k >> 1) : k);
+    if (col0 + kColsPerWarp <= k) {
+        quantize_segment<T, kMode, kSwizzle, true>(in_row, q_row, sf_lane, col0, k, lane);
+    } else {
+        quantize_segment<T, kMode, kSwizzle, false>(in_row, q_row, sf_lane, col0, k, lane);
     }
 }
 
