@@ -347,6 +347,95 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------- config 5 (N-sharded, strong scaling)
+
+
+def run_c5(args):
+    """Config 5: M=16384, N=57344, K=8192 MXFP8, weight rows (output columns) split
+    over the ranks; the activation is replicated and quantised on every rank.  Strong
+    scaling: the whole job is fixed, each rank computes N/world columns.  Reports the
+    aggregate TFLOPS of quantise + GEMM, of the GEMM alone, and with the NCCL all-gather
+    of the bf16 output added (max over ranks, CUDA events)."""
+    import halops_b200 as hq
+    from halops_b200.dist import ColumnParallelDenseGemm, shard_bounds
+
+    rank, world, local = _dist_env()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+    m, n, k = 16384, 57344, 8192
+    start, rows = shard_bounds(n, world, rank)
+    g = torch.Generator(device=dev).manual_seed(2031)
+    x = torch.randn([m, k], generator=g, device=dev).to(torch.bfloat16)
+    gw = torch.Generator(device=dev).manual_seed(7000 + rank)
+    w = (torch.randn([rows, k], generator=gw, device=dev) * 0.02).to(torch.bfloat16)
+    layer = ColumnParallelDenseGemm(w, mode=MODE)
+    out = torch.empty([m, rows], dtype=torch.bfloat16, device=dev)
+    xq = torch.empty([m, k], dtype=torch.float8_e4m3fn, device=dev)
+    sfa = torch.empty([m, k // 32], dtype=torch.uint8, device=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(reps):
+            fn()
+        e.record()
+        barrier()
+        t = torch.tensor([s.elapsed_time(e) / reps], device=dev, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def gemm_only():
+        layer.local_quantized(xq, sfa, out)
+
+    def quant_gemm():
+        hq.group_wise_quant(x, MODE, True, True, xq, sfa)
+        layer.local_quantized(xq, sfa, out)
+
+    def quant_gemm_gather():
+        quant_gemm()
+        layer.gather(out)
+
+    hq.group_wise_quant(x, MODE, True, True, xq, sfa)
+    reps = max(3, min(args.steps, 10))
+    t_gemm = timed(gemm_only, reps)
+    t_step = timed(quant_gemm, reps)
+    t_gather = timed(quant_gemm_gather, reps) if world > 1 else t_step
+    assert hq.device_status(dev) == 0
+    flops = 2.0 * m * n * k
+    if rank == 0:
+        print(json.dumps({
+            "metric": "mxfp8_dense_gemm_tflops_quant_incl", "value": flops / (t_step * 1e-3) / 1e12, "unit": "TFLOPS",
+            "n_gpus": world, "steps": reps, "warmup": 3, "ms_per_step": t_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32 accumulate -> bf16",
+            "data": "synthetic",
+            "config": {"workload": f"C5 N-sharded MXFP8 GEMM M={m} N={n} K={k}, {rows} weight rows per rank; "
+                                   "step = group_wise_quant(activation) + dense_gemm on the rank's shard "
+                                   "(weights quantised once at load)",
+                       "tile": hq.describe_tile(m, rows, k, MODE, device=local)},
+            "gemm_only": {"tflops": flops / (t_gemm * 1e-3) / 1e12, "ms": t_gemm},
+            "with_allgather": {"tflops": flops / (t_gather * 1e-3) / 1e12, "ms": t_gather,
+                               "gathered_bytes_per_rank": m * (n - rows) * 2},
+        }), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 # ----------------------------------------------------------------------------- shape sweep
 
 
@@ -436,9 +525,13 @@ def main():
                     help="run only warm-up and the timed steps (for profiler captures)")
     ap.add_argument("--sweep", action="store_true",
                     help="time every BASELINE configuration (GEMM only / quantizer only, cold L2) instead")
+    ap.add_argument("--c5", action="store_true",
+                    help="run config 5 (M=16384, N=57344, K=8192 split over the ranks, strong scaling) instead")
     args = ap.parse_args()
     if args.sweep:
         run_sweep(args)
+    elif args.c5:
+        run_c5(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

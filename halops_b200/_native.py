@@ -25,7 +25,7 @@ SIGNATURES = {
     "hq_sf_rows": (c_i64, [c_i64]),
     "hq_group_wise_quant": (c_int, [c_void_p, c_i64, c_int, c_i64, c_i64, c_int, c_int, c_int,
                                     c_void_p, c_void_p, c_int, c_void_p, c_char_p, c_size_t]),
-    "hq_dense_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+    "hq_dense_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_int, c_int, c_int,
                               c_int, c_void_p, c_char_p, c_size_t]),
     "hq_sm_count": (c_int, [c_int]),

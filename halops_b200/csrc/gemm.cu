@@ -150,13 +150,49 @@ __device__ __forceinline__ uint32_t instr_desc(uint32_t sf_id) {
            (uint32_t(kBM >> 4) << 24) | (sf_id << 29);
 }
 
+// Epilogue math for one 32-column chunk of one accumulator row:
+// y = acc * alpha (+ bias[col]); Identity stores bf16(y), Sigmoid stores
+// bf16(0.5 * tanh.approx(0.5 * y) + 0.5), the reference's formulation
+// (csrc/common/activation.cuh:25-27, csrc/kernel/gemm/epilogue.cuh:867-951).
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], uint32_t (&p)[16], float scale,
+                                               const __nv_bfloat16* __restrict__ bias_chunk, int epi_op) {
+    float y[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) y[i] = __uint_as_float(r[i]) * scale;
+    if (bias_chunk != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(bias_chunk) + j);
+            const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                y[8 * j + 2 * i] += __uint_as_float(w[i] << 16);
+                y[8 * j + 2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+            }
+        }
+    }
+    if (epi_op == HQ_EPILOGUE_SIGMOID) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            float t;
+            asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * y[i]));
+            y[i] = fmaf(0.5f, t, 0.5f);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const __nv_bfloat162 v = __float22bfloat162_rn(make_float2(y[2 * i], y[2 * i + 1]));
+        p[i] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+}
+
 template <int BN, int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_d, const uint8_t* __restrict__ sfa,
             const uint8_t* __restrict__ sfb, const float* __restrict__ alpha,
-            __nv_bfloat16* __restrict__ out, int64_t ldo, int M, int N, int k_tiles, int kq_dim,
-            int tiles_m, int tiles_n, int a_rows, int direct_store) {
+            const __nv_bfloat16* __restrict__ bias, int epi_op, __nv_bfloat16* __restrict__ out, int64_t ldo,
+            int M, int N, int k_tiles, int kq_dim, int tiles_m, int tiles_n, int a_rows, int direct_store) {
     using C = Cfg<BN, KIND>;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle of the operand tiles
@@ -342,12 +378,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[as]));
                 }
                 uint32_t p[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const __nv_bfloat162 v = __float22bfloat162_rn(make_float2(
-                        __uint_as_float(r[2 * i]) * scale, __uint_as_float(r[2 * i + 1]) * scale));
-                    p[i] = *reinterpret_cast<const uint32_t*>(&v);
-                }
+                epilogue_chunk(r, p, scale, bias != nullptr ? bias + n0 + c * kEpiChunk : nullptr, epi_op);
                 const int row = m0 + int(lane_base) + lane;
                 const int col = n0 + c * kEpiChunk;
                 if (m0 + int(lane_base) >= M) continue;  // this warp's 32 rows are all padding
@@ -461,8 +492,9 @@ template <int BN, int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_d, const __grid_constant__ CUtensorMap tm_sfa,
-                 const __grid_constant__ CUtensorMap tm_sfb, const float* __restrict__ alpha, int k_tiles,
-                 int kq_dim, int tiles_m, int tiles_n) {
+                 const __grid_constant__ CUtensorMap tm_sfb, const float* __restrict__ alpha,
+                 const __nv_bfloat16* __restrict__ bias, int epi_op, int k_tiles, int kq_dim, int tiles_m,
+                 int tiles_n) {
     using C = Cfg2<BN, KIND>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -676,12 +708,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     }
                 }
                 uint32_t p[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const __nv_bfloat162 v = __float22bfloat162_rn(make_float2(
-                        __uint_as_float(r[2 * i]) * scale, __uint_as_float(r[2 * i + 1]) * scale));
-                    p[i] = *reinterpret_cast<const uint32_t*>(&v);
-                }
+                epilogue_chunk(r, p, scale, bias != nullptr ? bias + n0 + c * kEpiChunk : nullptr, epi_op);
                 const uint32_t buf = epi_base + (ew * C::kEpiBufs + (stores % C::kEpiBufs)) * kEpiBufBytes;
                 if (lane == 0) ptx::bulk_wait_read<C::kEpiBufs - 1>();
                 __syncwarp();
@@ -759,6 +786,8 @@ struct GemmArgs {
     const uint8_t* sfa;
     const uint8_t* sfb;
     const float* alpha;
+    const __nv_bfloat16* bias;
+    int epi_op;
     __nv_bfloat16* out;
     int64_t ldo;
     int m, n;
@@ -803,7 +832,7 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     const int grid = min(g.sm_count, tiles_m * tiles_n);
     const int k_tiles = int(g.k_bytes / kBKBytes);
     HQ_CUDA_TRY(launch(gemm_kernel<BN, KIND>, dim3(grid), dim3(kThreads), size_t(C::kSmemBytes), g.stream,
-                       g.pdl, 1, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.out, g.ldo, g.m, g.n, k_tiles,
+                       g.pdl, 1, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.bias, g.epi_op, g.out, g.ldo, g.m, g.n, k_tiles,
                        g.kq_dim, tiles_m, tiles_n, a_rows, g.direct_store ? 1 : 0));
     return HQ_OK;
 }
@@ -865,7 +894,7 @@ int launch_pair(const GemmArgs& g, char* err, size_t errlen) {
     const int clusters = min(min(g.sm_count / 2, max_clusters[dev & 15]), tiles_m * tiles_n);
     const int k_tiles = int(g.k_bytes / kBKBytes);
     HQ_CUDA_TRY(launch(gemm_pair_kernel<BN, KIND>, dim3(2 * clusters), dim3(kThreads), size_t(C::kSmemBytes),
-                       g.stream, g.pdl, 2, tm_a, tm_b, tm_d, tm_sfa, tm_sfb, g.alpha, k_tiles, g.kq_dim, tiles_m,
+                       g.stream, g.pdl, 2, tm_a, tm_b, tm_d, tm_sfa, tm_sfb, g.alpha, g.bias, g.epi_op, k_tiles, g.kq_dim, tiles_m,
                        tiles_n));
     return HQ_OK;
 }
@@ -982,7 +1011,7 @@ extern "C" int hq_describe_tile(int64_t m, int64_t n, int64_t k, int mode, int s
 }
 
 extern "C" int hq_dense_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* out,
-                             const float* alpha, int64_t m, int64_t n, int64_t k, int64_t sfa_bytes,
+                             const void* bias, const float* alpha, int64_t m, int64_t n, int64_t k, int64_t sfa_bytes,
                              int64_t sfb_bytes, int64_t ldo, int mode, int epilogue, int sm_count,
                              int use_pdl, int device, void* stream, char* err, size_t errlen) {
     using hq::fail;
@@ -991,9 +1020,21 @@ extern "C" int hq_dense_gemm(const void* a, const void* b, const void* sfa, cons
         return fail(err, errlen, HQ_ERR_INVALID,
                     "Unsupported mode: %d. Expected 'w8a8-mxfp8', 'w4a4-mxfp4' or 'w4a4-nvfp4'.", mode);
     }
-    if (epilogue != HQ_EPILOGUE_IDENTITY) {
+    if (epilogue != HQ_EPILOGUE_IDENTITY && epilogue != HQ_EPILOGUE_SIGMOID) {
         return fail(err, errlen, HQ_ERR_UNSUPPORTED, "Unsupported epilogue %d for %s", epilogue,
                     hq::mode_name(mode));
+    }
+    if (bias != nullptr && mode != HQ_MODE_W8A8_MXFP8) {
+        return fail(err, errlen, HQ_ERR_INVALID, "W4A4 mode does not support bias yet.");
+    }
+    if (bias != nullptr && m % 256 != 0) {
+        // kept from the reference, whose bias tile has no per-row store predicate
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "the bias tile has no per-row store predicate yet, so M must be a multiple of 256 "
+                    "when bias is given, got %lld", (long long)m);
+    }
+    if (bias != nullptr && !hq::aligned(bias, 16)) {
+        return fail(err, errlen, HQ_ERR_INVALID, "bias must be 16-byte aligned");
     }
     if (m < 0 || n < 0 || k < 0 || m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) {
         return fail(err, errlen, HQ_ERR_INVALID, "input must be a 2D tensor of shape [M, K]");
@@ -1054,6 +1095,8 @@ extern "C" int hq_dense_gemm(const void* a, const void* b, const void* sfa, cons
     g.sfa = static_cast<const uint8_t*>(sfa);
     g.sfb = static_cast<const uint8_t*>(sfb);
     g.alpha = alpha;
+    g.bias = static_cast<const __nv_bfloat16*>(bias);
+    g.epi_op = epilogue;
     g.out = static_cast<__nv_bfloat16*>(out);
     g.ldo = ldo;
     g.m = int(m);

@@ -1,8 +1,9 @@
 """``dense_gemm``: same signature, defaults and error texts as the reference's
 ``halops.dense_gemm`` (``halops/gemm/dense_gemm.py:44-135``; host checks of
 ``csrc/kernel/gemm/dense_gemm.cu:23-189``), executed by this package's
-tcgen05 kernel through the C ABI.  Built: the Identity epilogue without bias
-for ``w8a8-mxfp8``, ``w4a4-nvfp4`` and ``w4a4-mxfp4``."""
+tcgen05 kernel through the C ABI.  Built: the Identity and Sigmoid epilogues
+for ``w8a8-mxfp8``, ``w4a4-nvfp4`` and ``w4a4-mxfp4``, with an optional bias
+for ``w8a8-mxfp8``."""
 
 from __future__ import annotations
 
@@ -71,8 +72,12 @@ def dense_gemm(
         sm_count: SMs to use (-1: all).
         mode: ``"w8a8-mxfp8"``, ``"w4a4-mxfp4"`` or ``"w4a4-nvfp4"``.
         use_pdl: launch with programmatic stream serialisation.
-        bias, epilogue (other than Identity), output_sf, situ_*: accepted for
-            signature compatibility; not built, a RuntimeError says so.
+        bias: optional [N] bfloat16 vector, ``w8a8-mxfp8`` only, M a multiple of 256
+            (the reference's rule).
+        epilogue: ``EpilogueOp.Identity`` or ``EpilogueOp.Sigmoid``
+            (``sigmoid(alpha * input @ weight^T + bias)``); ``SituQuant`` with
+            ``output_sf`` / ``situ_*`` is accepted for signature compatibility but
+            not built, a RuntimeError says so.
     """
     _check(
         mode in _native.MODE_IDS,
@@ -135,10 +140,15 @@ def dense_gemm(
         if not mxfp4:
             _check(alpha is not None, "W4A4-nvfp4 mode requires alpha input (per-batch scaling).")
     _check(
-        epilogue == EpilogueOp.Identity,
-        f"Unsupported epilogue {int(epilogue)} for {mode} (only EpilogueOp.Identity is built)",
+        epilogue in (EpilogueOp.Identity, EpilogueOp.Sigmoid),
+        f"Unsupported epilogue {int(epilogue)} for {mode} (EpilogueOp.Identity and EpilogueOp.Sigmoid are built)",
     )
-    _check(bias is None, "the bias epilogue is not built in this library")
+    bias_ptr = None
+    if bias is not None:
+        _check(bias.dtype == torch.bfloat16 and bias.dim() == 1 and bias.numel() == n and bias.is_contiguous(),
+               f"bias must be a contiguous bfloat16 vector of {n} elements")
+        _check(bias.is_cuda, "bias must be a CUDA tensor (this library has no CPU path)")
+        bias_ptr = bias.data_ptr()
     _check(output.dtype == torch.bfloat16, "output must be a bfloat16 tensor")
     _check(input.is_contiguous() and weight.is_contiguous() and sfb.is_contiguous(),
            "input, weight and sfb must be contiguous")
@@ -157,7 +167,7 @@ def dense_gemm(
     stream = torch.cuda.current_stream(input.device).cuda_stream
     _native.call(
         "hq_dense_gemm",
-        input.data_ptr(), weight.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), output.data_ptr(), alpha_ptr,
+        input.data_ptr(), weight.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), output.data_ptr(), bias_ptr, alpha_ptr,
         m, n, k, sfa.numel(), sfb.numel(), output.stride(0) if m > 0 else max(n, 8),
         _native.MODE_IDS[mode], int(epilogue), int(sm_count), int(bool(use_pdl)), dev, stream,
     )

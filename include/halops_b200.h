@@ -33,7 +33,7 @@ enum {
 enum { HQ_DTYPE_BF16 = 0, HQ_DTYPE_FP16 = 1 };
 
 /* Epilogue selector; values of the reference's EpilogueOp
- * (csrc/kernel/gemm/epilogue_op.h:21-28).  Only Identity is implemented. */
+ * (csrc/kernel/gemm/epilogue_op.h:21-28).  Identity and Sigmoid are implemented. */
 enum {
     HQ_EPILOGUE_IDENTITY = 0,
     HQ_EPILOGUE_QUANT = 1,
@@ -85,12 +85,15 @@ int hq_group_wise_quant(const void* input, int64_t ld_elems, int in_dtype,
 /*
  * out[M, N] = bf16(alpha * (A . B^T)) with block-scaled operands.
  * Replaces halops::DenseGemm (csrc/kernel/gemm/dense_gemm.cu:23-189, bound at
- * csrc/common/cpp_extensions.cc:280-286) for EpilogueOp::Identity without bias:
+ * csrc/common/cpp_extensions.cc:280-286) for EpilogueOp::Identity and
+ * EpilogueOp::Sigmoid (out = bf16(sigmoid(alpha * A.B^T + bias))):
  *   a     [M, K] e4m3 or [M, K/2] packed e2m1, row-major contiguous
  *   b     [N, K] / [N, K/2], same encoding
  *   sfa   SfAtom-swizzled scales of A, at least hq_sf_rows(M) * K/g bytes
  *   sfb   SfAtom-swizzled scales of B, at least hq_sf_rows(N) * K/g bytes
  *   out   [M, N] bf16, `ldo` elements between rows (ldo % 8 == 0)
+ *   bias  NULL or [N] bf16, 16-byte aligned; w8a8-mxfp8 only and, as in the
+ *         reference, only with M % 256 == 0 (csrc/kernel/gemm/dense_gemm.cu:96-99)
  *   alpha device pointer to one float: required for nvfp4, must be NULL for
  *         mxfp4, ignored for mxfp8 (csrc/kernel/gemm/dense_gemm.cu:126-164)
  *   sm_count <= 0 uses every SM of the device
@@ -98,7 +101,8 @@ int hq_group_wise_quant(const void* input, int64_t ld_elems, int in_dtype,
  * never written.
  */
 int hq_dense_gemm(const void* a, const void* b, const void* sfa,
-                  const void* sfb, void* out, const float* alpha, int64_t m,
+                  const void* sfb, void* out, const void* bias,
+                  const float* alpha, int64_t m,
                   int64_t n, int64_t k, int64_t sfa_bytes, int64_t sfb_bytes,
                   int64_t ldo, int mode, int epilogue, int sm_count,
                   int use_pdl, int device, void* stream, char* err,

@@ -56,7 +56,7 @@ def test_mode_helpers(native):
 
 def _gemm_rc(native, m, n, k, mode, alpha=None, epilogue=0):
     err = ctypes.create_string_buffer(512)
-    rc = native.lib().hq_dense_gemm(None, None, None, None, None, alpha, m, n, k, 1 << 40, 1 << 40, n,
+    rc = native.lib().hq_dense_gemm(None, None, None, None, None, None, alpha, m, n, k, 1 << 40, 1 << 40, n,
                                     mode, epilogue, -1, 0, 0, None, err, len(err))
     return rc, err.value.decode()
 
@@ -79,7 +79,7 @@ def test_gemm_argument_rules(native):
     assert rc == 1 and "does not take alpha" in msg
     rc, msg = _gemm_rc(native, 128, 256, 512, 2, alpha=None)
     assert rc == 1 and "requires alpha" in msg
-    rc, msg = _gemm_rc(native, 128, 256, 512, 0, epilogue=3)
+    rc, msg = _gemm_rc(native, 128, 256, 512, 0, epilogue=4)
     assert rc == 3 and "Unsupported epilogue" in msg
     rc, msg = _gemm_rc(native, 128, 256, 512, 7)
     assert rc == 1 and "Unsupported mode" in msg

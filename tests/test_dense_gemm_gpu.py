@@ -258,7 +258,7 @@ def test_errors_on_device(hq):
     with pytest.raises(RuntimeError, match="sfb must hold whole 128-row SfAtoms"):
         hq.dense_gemm(x, w, sfa, sfb[:128], out)
     with pytest.raises(RuntimeError, match="Unsupported epilogue"):
-        hq.dense_gemm(x, w, sfa, sfb, out, epilogue=hq.EpilogueOp.Sigmoid)
+        hq.dense_gemm(x, w, sfa, sfb, out, epilogue=hq.EpilogueOp.Quant)
     with pytest.raises(RuntimeError, match="multiple of 256"):
         hq.dense_gemm(x, w, sfa, sfb, out, torch.zeros([256], dtype=torch.bfloat16, device=dev))
 
@@ -283,3 +283,59 @@ def test_every_tile_shape(hq, monkeypatch, tile, mode, m, n, k):
     monkeypatch.delenv("HALOPS_B200_TILE")
     assert torch.equal(out, base), "tiles disagree bitwise"
     _check(out, aq, bq, sfa, sfb, mode, alpha=1.0 if mode == "w4a4-nvfp4" else None)
+
+
+@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4", "w4a4-mxfp4"])
+@pytest.mark.parametrize("m,n,k", [(16, 7168, 4096), (64, 4096, 512), (512, 4096, 1024), (4096, 7168, 2048)],
+                         ids=lambda v: str(v))
+def test_sigmoid_epilogue(hq, mode, m, n, k):
+    """Reference tests/test_dense_gemm.py:215-230: sigmoid of the Identity output,
+    rtol 1e-2 / atol 4e-3; also checked against the oracle's float32 product."""
+    a, b = _rand(m, k, 31), _rand(n, k, 32, "weight")
+    aq, bq, sfa, sfb = _quantize(hq, a, b, mode)
+    alpha = torch.full([1], 0.8, dtype=torch.float32, device="cuda") if mode == "w4a4-nvfp4" else None
+    ref = torch.empty([m, n], dtype=torch.bfloat16, device="cuda")
+    hq.dense_gemm(aq, bq, sfa, sfb, ref, None, alpha, -1, mode)
+    out = torch.empty([m, n], dtype=torch.bfloat16, device="cuda")
+    hq.dense_gemm(aq, bq, sfa, sfb, out, None, alpha, -1, mode, True, hq.EpilogueOp.Sigmoid)
+    assert hq.device_status() == 0
+    torch.testing.assert_close(out.float(), torch.sigmoid(ref.float()), rtol=1e-2, atol=4e-3)
+    if m <= 512:
+        acc = oracle.dequantize(aq, sfa, mode) @ oracle.dequantize(bq, sfb, mode).T
+        want = torch.sigmoid(acc * (0.8 if alpha is not None else 1.0))
+        torch.testing.assert_close(out.float().cpu(), want, rtol=1e-2, atol=4e-3)
+
+
+@pytest.mark.parametrize("m,n,k", [(1024, 4096, 1024), (2048, 7168, 512), (256, 256, 128)], ids=lambda v: str(v))
+@pytest.mark.parametrize("tile", ["", "pair256", "128"])
+def test_bias_and_sigmoid_bias(hq, monkeypatch, m, n, k, tile):
+    """Bias add (bf16 [N]) in the Identity epilogue against the oracle, and the
+    reference's sigmoid-with-bias check (tests/test_dense_gemm.py:233-243)."""
+    if tile and n % int(tile.replace("pair", "")):
+        pytest.skip("tile does not divide N")
+    monkeypatch.setenv("HALOPS_B200_TILE", tile)
+    a, b = _rand(m, k, 33), _rand(n, k, 34)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, "w8a8-mxfp8")
+    bias = torch.rand([n], generator=torch.Generator().manual_seed(35)).to(torch.bfloat16).cuda()
+    ref = torch.empty([m, n], dtype=torch.bfloat16, device="cuda")
+    hq.dense_gemm(aq, bq, sfa, sfb, ref, bias, None, -1, "w8a8-mxfp8")
+    acc = oracle.dequantize(aq, sfa, "w8a8-mxfp8") @ oracle.dequantize(bq, sfb, "w8a8-mxfp8").T
+    want = (acc + bias.float().cpu()).to(torch.bfloat16).float()
+    torch.testing.assert_close(ref.float().cpu(), want, **W8A8_TOL)
+    out = torch.empty([m, n], dtype=torch.bfloat16, device="cuda")
+    hq.dense_gemm(aq, bq, sfa, sfb, out, bias, None, -1, "w8a8-mxfp8", True, hq.EpilogueOp.Sigmoid)
+    assert hq.device_status() == 0
+    torch.testing.assert_close(out.float(), torch.sigmoid(ref.float()), rtol=1e-2, atol=8e-3)
+
+
+def test_bias_rules(hq):
+    a, b = _rand(200, 1024, 36), _rand(1024, 1024, 37)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, "w8a8-mxfp8")
+    out = torch.empty([200, 1024], dtype=torch.bfloat16, device="cuda")
+    bias = torch.zeros([1024], dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="multiple of 256"):
+        hq.dense_gemm(aq, bq, sfa, sfb, out, bias)
+    aq4, bq4, sfa4, sfb4 = _quantize(hq, _rand(256, 1024, 38), b, "w4a4-mxfp4")
+    with pytest.raises(RuntimeError, match="does not support bias"):
+        hq.dense_gemm(aq4, bq4, sfa4, sfb4, torch.empty([256, 1024], dtype=torch.bfloat16, device="cuda"), bias,
+                      None, -1, "w4a4-mxfp4")
