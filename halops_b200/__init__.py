@@ -1,15 +1,15 @@
 """B200-native (sm_100a) block-scaled quantize -> dense GEMM path.
 
-Drop-in for the reference's ``halops.group_wise_quant`` and
-``halops.dense_gemm`` (plus ``interleave_gate_up`` and ``EpilogueOp``): same
+Drop-in for the reference's ``halops.group_wise_quant``, ``halops.dense_gemm``
+and ``halops.rms_norm_quant`` (plus ``interleave_gate_up`` and ``EpilogueOp``): same
 Python signatures, executed by hand-written CUDA/PTX kernels through a C-ABI
 shared library.  There is no CPU path and no fallback.
 """
 
-from .gemm import EpilogueOp, dense_gemm, group_wise_quant, interleave_gate_up
+from .gemm import EpilogueOp, dense_gemm, group_wise_quant, interleave_gate_up, rms_norm_quant
 from ._native import lib_path
 
-__all__ = ["EpilogueOp", "dense_gemm", "group_wise_quant", "interleave_gate_up", "device_status",
+__all__ = ["EpilogueOp", "dense_gemm", "group_wise_quant", "interleave_gate_up", "rms_norm_quant", "device_status",
            "describe_tile", "lib_path"]
 __version__ = "0.1.0"
 

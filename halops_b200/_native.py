@@ -25,6 +25,8 @@ SIGNATURES = {
     "hq_sf_rows": (c_i64, [c_i64]),
     "hq_group_wise_quant": (c_int, [c_void_p, c_i64, c_int, c_i64, c_i64, c_int, c_int, c_int,
                                     c_void_p, c_void_p, c_int, c_void_p, c_char_p, c_size_t]),
+    "hq_rms_norm_quant": (c_int, [c_void_p, c_i64, c_void_p, ctypes.c_float, c_i64, c_i64, c_int, c_int,
+                                  c_void_p, c_void_p, c_int, c_void_p, c_char_p, c_size_t]),
     "hq_dense_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_int, c_int, c_int,
                               c_int, c_void_p, c_char_p, c_size_t]),

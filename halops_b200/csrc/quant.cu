@@ -154,6 +154,85 @@ __device__ __forceinline__ uint32_t e4m3x2(float x, float y) {
     return __nv_cvt_float2_to_fp8x2(make_float2(x, y), __NV_SATFINITE, __NV_E4M3);
 }
 
+// Scale byte and codes of the kEpl = 2 * kWords values one lane holds of a
+// quantisation group (packed two per word): 4 lanes share a 32-element group
+// and reduce its amax with two shuffles, NVFP4 gives a lane a whole 16-element
+// group.  codes[i] holds the two codes of word i: 16 bits (e4m3) or 8 bits
+// (e2m1).  Every lane of the warp must call it.
+template <typename T, int kMode>
+__device__ __forceinline__ uint32_t quantize_piece(
+    const uint32_t (&w)[(kMode == HQ_MODE_W4A4_NVFP4 ? 16 : 8) / 2],
+    uint32_t (&codes)[(kMode == HQ_MODE_W4A4_NVFP4 ? 16 : 8) / 2]) {
+    constexpr bool kNv = kMode == HQ_MODE_W4A4_NVFP4;
+    constexpr bool kFp4 = kMode != HQ_MODE_W8A8_MXFP8;
+    constexpr int kWords = (kNv ? 16 : 8) / 2;
+    using P = Pair<T>;
+    // group amax on the packed 16-bit values (NaN operands are ignored, as fmaxf does)
+    uint32_t mx = w[0] & 0x7fff7fffu;
+#pragma unroll
+    for (int i = 1; i < kWords; ++i) mx = P::max2(mx, w[i] & 0x7fff7fffu);
+    mx = P::max2(mx, __byte_perm(mx, 0, 0x1032));
+    if constexpr (!kNv) {
+        mx = P::max2(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = P::max2(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    }
+    const float amax = fmaxf(P::lo(mx), kAmaxFloor);
+
+    uint32_t sf_byte;
+    float inv;
+    if constexpr (kMode == HQ_MODE_W8A8_MXFP8) {
+        sf_byte = ue8m0_of_amax<0x00600000u, 8>(amax);
+        inv = inv_pow2(sf_byte);
+    } else if constexpr (kMode == HQ_MODE_W4A4_MXFP4) {
+        sf_byte = ue8m0_of_amax<0x00400000u, 2>(amax);
+        inv = inv_pow2(sf_byte);
+    } else {
+        const float s = fminf(fmaxf(__fdiv_rn(amax, kE2m1Max), 0.0f), kE4m3Max);
+        sf_byte = __nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3);
+        // UE4M3 may round a tiny scale to 0: smallest positive code (2^-9)
+        if (sf_byte == 0u) sf_byte = 1u;
+        const float dec = __half2float(__half(__nv_cvt_fp8_to_halfraw(
+            static_cast<__nv_fp8_storage_t>(sf_byte), __NV_E4M3)));
+        inv = __frcp_rn(dec);
+    }
+
+    // The reference clamps every scaled value with fminf(fmaxf(x, -MAX), MAX), which
+    // also turns NaN into -MAX.  Finite values never exceed MAX after scaling (or
+    // saturate in the conversion), so only the NaN rule needs work: NaN is replaced
+    // by -inf in the packed input, which scales to -inf and saturates to -MAX.  A
+    // group that holds an infinity has inv == 0 (inf * 0 = NaN) and takes the
+    // literal clamp.
+    if (inv != 0.0f) {
+        const float mult = kMode == HQ_MODE_W4A4_MXFP4 ? inv * (1.0f + 1.1920929e-7f) : inv;
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) {
+            const uint32_t g = P::max2(w[i], P::kNegInf2);
+            const float2 x = mul2(P::lo(g), P::hi(g), mult);
+            if constexpr (kMode == HQ_MODE_W8A8_MXFP8) {
+                codes[i] = e4m3x2(x.x, x.y);
+            } else if constexpr (kMode == HQ_MODE_W4A4_MXFP4) {
+                codes[i] = e2m1x2_rne(add_zero2(x)) & 0xffu;
+            } else {
+                codes[i] = e2m1x2_half_away(add_zero2(x)) & 0xffu;
+            }
+        }
+    } else {
+        const float lim = kFp4 ? kE2m1Max : kE4m3Max;
+#pragma unroll
+        for (int i = 0; i < kWords; ++i) {
+            const float a = clamp_sym(__fmul_rn(P::lo(w[i]), inv), lim);
+            const float b = clamp_sym(__fmul_rn(P::hi(w[i]), inv), lim);
+            if constexpr (!kFp4) {
+                codes[i] = e4m3x2(a, b);
+            } else {
+                codes[i] = e2m1x2_half_away(add_zero2(make_float2(a, b))) & 0xffu;
+            }
+        }
+    }
+
+    return sf_byte;
+}
+
 // One warp quantizes kColsPerWarp consecutive elements of one row.  A lane
 // handles kEpl elements per piece: 8 for the 32-element groups (4 lanes per
 // group), 16 for NVFP4 (one lane per group).  Every address is a per-lane base
@@ -195,69 +274,8 @@ __device__ __forceinline__ void quantize_segment(const T* __restrict__ in_row,
             w[4 * h + 2] = raw[p][h].z;
             w[4 * h + 3] = raw[p][h].w;
         }
-        // group amax on the packed 16-bit values (NaN operands are ignored, as fmaxf does)
-        uint32_t mx = w[0] & 0x7fff7fffu;
-#pragma unroll
-        for (int i = 1; i < kWords; ++i) mx = P::max2(mx, w[i] & 0x7fff7fffu);
-        mx = P::max2(mx, __byte_perm(mx, 0, 0x1032));
-        if constexpr (!kNv) {
-            mx = P::max2(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = P::max2(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        }
-        const float amax = fmaxf(P::lo(mx), kAmaxFloor);
-
-        uint32_t sf_byte;
-        float inv;
-        if constexpr (kMode == HQ_MODE_W8A8_MXFP8) {
-            sf_byte = ue8m0_of_amax<0x00600000u, 8>(amax);
-            inv = inv_pow2(sf_byte);
-        } else if constexpr (kMode == HQ_MODE_W4A4_MXFP4) {
-            sf_byte = ue8m0_of_amax<0x00400000u, 2>(amax);
-            inv = inv_pow2(sf_byte);
-        } else {
-            const float s = fminf(fmaxf(__fdiv_rn(amax, kE2m1Max), 0.0f), kE4m3Max);
-            sf_byte = __nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3);
-            // UE4M3 may round a tiny scale to 0: smallest positive code (2^-9)
-            if (sf_byte == 0u) sf_byte = 1u;
-            const float dec = __half2float(__half(__nv_cvt_fp8_to_halfraw(
-                static_cast<__nv_fp8_storage_t>(sf_byte), __NV_E4M3)));
-            inv = __frcp_rn(dec);
-        }
-
-        // The reference clamps every scaled value with fminf(fmaxf(x, -MAX), MAX), which
-        // also turns NaN into -MAX.  Finite values never exceed MAX after scaling (or
-        // saturate in the conversion), so only the NaN rule needs work: NaN is replaced
-        // by -inf in the packed input, which scales to -inf and saturates to -MAX.  A
-        // group that holds an infinity has inv == 0 (inf * 0 = NaN) and takes the
-        // literal clamp.
         uint32_t codes[kWords];
-        if (inv != 0.0f) {
-            const float mult = kMode == HQ_MODE_W4A4_MXFP4 ? inv * (1.0f + 1.1920929e-7f) : inv;
-#pragma unroll
-            for (int i = 0; i < kWords; ++i) {
-                const uint32_t g = P::max2(w[i], P::kNegInf2);
-                const float2 x = mul2(P::lo(g), P::hi(g), mult);
-                if constexpr (kMode == HQ_MODE_W8A8_MXFP8) {
-                    codes[i] = e4m3x2(x.x, x.y);
-                } else if constexpr (kMode == HQ_MODE_W4A4_MXFP4) {
-                    codes[i] = e2m1x2_rne(add_zero2(x)) & 0xffu;
-                } else {
-                    codes[i] = e2m1x2_half_away(add_zero2(x)) & 0xffu;
-                }
-            }
-        } else {
-            const float lim = kFp4 ? kE2m1Max : kE4m3Max;
-#pragma unroll
-            for (int i = 0; i < kWords; ++i) {
-                const float a = clamp_sym(__fmul_rn(P::lo(w[i]), inv), lim);
-                const float b = clamp_sym(__fmul_rn(P::hi(w[i]), inv), lim);
-                if constexpr (!kFp4) {
-                    codes[i] = e4m3x2(a, b);
-                } else {
-                    codes[i] = e2m1x2_half_away(add_zero2(make_float2(a, b))) & 0xffu;
-                }
-            }
-        }
+        const uint32_t sf_byte = quantize_piece<T, kMode>(w, codes);
 
         if constexpr (!kFp4) {
             // 4 x (2 codes in 16 bits) -> 2 words; 8 bytes per lane and piece
@@ -353,6 +371,93 @@ group_wise_quant_kernel(const T* __restrict__ input, int64_t ld,
         quantize_segment<T, kMode, kSwizzle, true>(in_row, q_row, sf_lane, col0, k, lane);
     } else {
         quantize_segment<T, kMode, kSwizzle, false>(in_row, q_row, sf_lane, col0, k, lane);
+    }
+}
+
+// RMSNorm fused with the MXFP8 quantizer: y = bf16(x * rsqrt(mean(x^2) + eps) * gamma)
+// quantised exactly as group_wise_quant(y) would, reading x once.  Replaces the
+// reference's rms_norm_quant_kernel (csrc/kernel/gemm/rms_norm_quant.cu:44-107):
+// there one thread owns a whole 32-element group; here one CTA owns a row, a lane
+// 8 consecutive elements (coalesced 16-byte loads, the row stays in registers),
+// the sum of squares is reduced by shuffles and one shared-memory pass, and the
+// quantisation is the quantizer's own per-piece code.
+constexpr int kRmsMaxK = 8192;
+
+template <bool kSwizzle>
+__global__ void __launch_bounds__(kRmsMaxK / 8)
+rms_norm_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld,
+                      const __nv_bfloat16* __restrict__ gamma, float eps, int64_t m, int k,
+                      uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
+    __shared__ float warp_sums[kRmsMaxK / 8 / 32];
+    const int64_t row = blockIdx.x;
+    const int t = threadIdx.x;
+    const int lane = t & 31;
+    const int col = t * 8;
+    const bool active = col < k;
+    const int kb_dim = k >> 5;
+
+    uint8_t* sf_lane;
+    if constexpr (kSwizzle) {
+        sf_lane = sf + ((row >> 7) * (kb_dim >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 +
+                  int64_t(col >> 7) * 512;
+    } else {
+        sf_lane = sf + row * int64_t(kb_dim) + (col >> 5);
+    }
+    // gamma does not depend on the producing kernel
+    const uint4 gw = active ? __ldg(reinterpret_cast<const uint4*>(gamma + col)) : make_uint4(0, 0, 0, 0);
+
+    pdl_wait();
+    pdl_launch_dependents();
+
+    if (row >= m) {  // padding rows of the last SfAtom (swizzled layout only)
+        if (kSwizzle && active && (lane & 15) == 0) *reinterpret_cast<uint32_t*>(sf_lane) = 0u;
+        return;
+    }
+
+    const uint4 raw = active ? ld_stream(x + row * ld + col) : make_uint4(0, 0, 0, 0);
+    const uint32_t xw[4] = {raw.x, raw.y, raw.z, raw.w};
+    const uint32_t gws[4] = {gw.x, gw.y, gw.z, gw.w};
+    using P = Pair<__nv_bfloat16>;
+    float v[8];
+    float sum_sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = P::lo(xw[i]);
+        v[2 * i + 1] = P::hi(xw[i]);
+        sum_sq = fmaf(v[2 * i], v[2 * i], sum_sq);
+        sum_sq = fmaf(v[2 * i + 1], v[2 * i + 1], sum_sq);
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) sum_sq += __shfl_xor_sync(0xffffffffu, sum_sq, s);
+    const int warps = blockDim.x >> 5;
+    if (warps > 1) {
+        if (lane == 0) warp_sums[t >> 5] = sum_sq;
+        __syncthreads();
+        sum_sq = 0.0f;
+        for (int i = 0; i < warps; ++i) sum_sq += warp_sums[i];
+    }
+    const float rrms = rsqrtf(sum_sq / float(k) + eps);
+
+    uint32_t yw[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 y = __float22bfloat162_rn(
+            make_float2(v[2 * i] * rrms * P::lo(gws[i]), v[2 * i + 1] * rrms * P::hi(gws[i])));
+        yw[i] = *reinterpret_cast<const uint32_t*>(&y);
+    }
+    uint32_t codes[4];
+    const uint32_t sf_byte = quantize_piece<__nv_bfloat16, HQ_MODE_W8A8_MXFP8>(yw, codes);
+    if (active) {
+        *reinterpret_cast<uint2*>(q + row * int64_t(k) + col) =
+            make_uint2(__byte_perm(codes[0], codes[1], 0x5410), __byte_perm(codes[2], codes[3], 0x5410));
+    }
+    if constexpr (kSwizzle) {
+        uint32_t word = sf_byte;
+        word |= __shfl_down_sync(0xffffffffu, word, 4) << 8;
+        word |= __shfl_down_sync(0xffffffffu, word, 8) << 16;
+        if (active && (lane & 15) == 0) *reinterpret_cast<uint32_t*>(sf_lane) = word;
+    } else {
+        if (active && (lane & 3) == 0) *sf_lane = uint8_t(sf_byte);
     }
 }
 
@@ -464,6 +569,46 @@ extern "C" int hq_group_wise_quant(const void* input, int64_t ld_elems, int in_d
                                               use_swizzle != 0, use_pdl != 0, s)
             : hq::launch_dtype<__half>(input, ld_elems, out_q, out_sf, m, int(k), mode,
                                        use_swizzle != 0, use_pdl != 0, s);
+    HQ_CUDA_TRY(e);
+    return HQ_OK;
+}
+
+extern "C" int hq_rms_norm_quant(const void* input, int64_t ld_elems, const void* weight, float eps,
+                                 int64_t m, int64_t k, int use_swizzle, int use_pdl, void* out_q,
+                                 void* out_sf, int device, void* stream, char* err, size_t errlen) {
+    using hq::fail;
+    if (m < 0 || k <= 0) {
+        return fail(err, errlen, HQ_ERR_INVALID, "input must be a 2D bfloat16 tensor [M, K]");
+    }
+    if (k % 128 != 0 || k > hq::kRmsMaxK) {
+        return fail(err, errlen, HQ_ERR_INVALID, "K must be a multiple of 128 and at most %d, got %lld",
+                    hq::kRmsMaxK, static_cast<long long>(k));
+    }
+    const int64_t rows_total = use_swizzle ? hq_sf_rows(m) : m;
+    if (rows_total == 0) return HQ_OK;
+    if (input == nullptr || weight == nullptr || out_q == nullptr || out_sf == nullptr) {
+        return fail(err, errlen, HQ_ERR_INVALID, "null pointer argument");
+    }
+    if (ld_elems < k || (ld_elems * 2) % 16 != 0 || !hq::aligned(input, 16)) {
+        return fail(err, errlen, HQ_ERR_INVALID, "input rows must be contiguous and 16-byte aligned");
+    }
+    if (!hq::aligned(weight, 16) || !hq::aligned(out_q, 16) || !hq::aligned(out_sf, use_swizzle ? 16 : 1)) {
+        return fail(err, errlen, HQ_ERR_INVALID, "weight, q and sf must be 16-byte aligned");
+    }
+    if (rows_total > INT32_MAX) return fail(err, errlen, HQ_ERR_INVALID, "m is too large for one launch");
+    const hq::DeviceGuard guard(device);
+    if (!guard.ok()) return fail(err, errlen, HQ_ERR_CUDA, "cannot select CUDA device %d", device);
+    const int threads = int((k / 8 + 31) / 32 * 32);
+    const auto* x = static_cast<const __nv_bfloat16*>(input);
+    const auto* g = static_cast<const __nv_bfloat16*>(weight);
+    auto* q = static_cast<uint8_t*>(out_q);
+    auto* sf = static_cast<uint8_t*>(out_sf);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const cudaError_t e =
+        use_swizzle ? hq::launch(hq::rms_norm_quant_kernel<true>, dim3(unsigned(rows_total)), dim3(threads), 0, s,
+                                 use_pdl != 0, 1, x, ld_elems, g, eps, m, int(k), q, sf)
+                    : hq::launch(hq::rms_norm_quant_kernel<false>, dim3(unsigned(rows_total)), dim3(threads), 0, s,
+                                 use_pdl != 0, 1, x, ld_elems, g, eps, m, int(k), q, sf);
     HQ_CUDA_TRY(e);
     return HQ_OK;
 }

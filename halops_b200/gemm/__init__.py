@@ -1,4 +1,5 @@
 from .dense_gemm import EpilogueOp, dense_gemm, interleave_gate_up
 from .group_wise_quant import group_wise_quant
+from .rms_norm_quant import rms_norm_quant
 
-__all__ = ["EpilogueOp", "dense_gemm", "group_wise_quant", "interleave_gate_up"]
+__all__ = ["EpilogueOp", "dense_gemm", "group_wise_quant", "interleave_gate_up", "rms_norm_quant"]

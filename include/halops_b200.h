@@ -83,6 +83,21 @@ int hq_group_wise_quant(const void* input, int64_t ld_elems, int in_dtype,
                         void* stream, char* err, size_t errlen);
 
 /*
+ * RMSNorm fused with the MXFP8 quantizer: y = bf16(x * rsqrt(mean(x^2) + eps) *
+ * weight), quantised as hq_group_wise_quant(y, HQ_MODE_W8A8_MXFP8) would.
+ * Replaces halops::RmsNormQuant (csrc/kernel/gemm/rms_norm_quant.cu:111-155,
+ * bound at csrc/common/cpp_extensions.cc) minus the tensor allocation:
+ *   input   [m, k] bf16, `ld_elems` between rows, rows 16-byte aligned;
+ *           k a multiple of 128 and at most 8192
+ *   weight  [k] bf16 (gamma)
+ *   out_q   [m, k] e4m3 bytes; out_sf as for hq_group_wise_quant
+ */
+int hq_rms_norm_quant(const void* input, int64_t ld_elems, const void* weight,
+                      float eps, int64_t m, int64_t k, int use_swizzle,
+                      int use_pdl, void* out_q, void* out_sf, int device,
+                      void* stream, char* err, size_t errlen);
+
+/*
  * out[M, N] = bf16(alpha * (A . B^T)) with block-scaled operands.
  * Replaces halops::DenseGemm (csrc/kernel/gemm/dense_gemm.cu:23-189, bound at
  * csrc/common/cpp_extensions.cc:280-286) for EpilogueOp::Identity and

@@ -21,6 +21,7 @@ from .quant import (  # noqa: F401
     decode_ue8m0,
     encode_e4m3_rn_satfinite,
     quant_group_wise,
+    rms_norm_ref,
     sf_atom_offsets,
     sf_rows,
     swizzle_sf,

@@ -122,7 +122,7 @@ def ue8m0_from_scale_closed_form(scale: np.ndarray) -> np.ndarray:
     quantizer executes): biased exponent, plus one when the mantissa is
     non-zero or the value is below 1.  Equal to :func:`ue8m0_from_scale` for
     every scale that is ``amax / 448`` or ``amax / 6`` of a bf16 or fp16 amax
-    (checked exhaustively in ``tests/test_oracle_quant.py``)."""
+    (checked exhaustively in ``tests/test_oracle_golden.py``)."""
     s = np.asarray(scale, dtype=np.float32)
     raw = s.view(np.uint32)
     exp = ((raw >> 23) & 0xFF).astype(np.int32)
@@ -264,3 +264,14 @@ def decode_e2m1_packed(packed: np.ndarray) -> np.ndarray:
     codes[:, 1::2] = packed >> 4
     vals = E2M1_VALUES[codes & 7]
     return np.where(codes & 8, -vals, vals).astype(np.float32)
+
+
+def rms_norm_ref(x, weight, eps: float = 1e-6):
+    """fp32 RMSNorm rounded to bf16: ``x * rsqrt(mean(x^2) + eps) * weight``, the
+    reference's ``ref_rms_norm`` (``tests/test_rms_norm_quant.py:36-40``).  Returns
+    a torch bfloat16 tensor."""
+    import torch
+
+    xf = x.detach().to("cpu").float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * weight.detach().to("cpu").float()
+    return y.to(torch.bfloat16)
