@@ -150,6 +150,97 @@ __device__ __forceinline__ uint32_t instr_desc(uint32_t sf_id) {
            (uint32_t(kBM >> 4) << 24) | (sf_id << 29);
 }
 
+// Parameters of the SiTU-GLU quantising epilogue (all zero for the other epilogues).
+struct SituParams {
+    uint8_t* q;       // [M, N/2] e4m3 output
+    uint8_t* sf;      // UE8M0 scales of the output, SfAtom order, kb_out scale columns
+    int64_t ldq;      // bytes between output rows
+    int kb_out;       // N / 2 / 32
+    float beta;       // gate soft-cap
+    float inv_beta;
+    float lin;        // up soft-cap, 0 = none
+    float inv_lin;
+};
+
+__device__ __forceinline__ float tanh_fast(float x) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+    return t;
+}
+
+// 16 SiTU-GLU outputs from one 32-column accumulator chunk whose first 16 columns
+// are gate rows and last 16 the matching up rows (the row order interleave_gate_up
+// produces): bf16(beta tanh(g / beta) sigmoid(g) * lin tanh(u / lin)), or * u when
+// there is no up soft-cap (reference: halops/gemm/dense_gemm.py:100-109,
+// csrc/common/activation.cuh:33-62; the sigmoid here is 0.5 tanh(g / 2) + 0.5).
+__device__ __forceinline__ void situ_chunk(const uint32_t (&r)[32], const __nv_bfloat16* __restrict__ bias_chunk,
+                                           const SituParams& sp, uint32_t* y8) {
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    if (bias_chunk != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(bias_chunk) + j);
+            const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[8 * j + 2 * i] += __uint_as_float(w[i] << 16);
+                v[8 * j + 2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+            }
+        }
+    }
+    float o[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float g = v[i];
+        const float u = v[16 + i];
+        const float gate = sp.beta * tanh_fast(g * sp.inv_beta) * fmaf(0.5f, tanh_fast(0.5f * g), 0.5f);
+        const float up = sp.lin != 0.0f ? sp.lin * tanh_fast(u * sp.inv_lin) : u;
+        o[i] = gate * up;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const __nv_bfloat162 p = __float22bfloat162_rn(make_float2(o[2 * i], o[2 * i + 1]));
+        y8[i] = *reinterpret_cast<const uint32_t*>(&p);
+    }
+}
+
+// MXFP8 quantisation of 32 bf16 values (16 packed words) of one row: UE8M0 byte
+// e = ceil(log2(amax / 448)) + 127 computed exactly on the bf16 bit fields (floor 85),
+// codes = e4m3(v * 2^(127 - e)) with NaN -> -448.  This is the exact-integer recipe of
+// the reference's quantising epilogue (csrc/common/mx_quant.cuh:60-71,
+// csrc/kernel/gemm/epilogue.cuh:990-1010), not the fast-math one of group_wise_quant.
+__device__ __forceinline__ uint32_t quant32_bf16(const uint32_t (&y)[16], uint4& lo, uint4& hi) {
+    uint32_t mx = y[0] & 0x7fff7fffu;
+#pragma unroll
+    for (int i = 1; i < 16; ++i) {
+        uint32_t a = y[i] & 0x7fff7fffu, m2;
+        asm("max.bf16x2 %0, %1, %2;" : "=r"(m2) : "r"(mx), "r"(a));
+        mx = m2;
+    }
+    uint32_t sw = __byte_perm(mx, 0, 0x1032), m2;
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(m2) : "r"(mx), "r"(sw));
+    const uint32_t bits = m2 & 0xffffu;                      // bf16 amax: 8 exponent, 7 mantissa bits
+    const uint32_t exp8 = ((bits + 31u) >> 7) & 0xffu;       // exponent, + 1 when the mantissa exceeds 1.75
+    const uint32_t e = max(exp8, 85u + 8u) - 8u;
+    const float mult = __uint_as_float((254u - e) << 23);
+    uint32_t c[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        uint32_t g;
+        asm("max.bf16x2 %0, %1, %2;" : "=r"(g) : "r"(y[i]), "r"(0xff80ff80u));  // NaN -> -inf -> -448
+        const float a = __uint_as_float(g << 16) * mult;
+        const float b = __uint_as_float(g & 0xffff0000u) * mult;
+        uint16_t h;
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(h) : "f"(a), "f"(b));
+        c[i] = h;
+    }
+    lo = make_uint4(c[0] | (c[1] << 16), c[2] | (c[3] << 16), c[4] | (c[5] << 16), c[6] | (c[7] << 16));
+    hi = make_uint4(c[8] | (c[9] << 16), c[10] | (c[11] << 16), c[12] | (c[13] << 16), c[14] | (c[15] << 16));
+    return e;
+}
+
 // Epilogue math for one 32-column chunk of one accumulator row:
 // y = acc * alpha (+ bias[col]); Identity stores bf16(y), Sigmoid stores
 // bf16(0.5 * tanh.approx(0.5 * y) + 0.5), the reference's formulation
@@ -192,7 +283,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const __grid_constant__ CUtensorMap tm_d, const uint8_t* __restrict__ sfa,
             const uint8_t* __restrict__ sfb, const float* __restrict__ alpha,
             const __nv_bfloat16* __restrict__ bias, int epi_op, __nv_bfloat16* __restrict__ out, int64_t ldo,
-            int M, int N, int k_tiles, int kq_dim, int tiles_m, int tiles_n, int a_rows, int direct_store) {
+            int M, int N, int k_tiles, int kq_dim, int tiles_m, int tiles_n, int a_rows, int direct_store,
+            const SituParams situ) {
     using C = Cfg<BN, KIND>;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle of the operand tiles
@@ -360,6 +452,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             if (!ok) break;
             ptx::tc_fence_after();
             const uint32_t acc = tmem + as * C::kAccStride + (lane_base << 16);
+            if (KIND == 0 && epi_op == HQ_EPILOGUE_SITU_QUANT) {
+                // quantising epilogue: 64 accumulator columns -> one group of 32 e4m3 outputs
+                constexpr int kGroups = C::kChunks / 2;
+#pragma unroll 1
+                for (int gi = 0; gi < kGroups; ++gi) {
+                    const int g = (C::kOverlap != 0 && as == 0) ? kGroups - 1 - gi : gi;
+                    uint32_t r0[32], r1[32];
+                    ptx::tc_load_32x32(acc + (2 * g) * kEpiChunk, r0);
+                    ptx::tc_load_32x32(acc + (2 * g + 1) * kEpiChunk, r1);
+                    ptx::tc_wait_ld();
+                    if (C::kOverlap != 0 && gi == (C::kOverlapChunks - 1) / 2) {
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->overlap_free[as]));
+                    }
+                    if (gi == kGroups - 1) {
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[as]));
+                    }
+                    if (m0 + int(lane_base) >= M) continue;  // this warp's 32 rows are all padding
+                    uint32_t y[16];
+                    const __nv_bfloat16* const bc = bias != nullptr ? bias + n0 + 2 * g * kEpiChunk : nullptr;
+                    situ_chunk(r0, bc, situ, &y[0]);
+                    situ_chunk(r1, bc != nullptr ? bc + kEpiChunk : nullptr, situ, &y[8]);
+                    uint4 lo, hi;
+                    const uint32_t e = quant32_bf16(y, lo, hi);
+                    const int64_t row = m0 + int(lane_base) + lane;
+                    if (row < M) {
+                        const int kb = (n0 >> 6) + g;  // group of 32 output columns
+                        uint4* const dst = reinterpret_cast<uint4*>(situ.q + row * situ.ldq + int64_t(kb) * 32);
+                        dst[0] = lo;
+                        dst[1] = hi;
+                        situ.sf[((row >> 7) * (situ.kb_out >> 2) + (kb >> 2)) * 512 + (row & 31) * 16 +
+                                ((row >> 5) & 3) * 4 + (kb & 3)] = uint8_t(e);
+                    }
+                }
+                continue;
+            }
 #pragma unroll 1
             for (int ci = 0; ci < C::kChunks; ++ci) {
                 // stage 0 shares its highest columns with stage 1, stage 1 its lowest with stage 0
@@ -788,6 +919,7 @@ struct GemmArgs {
     const float* alpha;
     const __nv_bfloat16* bias;
     int epi_op;
+    SituParams situ;
     __nv_bfloat16* out;
     int64_t ldo;
     int m, n;
@@ -822,7 +954,9 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
                      uint64_t(g.k_bytes), kBKBytes, uint32_t(a_rows), CU_TENSOR_MAP_SWIZZLE_128B) &&
         make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes), uint64_t(g.n),
                      uint64_t(g.k_bytes), kBKBytes, BN, CU_TENSOR_MAP_SWIZZLE_128B) &&
-        make_tmap_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out, uint64_t(g.n), uint64_t(g.m),
+        // (the quantising epilogue stores from registers; its map only has to be valid)
+        make_tmap_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out,
+                     uint64_t(g.epi_op == HQ_EPILOGUE_SITU_QUANT ? g.n / 4 : g.n), uint64_t(g.m),
                      uint64_t(g.ldo) * 2, kEpiChunk, 32, CU_TENSOR_MAP_SWIZZLE_64B);
     if (!maps_ok) {
         return fail(err, errlen, HQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the GEMM operands");
@@ -833,7 +967,7 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     const int k_tiles = int(g.k_bytes / kBKBytes);
     HQ_CUDA_TRY(launch(gemm_kernel<BN, KIND>, dim3(grid), dim3(kThreads), size_t(C::kSmemBytes), g.stream,
                        g.pdl, 1, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.bias, g.epi_op, g.out, g.ldo, g.m, g.n, k_tiles,
-                       g.kq_dim, tiles_m, tiles_n, a_rows, g.direct_store ? 1 : 0));
+                       g.kq_dim, tiles_m, tiles_n, a_rows, g.direct_store ? 1 : 0, g.situ));
     return HQ_OK;
 }
 
@@ -1010,24 +1144,33 @@ extern "C" int hq_describe_tile(int64_t m, int64_t n, int64_t k, int mode, int s
     return HQ_OK;
 }
 
-extern "C" int hq_dense_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* out,
-                             const void* bias, const float* alpha, int64_t m, int64_t n, int64_t k, int64_t sfa_bytes,
-                             int64_t sfb_bytes, int64_t ldo, int mode, int epilogue, int sm_count,
-                             int use_pdl, int device, void* stream, char* err, size_t errlen) {
-    using hq::fail;
+namespace hq {
+namespace {
+
+// Shared body of the GEMM entry points.  `situ` is null except for the SiTU-GLU
+// quantising epilogue, whose outputs it names (then `out` / `ldo` are unused).
+int dense_gemm_impl(const void* a, const void* b, const void* sfa, const void* sfb, void* out, const void* bias,
+                    const float* alpha, int64_t m, int64_t n, int64_t k, int64_t sfa_bytes, int64_t sfb_bytes,
+                    int64_t ldo, int mode, int epilogue, const SituParams* situ, int sm_count, int use_pdl,
+                    int device, void* stream, char* err, size_t errlen) {
     const int group = hq_group_size(mode);
     if (group == 0) {
         return fail(err, errlen, HQ_ERR_INVALID,
                     "Unsupported mode: %d. Expected 'w8a8-mxfp8', 'w4a4-mxfp4' or 'w4a4-nvfp4'.", mode);
     }
-    if (epilogue != HQ_EPILOGUE_IDENTITY && epilogue != HQ_EPILOGUE_SIGMOID) {
+    const bool is_situ = epilogue == HQ_EPILOGUE_SITU_QUANT && situ != nullptr;
+    if (epilogue != HQ_EPILOGUE_IDENTITY && epilogue != HQ_EPILOGUE_SIGMOID && !is_situ) {
+        return fail(err, errlen, HQ_ERR_UNSUPPORTED, "Unsupported epilogue %d for %s", epilogue,
+                    hq::mode_name(mode));
+    }
+    if (is_situ && mode != HQ_MODE_W8A8_MXFP8) {
         return fail(err, errlen, HQ_ERR_UNSUPPORTED, "Unsupported epilogue %d for %s", epilogue,
                     hq::mode_name(mode));
     }
     if (bias != nullptr && mode != HQ_MODE_W8A8_MXFP8) {
         return fail(err, errlen, HQ_ERR_INVALID, "W4A4 mode does not support bias yet.");
     }
-    if (bias != nullptr && m % 256 != 0) {
+    if (bias != nullptr && !is_situ && m % 256 != 0) {
         // kept from the reference, whose bias tile has no per-row store predicate
         return fail(err, errlen, HQ_ERR_INVALID,
                     "the bias tile has no per-row store predicate yet, so M must be a multiple of 256 "
@@ -1078,12 +1221,18 @@ extern "C" int hq_dense_gemm(const void* a, const void* b, const void* sfa, cons
     const int sm_all = hq_sm_count(device);
     const int sm = sm_count > 0 ? (sm_count < sm_all || sm_all == 0 ? sm_count : sm_all) : sm_all;
     if (sm <= 0) return fail(err, errlen, HQ_ERR_CUDA, "cannot query the SM count of device %d", device);
-    const hq::TilePick pick = hq::pick_tile(m, n, k, mode, sm);
+    hq::TilePick pick = hq::pick_tile(m, n, k, mode, sm);
+    if (is_situ) {
+        // the quantising epilogue lives in the single-CTA kernel
+        pick.pair = false;
+        out = situ->q;
+        ldo = situ->ldq / 2;
+    }
     if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || out == nullptr) {
         return fail(err, errlen, HQ_ERR_INVALID, "null pointer argument");
     }
     if (!hq::aligned(a, 16) || !hq::aligned(b, 16) || !hq::aligned(sfa, 16) || !hq::aligned(sfb, 16) ||
-        !hq::aligned(out, 16) || ldo < n || ldo % 8 != 0) {
+        !hq::aligned(out, 16) || ldo < (is_situ ? n / 4 : n) || ldo % 8 != 0) {
         return fail(err, errlen, HQ_ERR_INVALID,
                     "operands, scales and output must be 16-byte aligned and the output row stride a "
                     "multiple of 8 elements");
@@ -1097,6 +1246,7 @@ extern "C" int hq_dense_gemm(const void* a, const void* b, const void* sfa, cons
     g.alpha = alpha;
     g.bias = static_cast<const __nv_bfloat16*>(bias);
     g.epi_op = epilogue;
+    g.situ = is_situ ? *situ : hq::SituParams{};
     g.out = static_cast<__nv_bfloat16*>(out);
     g.ldo = ldo;
     g.m = int(m);
@@ -1133,6 +1283,51 @@ extern "C" int hq_dense_gemm(const void* a, const void* b, const void* sfa, cons
         HQ_DISPATCH(2)
     }
 #undef HQ_DISPATCH
+}
+
+}  // namespace
+}  // namespace hq
+
+extern "C" int hq_dense_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* out,
+                             const void* bias, const float* alpha, int64_t m, int64_t n, int64_t k, int64_t sfa_bytes,
+                             int64_t sfb_bytes, int64_t ldo, int mode, int epilogue, int sm_count,
+                             int use_pdl, int device, void* stream, char* err, size_t errlen) {
+    return hq::dense_gemm_impl(a, b, sfa, sfb, out, bias, alpha, m, n, k, sfa_bytes, sfb_bytes, ldo, mode,
+                               epilogue, nullptr, sm_count, use_pdl, device, stream, err, errlen);
+}
+
+extern "C" int hq_dense_gemm_situ_quant(const void* a, const void* b, const void* sfa, const void* sfb,
+                                        void* out_q, void* out_sf, const void* bias, int64_t m, int64_t n,
+                                        int64_t k, int64_t sfa_bytes, int64_t sfb_bytes, int64_t out_sf_bytes,
+                                        float situ_beta, float situ_linear_beta, int sm_count, int use_pdl,
+                                        int device, void* stream, char* err, size_t errlen) {
+    // N / 2 / 32 output scale columns must fill whole SfAtoms (4 columns)
+    if (n % 256 != 0) {
+        return hq::fail(err, errlen, HQ_ERR_INVALID,
+                        "No dense w8a8-mxfp8 tile for M=%lld (grid M=%lld), N=%lld, K=%lld", (long long)m,
+                        (long long)m, (long long)n, (long long)k);
+    }
+    if (!(situ_beta > 0.0f) || situ_linear_beta < 0.0f) {
+        return hq::fail(err, errlen, HQ_ERR_INVALID, "situ_beta must be positive and situ_linear_beta non-negative");
+    }
+    const int64_t kb_out = n / 2 / 32;
+    if (out_q == nullptr || out_sf == nullptr || out_sf_bytes < hq_sf_rows(m) * kb_out) {
+        return hq::fail(err, errlen, HQ_ERR_INVALID,
+                        "output_sf must hold whole 128-row SfAtoms: expected at least %lld bytes, got %lld",
+                        (long long)(hq_sf_rows(m) * kb_out), (long long)out_sf_bytes);
+    }
+    hq::SituParams sp;
+    sp.q = static_cast<uint8_t*>(out_q);
+    sp.sf = static_cast<uint8_t*>(out_sf);
+    sp.ldq = n / 2;
+    sp.kb_out = int(kb_out);
+    sp.beta = situ_beta;
+    sp.inv_beta = 1.0f / situ_beta;
+    sp.lin = situ_linear_beta;
+    sp.inv_lin = situ_linear_beta != 0.0f ? 1.0f / situ_linear_beta : 0.0f;
+    return hq::dense_gemm_impl(a, b, sfa, sfb, out_q, bias, nullptr, m, n, k, sfa_bytes, sfb_bytes, n / 4,
+                               HQ_MODE_W8A8_MXFP8, HQ_EPILOGUE_SITU_QUANT, &sp, sm_count, use_pdl, device, stream,
+                               err, errlen);
 }
 
 extern "C" int hq_device_status(int device, void* stream, uint32_t* status, char* err, size_t errlen) {

@@ -2,8 +2,8 @@
 ``halops.dense_gemm`` (``halops/gemm/dense_gemm.py:44-135``; host checks of
 ``csrc/kernel/gemm/dense_gemm.cu:23-189``), executed by this package's
 tcgen05 kernel through the C ABI.  Built: the Identity and Sigmoid epilogues
-for ``w8a8-mxfp8``, ``w4a4-nvfp4`` and ``w4a4-mxfp4``, with an optional bias
-for ``w8a8-mxfp8``."""
+for ``w8a8-mxfp8``, ``w4a4-nvfp4`` and ``w4a4-mxfp4``, an optional bias and the
+SituQuant (SiTU-GLU + MXFP8 re-quantisation) epilogue for ``w8a8-mxfp8``."""
 
 from __future__ import annotations
 
@@ -74,10 +74,16 @@ def dense_gemm(
         use_pdl: launch with programmatic stream serialisation.
         bias: optional [N] bfloat16 vector, ``w8a8-mxfp8`` only, M a multiple of 256
             (the reference's rule).
-        epilogue: ``EpilogueOp.Identity`` or ``EpilogueOp.Sigmoid``
-            (``sigmoid(alpha * input @ weight^T + bias)``); ``SituQuant`` with
-            ``output_sf`` / ``situ_*`` is accepted for signature compatibility but
-            not built, a RuntimeError says so.
+        epilogue: ``EpilogueOp.Identity``, ``EpilogueOp.Sigmoid``
+            (``sigmoid(alpha * input @ weight^T + bias)``) or ``EpilogueOp.SituQuant``
+            (``w8a8-mxfp8`` SiTU-GLU: with ``y = input @ weight^T + bias`` and the
+            ``[gate; up]`` rows of weight, sfb and bias reordered by ``interleave_gate_up``,
+            ``output`` [M, N/2] float8_e4m3fn holds ``situ_beta * tanh(gate / situ_beta) *
+            sigmoid(gate) * situ_linear_beta * tanh(up / situ_linear_beta)`` (``up`` as is
+            when ``situ_linear_beta`` is None) with UE8M0 scales per 32 columns in
+            ``output_sf``).
+        output_sf: SfAtom scales of the quantised output ([ceil(M/128)*128, N/64] uint8).
+        situ_beta / situ_linear_beta: gate and up soft-caps.
     """
     _check(
         mode in _native.MODE_IDS,
@@ -140,8 +146,8 @@ def dense_gemm(
         if not mxfp4:
             _check(alpha is not None, "W4A4-nvfp4 mode requires alpha input (per-batch scaling).")
     _check(
-        epilogue in (EpilogueOp.Identity, EpilogueOp.Sigmoid),
-        f"Unsupported epilogue {int(epilogue)} for {mode} (EpilogueOp.Identity and EpilogueOp.Sigmoid are built)",
+        epilogue in (EpilogueOp.Identity, EpilogueOp.Sigmoid) or (epilogue == EpilogueOp.SituQuant and fp8),
+        f"Unsupported epilogue {int(epilogue)} for {mode}",
     )
     bias_ptr = None
     if bias is not None:
@@ -149,6 +155,26 @@ def dense_gemm(
                f"bias must be a contiguous bfloat16 vector of {n} elements")
         _check(bias.is_cuda, "bias must be a CUDA tensor (this library has no CPU path)")
         bias_ptr = bias.data_ptr()
+    if epilogue == EpilogueOp.SituQuant:
+        _check(output.dtype == torch.float8_e4m3fn and output.is_contiguous(),
+               "output must be a contiguous float8_e4m3fn tensor for EpilogueOp.SituQuant")
+        _check(output_sf is not None and output_sf.dtype == torch.uint8 and output_sf.is_contiguous(),
+               "EpilogueOp.SituQuant needs a contiguous uint8 output_sf")
+        _check(input.is_contiguous() and weight.is_contiguous() and sfb.is_contiguous(),
+               "input, weight and sfb must be contiguous")
+        if m > 0 and n > 0:
+            _native.call("hq_describe_tile", m, n, k, _native.MODE_IDS[mode], 148, -1)
+        for name, t in (("input", input), ("weight", weight), ("sfa", sfa), ("sfb", sfb), ("output", output),
+                        ("output_sf", output_sf)):
+            _check(t.is_cuda, f"{name} must be a CUDA tensor (this library has no CPU path)")
+        _native.call(
+            "hq_dense_gemm_situ_quant",
+            input.data_ptr(), weight.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), output.data_ptr(),
+            output_sf.data_ptr(), bias_ptr, m, n, k, sfa.numel(), sfb.numel(), output_sf.numel(),
+            float(situ_beta), 0.0 if situ_linear_beta is None else float(situ_linear_beta), int(sm_count),
+            int(bool(use_pdl)), input.device.index, torch.cuda.current_stream(input.device).cuda_stream,
+        )
+        return
     _check(output.dtype == torch.bfloat16, "output must be a bfloat16 tensor")
     _check(input.is_contiguous() and weight.is_contiguous() and sfb.is_contiguous(),
            "input, weight and sfb must be contiguous")

@@ -33,7 +33,8 @@ enum {
 enum { HQ_DTYPE_BF16 = 0, HQ_DTYPE_FP16 = 1 };
 
 /* Epilogue selector; values of the reference's EpilogueOp
- * (csrc/kernel/gemm/epilogue_op.h:21-28).  Identity and Sigmoid are implemented. */
+ * (csrc/kernel/gemm/epilogue_op.h:21-28).  Identity, Sigmoid and SituQuant (through
+ * hq_dense_gemm_situ_quant) are implemented. */
 enum {
     HQ_EPILOGUE_IDENTITY = 0,
     HQ_EPILOGUE_QUANT = 1,
@@ -122,6 +123,26 @@ int hq_dense_gemm(const void* a, const void* b, const void* sfa,
                   int64_t ldo, int mode, int epilogue, int sm_count,
                   int use_pdl, int device, void* stream, char* err,
                   size_t errlen);
+
+/*
+ * SiTU-GLU quantising GEMM: with y = A . B^T + bias and the rows of B (and bias)
+ * ordered [16 gate rows, 16 up rows, ...] (the reference's interleave_gate_up),
+ *   out_q[M, N/2] = e4m3( situ_beta tanh(gate / situ_beta) sigmoid(gate)
+ *                         * situ_linear_beta tanh(up / situ_linear_beta) )   (times up
+ * itself when situ_linear_beta == 0), rounded to bf16 and then quantised per 32
+ * output columns with UE8M0 scales written to out_sf in SfAtom order
+ * (hq_sf_rows(M) x N/64 bytes; padding rows are left untouched).
+ * Replaces halops::DenseGemm with EpilogueOp::SituQuant
+ * (csrc/kernel/gemm/dense_gemm.cu:100-125, csrc/kernel/gemm/epilogue.cuh:867-905,990-1051).
+ * MXFP8 operands only; N % 256 == 0 (the output's N/64 scale columns fill whole atoms).
+ */
+int hq_dense_gemm_situ_quant(const void* a, const void* b, const void* sfa,
+                             const void* sfb, void* out_q, void* out_sf,
+                             const void* bias, int64_t m, int64_t n, int64_t k,
+                             int64_t sfa_bytes, int64_t sfb_bytes,
+                             int64_t out_sf_bytes, float situ_beta,
+                             float situ_linear_beta, int sm_count, int use_pdl,
+                             int device, void* stream, char* err, size_t errlen);
 
 /* Number of SMs of `device`, cached per device.
  * Replaces GetSmCount (csrc/kernel/gemm/gemm_utils.h:29-37), whose cache is

@@ -339,3 +339,49 @@ def test_bias_rules(hq):
     with pytest.raises(RuntimeError, match="does not support bias"):
         hq.dense_gemm(aq4, bq4, sfa4, sfb4, torch.empty([256, 1024], dtype=torch.bfloat16, device="cuda"), bias,
                       None, -1, "w4a4-mxfp4")
+
+
+@pytest.mark.parametrize("m, n, k, with_bias, beta, linear_beta", [
+    (16, 8192, 4096, False, 4.0, 25.0), (64, 16384, 1024, False, 4.0, 25.0), (100, 4096, 512, False, 4.0, 25.0),
+    (512, 4096, 1024, False, 4.0, 25.0), (4096, 7168, 2048, False, 4.0, 25.0), (1024, 4096, 1024, True, 4.0, 25.0),
+    (16, 8192, 4096, True, 4.0, 25.0), (100, 4096, 512, True, 4.0, 25.0), (16, 8192, 4096, False, 2.0, None),
+    (512, 4096, 1024, False, 1.0, 8.0), (200, 256, 256, True, 4.0, 25.0)], ids=lambda v: str(v))
+def test_situ_quant_epilogue(hq, m, n, k, with_bias, beta, linear_beta):
+    """SiTU-GLU + MXFP8 re-quantisation (reference tests/test_dense_gemm.py:250-305): the
+    dequantised output is within one e4m3 step of the float32 formula, and every scale
+    is the smallest power of two that keeps its group inside +-448."""
+    g = torch.Generator().manual_seed(41)
+    a, b = _rand(m, k, 41), _rand(n, k, 42, "weight") * 4
+    aq, sfa = hq.group_wise_quant(a.cuda())
+    bq, sfb_unused = hq.group_wise_quant(b.cuda())
+    del sfb_unused
+    bias = torch.randn([n], generator=g).to(torch.bfloat16) if with_bias else None
+    # float32 reference on the dequantised operands, gate = first half of the columns
+    y = oracle.dequantize(aq, sfa, "w8a8-mxfp8") @ oracle.dequantize(*hq.group_wise_quant(b.cuda()), "w8a8-mxfp8").T
+    gate, up = (y + (bias.float() if with_bias else 0)).chunk(2, dim=1)
+    ref = beta * torch.tanh(gate / beta) * torch.sigmoid(gate)
+    ref = ref * (linear_beta * torch.tanh(up / linear_beta) if linear_beta is not None else up)
+    ref = ref.to(torch.bfloat16).float()
+    # kernel inputs: [gate; up] rows interleaved in blocks of 16
+    w_il = hq.interleave_gate_up(b.cuda()).contiguous()
+    wq, sfb = hq.group_wise_quant(w_il)
+    b_il = hq.interleave_gate_up(bias.cuda()).contiguous() if with_bias else None
+    q = torch.empty([m, n // 2], dtype=torch.float8_e4m3fn, device="cuda")
+    kb_out = n // 2 // 32
+    m_sf = (m + 127) // 128 * 128
+    sf = torch.zeros([m_sf * kb_out], dtype=torch.uint8, device="cuda")
+    hq.dense_gemm(aq, wq, sfa, sfb, q, b_il, None, -1, "w8a8-mxfp8", True, hq.EpilogueOp.SituQuant, sf, beta,
+                  linear_beta)
+    assert hq.device_status() == 0
+    sf_log = torch.from_numpy(oracle.unswizzle_sf(sf.cpu().numpy().reshape(m_sf, kb_out), m))
+    scale = torch.exp2(sf_log.float() - 127).repeat_interleave(32, 1)
+    deq = q.float().cpu() * scale
+    err = (deq - ref).abs()
+    assert (err <= ref.abs() * 2 ** -3 + scale * 2 ** -9).all()
+    assert (err.norm() / ref.norm()) < 0.04
+    # scales: smallest power of two >= amax / 448 of what was actually stored, never too small
+    amax = deq.abs().reshape(m, kb_out, 32).amax(-1)
+    s = scale.reshape(m, kb_out, 32)[:, :, 0]
+    assert (amax <= 448 * s).all()
+    nz = ref.abs().reshape(m, kb_out, 32).amax(-1) > 1e-6
+    assert (amax[nz] > 448 * s[nz] / 2 * 0.9).all(), "a scale is a step too large"
