@@ -329,8 +329,11 @@ def run_ours(args):
                       "gbs_alone": quant_bytes / (quant_only_ms * 1e-3) / 1e9,
                       "frac_of_hbm": quant_bytes / (quant_only_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                       "bytes_per_element": 3.03125},
-            "roofline": {"kernel": "gemm_kernel<256, mxfp8>", "bound": "tensor", "achieved": gemm_tflops,
-                         "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak, "traffic": None,
+            "roofline": {"kernel": "gemm_kernel<256, mxfp8> (128x256x128 single-CTA tile)", "bound": "tensor", "achieved": gemm_tflops,
+                         "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
+                         # workload (ncu capture summarised in profiles/gemm_kernel_mxfp8_128x256_c2_ncu.md)
+                         "traffic": 605.2e6, "algorithmic_bytes": 64 * 2**20 * 2 + 4 * 2**20 + 128 * 2**20,
                          "peak_source": f"2 x {peaks['source']} cuBLAS bf16 "
                                         f"({'burst' if timed_seconds < 1.0 else 'sustained'}) as the dense fp8 peak"},
             "e2e": {"value": world * flops_rank / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
@@ -517,7 +520,7 @@ def run_sweep(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -1086,24 +1086,34 @@ TilePick pick_tile(int64_t m, int64_t n, int64_t k, int mode, int sm_count) {
         }
         return {best, false};
     }
+    // Several rows of tiles: waves x time per tile.  The per-k-tile times are measured
+    // on B200 at M = N = K = 8192 (MXFP8; the FP4 kinds move the same bytes per k-tile):
+    // 128x256 0.457 us (404 us total), 256x256 pair 0.53 us (475 us), 128x128 0.35 us
+    // (620 us), 256x128 pair 0.45 us (807 us); 128x64 is extrapolated.  A tile also
+    // pays about one k-tile of fill and drain.
     struct Cand {
         int bn;
         bool pair;
+        double us_per_ktile;
     };
-    // measured on B200 (M=N=K=8192 MXFP8): 128x256 single-CTA 404 us, 256x256 pair 475 us,
-    // 128x128 620 us, 256x128 pair 807 us
-    const Cand order[4] = {{256, false}, {256, true}, {128, false}, {64, false}};
-    int narrowest = 0;
-    for (const Cand& c : order) {
-        if (n % c.bn != 0 || (c.bn == 64 && !fp8)) continue;
-        if (c.pair) {
-            if (m > kBM && tiles_m2 * (n / c.bn) >= sm_count / 2) return {c.bn, true};
-        } else {
-            if (tiles_m * (n / c.bn) >= sm_count) return {c.bn, false};
-            narrowest = c.bn;
+    const Cand cands[5] = {{256, false, 0.457}, {256, true, 0.53}, {128, false, 0.35},
+                           {128, true, 0.45},   {64, false, 0.27}};
+    const double k_tiles = double(k) / (fp8 ? 128.0 : 256.0);
+    TilePick best = {0, false};
+    double best_cost = 0.0;
+    for (const Cand& c : cands) {
+        if (n % c.bn != 0 || (c.bn == 64 && !fp8) || (c.pair && m <= kBM)) continue;
+        const int64_t tiles = (c.pair ? tiles_m2 : tiles_m) * (n / c.bn);
+        const int64_t units = c.pair ? sm_count / 2 : sm_count;
+        if (units < 1) continue;
+        const double waves = double((tiles + units - 1) / units);
+        const double cost = waves * (k_tiles + 1.0) * c.us_per_ktile;
+        if (best.bn == 0 || cost < best_cost * 0.999) {
+            best = {c.bn, c.pair};
+            best_cost = cost;
         }
     }
-    return {narrowest, false};
+    return best;
 }
 
 std::mutex g_sm_mutex;
