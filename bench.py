@@ -515,6 +515,45 @@ def run_sweep(args):
             "quant_b_gbs": round(n * k * q_bpe / qb_us / 1e3, 1),
             "quant_incl_tflops": round(flops / (gemm_us + qa_us + qb_us) / 1e6, 1),
         }), flush=True)
+    run_sweep_next_rows(median_us, dev, peaks)
+
+
+def run_sweep_next_rows(median_us, dev, peaks):
+    """Rows beyond the dense path: rms_norm_quant and the non-Identity epilogues."""
+    import halops_b200 as hq
+
+    for m, k in ((3072, 8192), (16384, 4096), (128, 4096)):
+        g = torch.Generator(device=dev).manual_seed(9)
+        x = (torch.randn([m, k], generator=g, device=dev) * 3).to(torch.bfloat16)
+        w = (torch.rand([k], generator=g, device=dev) + 0.5).to(torch.bfloat16)
+        us = median_us(lambda: hq.rms_norm_quant(x, w, 1e-6, True, False))
+        nbytes = m * k * 3.03125 + k * 2
+        print(json.dumps({"config": "rms_norm_quant", "m": m, "k": k, "us": round(us, 2),
+                          "gbs": round(nbytes / us / 1e3, 1),
+                          "frac_of_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 3)}), flush=True)
+    m, n, k = 4096, 7168, 2048
+    g = torch.Generator(device=dev).manual_seed(10)
+    a = torch.randn([m, k], generator=g, device=dev).to(torch.bfloat16)
+    b = (torch.randn([n, k], generator=g, device=dev) * 0.05).to(torch.bfloat16)
+    bias = torch.rand([n], generator=g, device=dev).to(torch.bfloat16)
+    aq, sfa = hq.group_wise_quant(a)
+    bq, sfb = hq.group_wise_quant(hq.interleave_gate_up(b).contiguous())
+    out = torch.empty([m, n], dtype=torch.bfloat16, device=dev)
+    q = torch.empty([m, n // 2], dtype=torch.float8_e4m3fn, device=dev)
+    sf = torch.zeros([m * n // 64], dtype=torch.uint8, device=dev)
+    flops = 2.0 * m * n * k
+    for label, fn in (
+        ("identity", lambda: hq.dense_gemm(aq, bq, sfa, sfb, out, None, None, -1, MODE, False)),
+        ("bias", lambda: hq.dense_gemm(aq, bq, sfa, sfb, out, bias, None, -1, MODE, False)),
+        ("sigmoid+bias", lambda: hq.dense_gemm(aq, bq, sfa, sfb, out, bias, None, -1, MODE, False,
+                                                 hq.EpilogueOp.Sigmoid)),
+        ("situ_quant", lambda: hq.dense_gemm(aq, bq, sfa, sfb, q, None, None, -1, MODE, False,
+                                               hq.EpilogueOp.SituQuant, sf, 4.0, 25.0)),
+    ):
+        us = median_us(fn)
+        print(json.dumps({"config": f"epilogue {label}", "m": m, "n": n, "k": k, "us": round(us, 2),
+                          "tflops": round(flops / us / 1e6, 1)}), flush=True)
+    assert hq.device_status(dev) == 0
 
 
 def main():

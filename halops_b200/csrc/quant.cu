@@ -383,8 +383,11 @@ group_wise_quant_kernel(const T* __restrict__ input, int64_t ld,
 // quantisation is the quantizer's own per-piece code.
 constexpr int kRmsMaxK = 8192;
 
-template <bool kSwizzle>
-__global__ void __launch_bounds__(kRmsMaxK / 8)
+// kPieces 8-element pieces per thread: piece p of thread t covers columns
+// (p * blockDim.x + t) * 8 .. + 8, so every load instruction of a warp is one
+// contiguous 512-byte run and several rows are in flight per SM.
+template <bool kSwizzle, int kPieces>
+__global__ void __launch_bounds__(kRmsMaxK / 8 / kPieces)
 rms_norm_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld,
                       const __nv_bfloat16* __restrict__ gamma, float eps, int64_t m, int k,
                       uint8_t* __restrict__ q, uint8_t* __restrict__ sf) {
@@ -392,44 +395,58 @@ rms_norm_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld,
     const int64_t row = blockIdx.x;
     const int t = threadIdx.x;
     const int lane = t & 31;
-    const int col = t * 8;
-    const bool active = col < k;
+    const int threads = blockDim.x;
     const int kb_dim = k >> 5;
+    using P = Pair<__nv_bfloat16>;
 
-    uint8_t* sf_lane;
+    uint8_t* sf_row;
     if constexpr (kSwizzle) {
-        sf_lane = sf + ((row >> 7) * (kb_dim >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 +
-                  int64_t(col >> 7) * 512;
+        sf_row = sf + ((row >> 7) * (kb_dim >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4;
     } else {
-        sf_lane = sf + row * int64_t(kb_dim) + (col >> 5);
+        sf_row = sf + row * int64_t(kb_dim);
     }
     // gamma does not depend on the producing kernel
-    const uint4 gw = active ? __ldg(reinterpret_cast<const uint4*>(gamma + col)) : make_uint4(0, 0, 0, 0);
+    uint4 gw[kPieces];
+#pragma unroll
+    for (int p = 0; p < kPieces; ++p) {
+        const int col = (p * threads + t) * 8;
+        gw[p] = col < k ? __ldg(reinterpret_cast<const uint4*>(gamma + col)) : make_uint4(0, 0, 0, 0);
+    }
 
     pdl_wait();
     pdl_launch_dependents();
 
     if (row >= m) {  // padding rows of the last SfAtom (swizzled layout only)
-        if (kSwizzle && active && (lane & 15) == 0) *reinterpret_cast<uint32_t*>(sf_lane) = 0u;
+        if constexpr (kSwizzle) {
+#pragma unroll
+            for (int p = 0; p < kPieces; ++p) {
+                const int col = (p * threads + t) * 8;
+                if (col < k && (lane & 15) == 0) *reinterpret_cast<uint32_t*>(sf_row + int64_t(col >> 7) * 512) = 0u;
+            }
+        }
         return;
     }
 
-    const uint4 raw = active ? ld_stream(x + row * ld + col) : make_uint4(0, 0, 0, 0);
-    const uint32_t xw[4] = {raw.x, raw.y, raw.z, raw.w};
-    const uint32_t gws[4] = {gw.x, gw.y, gw.z, gw.w};
-    using P = Pair<__nv_bfloat16>;
-    float v[8];
+    uint4 raw[kPieces];
     float sum_sq = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        v[2 * i] = P::lo(xw[i]);
-        v[2 * i + 1] = P::hi(xw[i]);
-        sum_sq = fmaf(v[2 * i], v[2 * i], sum_sq);
-        sum_sq = fmaf(v[2 * i + 1], v[2 * i + 1], sum_sq);
+    for (int p = 0; p < kPieces; ++p) {
+        const int col = (p * threads + t) * 8;
+        raw[p] = col < k ? ld_stream(x + row * ld + col) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int p = 0; p < kPieces; ++p) {
+        const uint32_t xw[4] = {raw[p].x, raw[p].y, raw[p].z, raw[p].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float a = P::lo(xw[i]), b = P::hi(xw[i]);
+            sum_sq = fmaf(a, a, sum_sq);
+            sum_sq = fmaf(b, b, sum_sq);
+        }
     }
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) sum_sq += __shfl_xor_sync(0xffffffffu, sum_sq, s);
-    const int warps = blockDim.x >> 5;
+    const int warps = threads >> 5;
     if (warps > 1) {
         if (lane == 0) warp_sums[t >> 5] = sum_sq;
         __syncthreads();
@@ -438,26 +455,33 @@ rms_norm_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld,
     }
     const float rrms = rsqrtf(sum_sq / float(k) + eps);
 
-    uint32_t yw[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const __nv_bfloat162 y = __float22bfloat162_rn(
-            make_float2(v[2 * i] * rrms * P::lo(gws[i]), v[2 * i + 1] * rrms * P::hi(gws[i])));
-        yw[i] = *reinterpret_cast<const uint32_t*>(&y);
-    }
-    uint32_t codes[4];
-    const uint32_t sf_byte = quantize_piece<__nv_bfloat16, HQ_MODE_W8A8_MXFP8>(yw, codes);
-    if (active) {
-        *reinterpret_cast<uint2*>(q + row * int64_t(k) + col) =
-            make_uint2(__byte_perm(codes[0], codes[1], 0x5410), __byte_perm(codes[2], codes[3], 0x5410));
-    }
-    if constexpr (kSwizzle) {
-        uint32_t word = sf_byte;
-        word |= __shfl_down_sync(0xffffffffu, word, 4) << 8;
-        word |= __shfl_down_sync(0xffffffffu, word, 8) << 16;
-        if (active && (lane & 15) == 0) *reinterpret_cast<uint32_t*>(sf_lane) = word;
-    } else {
-        if (active && (lane & 3) == 0) *sf_lane = uint8_t(sf_byte);
+    for (int p = 0; p < kPieces; ++p) {
+        const int col = (p * threads + t) * 8;
+        const bool active = col < k;
+        const uint32_t xw[4] = {raw[p].x, raw[p].y, raw[p].z, raw[p].w};
+        const uint32_t gws[4] = {gw[p].x, gw[p].y, gw[p].z, gw[p].w};
+        uint32_t yw[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 y = __float22bfloat162_rn(
+                make_float2(P::lo(xw[i]) * rrms * P::lo(gws[i]), P::hi(xw[i]) * rrms * P::hi(gws[i])));
+            yw[i] = *reinterpret_cast<const uint32_t*>(&y);
+        }
+        uint32_t codes[4];
+        const uint32_t sf_byte = quantize_piece<__nv_bfloat16, HQ_MODE_W8A8_MXFP8>(yw, codes);
+        if (active) {
+            *reinterpret_cast<uint2*>(q + row * int64_t(k) + col) =
+                make_uint2(__byte_perm(codes[0], codes[1], 0x5410), __byte_perm(codes[2], codes[3], 0x5410));
+        }
+        if constexpr (kSwizzle) {
+            uint32_t word = sf_byte;
+            word |= __shfl_down_sync(0xffffffffu, word, 4) << 8;
+            word |= __shfl_down_sync(0xffffffffu, word, 8) << 16;
+            if (active && (lane & 15) == 0) *reinterpret_cast<uint32_t*>(sf_row + int64_t(col >> 7) * 512) = word;
+        } else {
+            if (active && (lane & 3) == 0) sf_row[col >> 5] = uint8_t(sf_byte);
+        }
     }
 }
 
@@ -598,17 +622,29 @@ extern "C" int hq_rms_norm_quant(const void* input, int64_t ld_elems, const void
     if (rows_total > INT32_MAX) return fail(err, errlen, HQ_ERR_INVALID, "m is too large for one launch");
     const hq::DeviceGuard guard(device);
     if (!guard.ok()) return fail(err, errlen, HQ_ERR_CUDA, "cannot select CUDA device %d", device);
-    const int threads = int((k / 8 + 31) / 32 * 32);
+    // 1, 2 or 4 pieces of 8 elements per thread, at least 128 threads per row when K allows
+    const int pieces = k >= 4096 ? 4 : (k >= 2048 ? 2 : 1);
+    const int threads = int((k / (8 * pieces) + 31) / 32 * 32);
     const auto* x = static_cast<const __nv_bfloat16*>(input);
     const auto* g = static_cast<const __nv_bfloat16*>(weight);
     auto* q = static_cast<uint8_t*>(out_q);
     auto* sf = static_cast<uint8_t*>(out_sf);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const cudaError_t e =
-        use_swizzle ? hq::launch(hq::rms_norm_quant_kernel<true>, dim3(unsigned(rows_total)), dim3(threads), 0, s,
-                                 use_pdl != 0, 1, x, ld_elems, g, eps, m, int(k), q, sf)
-                    : hq::launch(hq::rms_norm_quant_kernel<false>, dim3(unsigned(rows_total)), dim3(threads), 0, s,
-                                 use_pdl != 0, 1, x, ld_elems, g, eps, m, int(k), q, sf);
+    const dim3 grid(static_cast<unsigned>(rows_total));
+    cudaError_t e;
+#define HQ_RMS_LAUNCH(SW, PC)                                                                          \
+    e = hq::launch(hq::rms_norm_quant_kernel<SW, PC>, grid, dim3(threads), 0, s, use_pdl != 0, 1, x, \
+                   ld_elems, g, eps, m, int(k), q, sf)
+    if (use_swizzle) {
+        if (pieces == 4) HQ_RMS_LAUNCH(true, 4);
+        else if (pieces == 2) HQ_RMS_LAUNCH(true, 2);
+        else HQ_RMS_LAUNCH(true, 1);
+    } else {
+        if (pieces == 4) HQ_RMS_LAUNCH(false, 4);
+        else if (pieces == 2) HQ_RMS_LAUNCH(false, 2);
+        else HQ_RMS_LAUNCH(false, 1);
+    }
+#undef HQ_RMS_LAUNCH
     HQ_CUDA_TRY(e);
     return HQ_OK;
 }
