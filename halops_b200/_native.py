@@ -33,6 +33,10 @@ SIGNATURES = {
     "hq_dense_gemm_situ_quant": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, ctypes.c_float, ctypes.c_float,
                                          c_int, c_int, c_int, c_void_p, c_char_p, c_size_t]),
+    "hq_batch_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_int, c_int, c_int,
+                              c_int, c_void_p, c_char_p, c_size_t]),
+    "hq_describe_batch_tile": (c_int, [c_i64, c_i64, c_i64, c_i64, c_int, c_int, c_int, c_char_p, c_size_t]),
     "hq_sm_count": (c_int, [c_int]),
     "hq_device_status": (c_int, [c_int, c_void_p, ctypes.POINTER(ctypes.c_uint32), c_char_p, c_size_t]),
     "hq_describe_tile": (c_int, [c_i64, c_i64, c_i64, c_int, c_int, c_int, c_char_p, c_size_t]),

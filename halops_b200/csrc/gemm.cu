@@ -139,6 +139,43 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles
     return {first_m + r % gsz, r / gsz};
 }
 
+// What one persistent-loop iteration of the single-CTA kernel works on.
+struct Work {
+    int a_row0;    // first row of the A box (and 128 * scale-atom row tile)
+    int b_row0;    // first row of the B box
+    int out_row0;  // output row of accumulator row 0 (negative when the tile starts in the previous batch)
+    int out_col0;  // first output (and bias) column
+    int batch;
+    int sfb_tile;  // 128-row scale atom row of the B box
+    int sfb_shift; // 32-row group of the B box inside that atom (BN = 64 only)
+};
+
+// Dense: tile -> (row tile, column tile) in grouped raster order.
+// Batch (batches > 0): A is [batches * m, K] with scale atoms over the stacked rows, so
+// tiles are cut on 128-row boundaries of the stacked rows; a tile that straddles two
+// batches is worked once per batch with that batch's weight (the reference's rule,
+// csrc/kernel/gemm/gemm_dispatch.cuh:90-93).  `tiles_m` then counts (batch, row tile)
+// pairs and output rows outside [0, m) belong to the neighbouring batch.
+template <int BN>
+__device__ __forceinline__ Work decode_work(int tile, int tiles_m, int tiles_n, int batches, int m, int n) {
+    if (batches == 0) {
+        const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+        return {tc.m * kBM, tc.n * BN, tc.m * kBM, tc.n * BN, 0, (tc.n * BN) / 128, ((tc.n * BN) % 128) / 32};
+    }
+    int pair = tile / tiles_n;
+    const int nt = tile - pair * tiles_n;
+    int b = 0;
+    for (;; ++b) {
+        const int cnt = ((b + 1) * m - 1) / kBM - (b * m) / kBM + 1;
+        if (pair < cnt) break;
+        pair -= cnt;
+    }
+    const int mt = (b * m) / kBM + pair;
+    // each batch's weight scales start on their own 128-row atom
+    return {mt * kBM, b * n + nt * BN, mt * kBM - b * m, b * n + nt * BN, b,
+            b * ((n + 127) / 128) + (nt * BN) / 128, ((nt * BN) % 128) / 32};
+}
+
 template <int BN, int KIND>
 __device__ __forceinline__ uint32_t instr_desc(uint32_t sf_id) {
     // block-scaled instruction descriptor: [4,6) SFB byte id, [7,10) A format,
@@ -284,7 +321,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const uint8_t* __restrict__ sfb, const float* __restrict__ alpha,
             const __nv_bfloat16* __restrict__ bias, int epi_op, __nv_bfloat16* __restrict__ out, int64_t ldo,
             int M, int N, int k_tiles, int kq_dim, int tiles_m, int tiles_n, int a_rows, int direct_store,
-            const SituParams situ) {
+            int batches, const SituParams situ) {
     using C = Cfg<BN, KIND>;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle of the operand tiles
@@ -338,11 +375,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
-                const int m0 = tc.m * kBM;
-                const int n0 = tc.n * BN;
-                const uint8_t* const sfa_row = sfa + int64_t(tc.m) * kq_dim * 512;
-                const uint8_t* const sfb_row = sfb + int64_t(n0 / 128) * kq_dim * 512;
+                const Work wk = decode_work<BN>(tile, tiles_m, tiles_n, batches, M, N);
+                const int m0 = wk.a_row0;
+                const int n0 = wk.b_row0;
+                const uint8_t* const sfa_row = sfa + int64_t(m0 / kBM) * kq_dim * 512;
+                const uint8_t* const sfb_row = sfb + int64_t(wk.sfb_tile) * kq_dim * 512;
                 for (int kt = 0; kt < k_tiles; ++kt, ++it) {
                     const uint32_t s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1u;
@@ -372,7 +409,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             uint32_t t = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++t) {
-                const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+                const Work wk = decode_work<BN>(tile, tiles_m, tiles_n, batches, M, N);
                 const uint32_t as = t & 1u;
                 const uint32_t aph = (t >> 1) & 1u;
                 ok = wait_bar(ptx::smem_u32(&bars->acc_empty[as]), aph ^ 1u, abort, kStatusMma);
@@ -386,7 +423,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 ptx::tc_fence_after();
                 const uint32_t acc = tmem + as * C::kAccStride;
                 // a 64-wide tile uses half of a 128-row scale atom
-                const uint32_t sfb_shift = BN == 64 ? uint32_t((tc.n * BN) % 128) / 32u : 0u;
+                const uint32_t sfb_shift = BN == 64 ? uint32_t(wk.sfb_shift) : 0u;
                 for (int kt = 0; kt < k_tiles; ++kt, ++it) {
                     const uint32_t s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1u;
@@ -438,14 +475,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         // ------------------------------------------------------------ epilogue
         const int ew = warp - 2;                  // staging buffer owner
         const uint32_t lane_base = (warp & 3) * 32;  // tensor-memory lanes this warp may read
-        const float scale = (KIND == 1 && alpha != nullptr) ? __ldg(alpha) : 1.0f;
         uint32_t t = 0;
         uint32_t stores = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++t) {
-            const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
-            const int m0 = tc.m * kBM;
-            const int n0 = tc.n * BN;
+            const Work wk = decode_work<BN>(tile, tiles_m, tiles_n, batches, M, N);
+            const int m0 = wk.out_row0;  // output row of accumulator row 0
+            const int n0 = wk.out_col0;
+            // per-tensor (dense) or per-batch factor of the NVFP4 recipe
+            const float scale = (KIND == 1 && alpha != nullptr) ? __ldg(alpha + wk.batch) : 1.0f;
             const uint32_t as = t & 1u;
             const uint32_t aph = (t >> 1) & 1u;
             ok = wait_bar(ptx::smem_u32(&bars->acc_full[as]), aph, abort, kStatusEpilogue);
@@ -512,9 +550,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 epilogue_chunk(r, p, scale, bias != nullptr ? bias + n0 + c * kEpiChunk : nullptr, epi_op);
                 const int row = m0 + int(lane_base) + lane;
                 const int col = n0 + c * kEpiChunk;
-                if (m0 + int(lane_base) >= M) continue;  // this warp's 32 rows are all padding
-                if (direct_store) {
-                    if (row < M) {
+                // this warp's 32 rows are all padding (or all belong to a neighbouring batch)
+                if (m0 + int(lane_base) >= M || m0 + int(lane_base) + 31 < 0) continue;
+                if (direct_store || batches != 0) {
+                    if (row >= 0 && row < M) {
                         uint4* dst = reinterpret_cast<uint4*>(out + int64_t(row) * ldo + col);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
@@ -922,7 +961,8 @@ struct GemmArgs {
     SituParams situ;
     __nv_bfloat16* out;
     int64_t ldo;
-    int m, n;
+    int m, n;          // batch mode: rows per batch, columns per batch
+    int batches;       // 0 = dense
     int64_t k_bytes;
     int kq_dim;
     int sm_count;
@@ -948,26 +988,35 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     // M < 128: the A box holds only the rows that exist (rounded up to the 8-row
     // swizzle period); the other rows of the shared-memory tile keep stale bytes,
     // which only feed accumulator rows that are never stored
-    const int a_rows = g.m >= kBM ? kBM : (g.m + 7) / 8 * 8;
+    const int64_t rows_a = g.batches > 0 ? int64_t(g.batches) * g.m : g.m;
+    const int64_t rows_b = g.batches > 0 ? int64_t(g.batches) * g.n : g.n;
+    const int a_rows = rows_a >= kBM ? kBM : int((rows_a + 7) / 8 * 8);
     const bool maps_ok =
-        make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.a, uint64_t(g.k_bytes), uint64_t(g.m),
+        make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.a, uint64_t(g.k_bytes), uint64_t(rows_a),
                      uint64_t(g.k_bytes), kBKBytes, uint32_t(a_rows), CU_TENSOR_MAP_SWIZZLE_128B) &&
-        make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes), uint64_t(g.n),
+        make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes), uint64_t(rows_b),
                      uint64_t(g.k_bytes), kBKBytes, BN, CU_TENSOR_MAP_SWIZZLE_128B) &&
         // (the quantising epilogue stores from registers; its map only has to be valid)
         make_tmap_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out,
-                     uint64_t(g.epi_op == HQ_EPILOGUE_SITU_QUANT ? g.n / 4 : g.n), uint64_t(g.m),
+                     uint64_t(g.epi_op == HQ_EPILOGUE_SITU_QUANT ? g.n / 4 : rows_b), uint64_t(g.m),
                      uint64_t(g.ldo) * 2, kEpiChunk, 32, CU_TENSOR_MAP_SWIZZLE_64B);
     if (!maps_ok) {
         return fail(err, errlen, HQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the GEMM operands");
     }
-    const int tiles_m = (g.m + kBM - 1) / kBM;
+    int tiles_m = (g.m + kBM - 1) / kBM;
+    if (g.batches > 0) {
+        // (batch, 128-row tile of the stacked rows) pairs; straddling tiles count once per batch
+        tiles_m = 0;
+        for (int b = 0; b < g.batches; ++b) {
+            tiles_m += int(((int64_t(b) + 1) * g.m - 1) / kBM - (int64_t(b) * g.m) / kBM + 1);
+        }
+    }
     const int tiles_n = g.n / BN;
     const int grid = min(g.sm_count, tiles_m * tiles_n);
     const int k_tiles = int(g.k_bytes / kBKBytes);
     HQ_CUDA_TRY(launch(gemm_kernel<BN, KIND>, dim3(grid), dim3(kThreads), size_t(C::kSmemBytes), g.stream,
                        g.pdl, 1, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.bias, g.epi_op, g.out, g.ldo, g.m, g.n, k_tiles,
-                       g.kq_dim, tiles_m, tiles_n, a_rows, g.direct_store ? 1 : 0, g.situ));
+                       g.kq_dim, tiles_m, tiles_n, a_rows, g.direct_store ? 1 : 0, g.batches, g.situ));
     return HQ_OK;
 }
 
@@ -1261,6 +1310,7 @@ int dense_gemm_impl(const void* a, const void* b, const void* sfa, const void* s
     g.ldo = ldo;
     g.m = int(m);
     g.n = int(n);
+    g.batches = 0;
     g.k_bytes = mode == HQ_MODE_W8A8_MXFP8 ? k : k / 2;
     g.kq_dim = int(sf_k / 4);
     g.sm_count = sm;
@@ -1338,6 +1388,150 @@ extern "C" int hq_dense_gemm_situ_quant(const void* a, const void* b, const void
     return hq::dense_gemm_impl(a, b, sfa, sfb, out_q, bias, nullptr, m, n, k, sfa_bytes, sfb_bytes, n / 4,
                                HQ_MODE_W8A8_MXFP8, HQ_EPILOGUE_SITU_QUANT, &sp, sm_count, use_pdl, device, stream,
                                err, errlen);
+}
+
+namespace hq {
+namespace {
+// Batch mode runs in the single-CTA kernel; the waves are sized by the (batch, row
+// tile) pairs, which exceed the stacked row tiles when tiles straddle batches.
+TilePick pick_tile_batch(int64_t batches, int64_t m, int64_t n, int64_t k, int mode, int sm_count) {
+    const int64_t pad = m % kBM != 0 ? (batches - 1) * kBM : 0;
+    TilePick pick = pick_tile(batches * m + pad, n, k, mode, sm_count);
+    if (pick.pair) {
+        // the forced or modelled pair choice has no batch walk: fall back to the same width
+        pick.pair = false;
+    }
+    return pick;
+}
+}  // namespace
+}  // namespace hq
+
+extern "C" int hq_describe_batch_tile(int64_t batches, int64_t m, int64_t n, int64_t k, int mode, int sm_count,
+                                      int device, char* buf, size_t buflen) {
+    if (hq_group_size(mode) == 0) return hq::fail(buf, buflen, HQ_ERR_INVALID, "Unsupported mode: %d", mode);
+    const int sm = sm_count > 0 ? sm_count : hq_sm_count(device);
+    const hq::TilePick pick = batches > 0 ? hq::pick_tile_batch(batches, m, n, k, mode, sm > 0 ? sm : 148)
+                                          : hq::TilePick{0, false};
+    if (pick.bn == 0) {
+        return hq::fail(buf, buflen, HQ_ERR_INVALID, "No batch %s tile for M=%lld (grid M=%lld), N=%lld, K=%lld",
+                        hq::mode_name(mode), (long long)m, (long long)(batches * m), (long long)n, (long long)k);
+    }
+    if (buf != nullptr && buflen > 0) {
+        snprintf(buf, buflen, "[gemm] mode=batch kind=%s b=%lld m=%lld n=%lld k=%lld sm=%d -> %dx%d/%d pair=0",
+                 hq::mode_name(mode), (long long)batches, (long long)m, (long long)n, (long long)k, sm, hq::kBM,
+                 pick.bn, mode == HQ_MODE_W8A8_MXFP8 ? 128 : 256);
+    }
+    return HQ_OK;
+}
+
+extern "C" int hq_batch_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* out,
+                             const void* bias, const float* alpha, int64_t batches, int64_t m, int64_t n,
+                             int64_t k, int64_t sfa_bytes, int64_t sfb_bytes, int64_t ldo, int mode, int epilogue,
+                             int sm_count, int use_pdl, int device, void* stream, char* err, size_t errlen) {
+    using hq::fail;
+    const int group = hq_group_size(mode);
+    if (group == 0) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "Unsupported mode: %d. Expected 'w8a8-mxfp8', 'w4a4-nvfp4' or 'w4a4-mxfp4'.", mode);
+    }
+    if (batches < 0 || m < 0 || n < 0 || k < 0 || batches * m > INT32_MAX || batches * n > INT32_MAX ||
+        k > INT32_MAX) {
+        return fail(err, errlen, HQ_ERR_INVALID, "input must be a 3D tensor of shape [B, M, K]");
+    }
+    if (epilogue != HQ_EPILOGUE_IDENTITY) {
+        return fail(err, errlen, HQ_ERR_UNSUPPORTED, "Unsupported epilogue %d for %s", epilogue,
+                    hq::mode_name(mode));
+    }
+    if (bias != nullptr && mode != HQ_MODE_W8A8_MXFP8) {
+        return fail(err, errlen, HQ_ERR_INVALID, "W4A4 batch GEMM does not support bias yet.");
+    }
+    if (bias != nullptr && !hq::aligned(bias, 16)) {
+        return fail(err, errlen, HQ_ERR_INVALID, "bias must be 16-byte aligned");
+    }
+    if (mode == HQ_MODE_W4A4_MXFP4 && alpha != nullptr) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "'w4a4-mxfp4' does not take alpha; the per-batch scaling factor is only used by "
+                    "'w4a4-nvfp4'.");
+    }
+    if (mode == HQ_MODE_W4A4_NVFP4 && alpha == nullptr) {
+        return fail(err, errlen, HQ_ERR_INVALID, "W4A4-nvfp4 mode requires alpha input (per-batch scaling).");
+    }
+    if (batches == 0 || m == 0 || n == 0) return HQ_OK;
+    const int64_t grid_m = batches * m;
+    if (hq::pick_tile_batch(batches, m, n, k, mode, 148).bn == 0) {
+        return fail(err, errlen, HQ_ERR_INVALID, "No batch %s tile for M=%lld (grid M=%lld), N=%lld, K=%lld",
+                    hq::mode_name(mode), (long long)m, (long long)grid_m, (long long)n, (long long)k);
+    }
+    const int64_t sf_k = k / group;
+    const int64_t need_a = hq_sf_rows(grid_m) * sf_k;
+    const int64_t need_b = batches * hq_sf_rows(n) * sf_k;
+    if (sfa_bytes < need_a) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "sfa must hold whole 128-row SfAtoms over the stacked rows: expected at least %lld "
+                    "elements (%lld x %lld) for B*M=%lld, got %lld",
+                    (long long)need_a, (long long)hq_sf_rows(grid_m), (long long)sf_k, (long long)grid_m,
+                    (long long)sfa_bytes);
+    }
+    if (sfb_bytes < need_b) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "sfb must hold whole 128-row SfAtoms per batch: expected at least %lld elements "
+                    "(%lld x %lld x %lld) for N=%lld, got %lld",
+                    (long long)need_b, (long long)batches, (long long)hq_sf_rows(n), (long long)sf_k,
+                    (long long)n, (long long)sfb_bytes);
+    }
+    const hq::DeviceGuard guard(device);
+    if (!guard.ok()) return fail(err, errlen, HQ_ERR_CUDA, "cannot select CUDA device %d", device);
+    const int sm_all = hq_sm_count(device);
+    const int sm = sm_count > 0 ? (sm_count < sm_all || sm_all == 0 ? sm_count : sm_all) : sm_all;
+    if (sm <= 0) return fail(err, errlen, HQ_ERR_CUDA, "cannot query the SM count of device %d", device);
+    if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || out == nullptr) {
+        return fail(err, errlen, HQ_ERR_INVALID, "null pointer argument");
+    }
+    if (!hq::aligned(a, 16) || !hq::aligned(b, 16) || !hq::aligned(sfa, 16) || !hq::aligned(sfb, 16) ||
+        !hq::aligned(out, 16) || ldo < batches * n || ldo % 8 != 0) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "operands, scales and output must be 16-byte aligned and the output row stride a "
+                    "multiple of 8 elements");
+    }
+    const hq::TilePick pick = hq::pick_tile_batch(batches, m, n, k, mode, sm);
+
+    hq::GemmArgs g;
+    g.a = a;
+    g.b = b;
+    g.sfa = static_cast<const uint8_t*>(sfa);
+    g.sfb = static_cast<const uint8_t*>(sfb);
+    g.alpha = alpha;
+    g.bias = static_cast<const __nv_bfloat16*>(bias);
+    g.epi_op = epilogue;
+    g.situ = hq::SituParams{};
+    g.out = static_cast<__nv_bfloat16*>(out);
+    g.ldo = ldo;
+    g.m = int(m);
+    g.n = int(n);
+    g.batches = int(batches);
+    g.k_bytes = mode == HQ_MODE_W8A8_MXFP8 ? k : k / 2;
+    g.kq_dim = int(sf_k / 4);
+    g.sm_count = sm;
+    g.pdl = use_pdl != 0;
+    g.direct_store = true;
+    g.stream = static_cast<cudaStream_t>(stream);
+#define HQ_DISPATCH(KIND)                                          \
+    switch (pick.bn) {                                             \
+        case 256:                                                  \
+            return hq::launch_tile<256, KIND>(g, err, errlen);     \
+        case 128:                                                  \
+            return hq::launch_tile<128, KIND>(g, err, errlen);     \
+        default:                                                   \
+            return hq::launch_tile<64, KIND>(g, err, errlen);      \
+    }
+    if (mode == HQ_MODE_W8A8_MXFP8) {
+        HQ_DISPATCH(0)
+    } else if (mode == HQ_MODE_W4A4_NVFP4) {
+        HQ_DISPATCH(1)
+    } else {
+        HQ_DISPATCH(2)
+    }
+#undef HQ_DISPATCH
 }
 
 extern "C" int hq_device_status(int device, void* stream, uint32_t* status, char* err, size_t errlen) {

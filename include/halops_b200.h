@@ -144,6 +144,39 @@ int hq_dense_gemm_situ_quant(const void* a, const void* b, const void* sfa,
                              float situ_linear_beta, int sm_count, int use_pdl,
                              int device, void* stream, char* err, size_t errlen);
 
+/*
+ * Batch GEMM: out[:, b*N:(b+1)*N] = alpha[b] * (A[b] . B[b]^T) + bias[b] for b < batches.
+ * Replaces halops::BatchGemm with EpilogueOp::Identity
+ * (csrc/kernel/gemm/batch_gemm.cu:22-188, bound at csrc/common/cpp_extensions.cc
+ * "batch_gemm"; Python face halops/gemm/batch_gemm.py:27-117).
+ *   a     [batches, M, K] e4m3 bytes or [batches, M, K/2] packed e2m1, contiguous
+ *   b     [batches, N, K] / [batches, N, K/2], contiguous
+ *   sfa   SfAtom-swizzled scales over the STACKED rows [batches * M]: at least
+ *         hq_sf_rows(batches * M) * K/g bytes (what hq_group_wise_quant returns for
+ *         the [batches * M, K] view)
+ *   sfb   per batch its own atoms: batches * hq_sf_rows(N) * K/g bytes
+ *   out   [M, batches * N] bf16, `ldo` elements between rows (ldo % 8 == 0)
+ *   bias  NULL or [batches, N] bf16 (w8a8-mxfp8 only); any M
+ *   alpha NULL or [batches] float on the device: required for nvfp4, must be NULL
+ *         for mxfp4, ignored for mxfp8
+ * A 128-row tile of the stacked rows that straddles two batches is worked once per
+ * batch (csrc/kernel/gemm/gemm_dispatch.cuh:90-93); every output element is written
+ * exactly once.  The quantising epilogues of the reference (Quant, GateMulQuant,
+ * SigmoidGateMulQuant) return HQ_ERR_UNSUPPORTED.
+ */
+int hq_batch_gemm(const void* a, const void* b, const void* sfa, const void* sfb,
+                  void* out, const void* bias, const float* alpha,
+                  int64_t batches, int64_t m, int64_t n, int64_t k,
+                  int64_t sfa_bytes, int64_t sfb_bytes, int64_t ldo, int mode,
+                  int epilogue, int sm_count, int use_pdl, int device,
+                  void* stream, char* err, size_t errlen);
+
+/* hq_describe_tile for the batch GEMM: the tile picked for `batches` problems of
+ * [m, n, k], or the reference's "No batch <mode> tile for M=.. (grid M=..), N=.., K=.."
+ * text (csrc/kernel/gemm/gemm_dispatch.cuh:65-100) with HQ_ERR_INVALID.  Needs no device. */
+int hq_describe_batch_tile(int64_t batches, int64_t m, int64_t n, int64_t k, int mode,
+                           int sm_count, int device, char* buf, size_t buflen);
+
 /* Number of SMs of `device`, cached per device.
  * Replaces GetSmCount (csrc/kernel/gemm/gemm_utils.h:29-37), whose cache is
  * keyed by nothing and so returns the first device's count on every device. */

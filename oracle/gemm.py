@@ -62,3 +62,33 @@ def dense_gemm_ref(a_q, b_q, sfa, sfb, mode: str = "w8a8-mxfp8", alpha: float | 
     if alpha is not None:
         acc = acc * float(alpha)
     return acc.to(out_dtype)
+
+
+def batch_gemm_ref(a_q, b_q, sfa, sfb, mode: str = "w8a8-mxfp8", alpha=None, bias=None,
+                   out_dtype=torch.bfloat16) -> torch.Tensor:
+    """``out[:, b*N:(b+1)*N] = alpha[b] * (dequant(A[b]) @ dequant(B[b])^T) + bias[b]``.
+
+    Follows the reference's ``tests/test_batch_gemm.py:49-100`` (``ref_batch_gemm_fp8`` /
+    ``ref_batch_gemm_fp4``) and the token-major output of ``assert_close_per_batch``
+    there: ``a_q`` [B, M, K or K/2] with ``sfa`` in SfAtom order over the stacked
+    ``B * M`` rows, ``b_q`` [B, N, K or K/2] with ``sfb`` in SfAtom order per batch.
+    The bias is added to the float32 product (the reference model adds it after a
+    bfloat16 rounding; the difference is below the comparison tolerance)."""
+    a_q = _np(a_q)
+    b_q = _np(b_q)
+    batches, m = a_q.shape[0], a_q.shape[1]
+    n = b_q.shape[1]
+    g = GROUP_SIZE[mode]
+    k = a_q.shape[2] * (1 if mode == "w8a8-mxfp8" else 2)
+    a = dequantize(a_q.reshape(batches * m, -1), sfa, mode)
+    sfb = _np(sfb).reshape(batches, -1, k // g)
+    out = torch.empty([m, batches * n], dtype=torch.float32)
+    for b in range(batches):
+        w = dequantize(b_q[b], sfb[b], mode)
+        acc = torch.matmul(a[b * m:(b + 1) * m], w.T)
+        if alpha is not None:
+            acc = acc * float(alpha[b])
+        if bias is not None:
+            acc = acc + bias[b].float().cpu().reshape(1, n)
+        out[:, b * n:(b + 1) * n] = acc
+    return out.to(out_dtype)

@@ -154,6 +154,54 @@ def test_python_wrapper_errors_without_a_device():
         hq.dense_gemm(a, w, sfa, sfb, out)
 
 
+def test_batch_gemm_rules_without_a_device(native):
+    """Host checks of the batch GEMM (texts of the reference's tests/test_batch_gemm.py:313-363,
+    537-590) through the C entry point with null operands and through the Python wrapper."""
+    import halops_b200 as hq
+
+    def rc(batches, m, n, k, mode, alpha=None, bias=None, epilogue=0):
+        err = ctypes.create_string_buffer(512)
+        code = native.lib().hq_batch_gemm(None, None, None, None, None, bias, alpha, batches, m, n, k, 1 << 40,
+                                          1 << 40, batches * n, mode, epilogue, -1, 0, 0, None, err, len(err))
+        return code, err.value.decode()
+
+    fake = ctypes.cast(16, ctypes.c_void_p)
+    code, msg = rc(2, 128, 256, 96, 0)
+    assert code == 1 and "No batch w8a8-mxfp8 tile for M=128 (grid M=256), N=256, K=96" in msg
+    code, msg = rc(2, 128, 256, 256, 2)
+    assert code == 1 and "requires alpha input (per-batch scaling)" in msg
+    code, msg = rc(2, 128, 256, 512, 1, alpha=fake)
+    assert code == 1 and "does not take alpha; the per-batch scaling factor" in msg
+    code, msg = rc(2, 128, 256, 256, 2, alpha=fake, bias=fake)
+    assert code == 1 and "W4A4 batch GEMM does not support bias" in msg
+    code, msg = rc(2, 128, 256, 128, 0, epilogue=1)
+    assert code == 3 and "Unsupported epilogue 1" in msg
+    assert rc(0, 128, 256, 128, 0)[0] == 0 and rc(2, 0, 256, 128, 0)[0] == 0
+    err = ctypes.create_string_buffer(512)
+    assert native.lib().hq_batch_gemm(fake, fake, fake, fake, fake, None, None, 2, 100, 256, 128, 256 * 4 - 1,
+                                      1 << 40, 512, 0, 0, -1, 0, 0, None, err, len(err)) == 1
+    assert b"sfa must hold whole 128-row SfAtoms over the stacked rows" in err.value
+
+    x = torch.empty([2, 128, 128], dtype=torch.float8_e4m3fn)
+    w = torch.empty([2, 256, 128], dtype=torch.float8_e4m3fn)
+    sfa = torch.empty([256, 4], dtype=torch.uint8)
+    sfb = torch.empty([2, 256, 4], dtype=torch.uint8)
+    out = torch.empty([128, 512], dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="input must be a 3D tensor"):
+        hq.batch_gemm(x[0], w, sfa, sfb, out)
+    with pytest.raises(RuntimeError, match="weight batch dim must match input batch dim, got 3"):
+        hq.batch_gemm(x, torch.empty([3, 256, 128], dtype=torch.float8_e4m3fn), sfa, sfb, out)
+    with pytest.raises(RuntimeError, match=re.escape("output must be a 2D tensor of shape [M, B * N]")):
+        hq.batch_gemm(x, w, sfa, sfb, out.view(2, 64, 512))
+    with pytest.raises(RuntimeError, match=re.escape("output shape must be [M, B * N]")):
+        hq.batch_gemm(x, w, sfa, sfb, out[:, :256])
+    with pytest.raises(RuntimeError, match="Unsupported mode: w2a2"):
+        hq.batch_gemm(x, w, sfa, sfb, out, mode="w2a2")
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        hq.batch_gemm(x, w, sfa, sfb, out)
+    assert "mode=batch" in hq.describe_batch_tile(4, 200, 256, 128)
+
+
 def test_enum_and_interleave():
     import halops_b200 as hq
 
