@@ -1,16 +1,27 @@
 """B200-native (sm_100a) block-scaled quantize -> dense GEMM path.
 
 Drop-in for the reference's ``halops.group_wise_quant``, ``halops.dense_gemm``,
-``halops.batch_gemm`` and ``halops.rms_norm_quant`` (plus ``interleave_gate_up`` and ``EpilogueOp``): same
+``halops.batch_gemm``, ``halops.group_masked_gemm``, ``halops.group_contiguous_gemm`` and
+``halops.rms_norm_quant`` (plus ``interleave_gate_up`` and ``EpilogueOp``): same
 Python signatures, executed by hand-written CUDA/PTX kernels through a C-ABI
 shared library.  There is no CPU path and no fallback.
 """
 
-from .gemm import EpilogueOp, batch_gemm, dense_gemm, group_wise_quant, interleave_gate_up, rms_norm_quant
+from .gemm import (
+    EpilogueOp,
+    batch_gemm,
+    dense_gemm,
+    group_contiguous_gemm,
+    group_masked_gemm,
+    group_wise_quant,
+    interleave_gate_up,
+    rms_norm_quant,
+)
 from ._native import lib_path
 
-__all__ = ["EpilogueOp", "batch_gemm", "dense_gemm", "group_wise_quant", "interleave_gate_up", "rms_norm_quant", "device_status",
-           "describe_tile", "describe_batch_tile", "lib_path"]
+__all__ = ["EpilogueOp", "batch_gemm", "dense_gemm", "group_contiguous_gemm", "group_masked_gemm",
+           "group_wise_quant", "interleave_gate_up", "rms_norm_quant", "device_status", "describe_tile",
+           "describe_group_tile", "lib_path"]
 __version__ = "0.1.0"
 
 
@@ -46,17 +57,20 @@ def describe_tile(m: int, n: int, k: int, mode: str = "w8a8-mxfp8", sm_count: in
     return buf.value.decode()
 
 
-def describe_batch_tile(batches: int, m: int, n: int, k: int, mode: str = "w8a8-mxfp8", sm_count: int = -1,
-                        device: int = -1) -> str:
-    """``describe_tile`` for ``batch_gemm``; raises the reference's "No batch ... tile"
-    error for an illegal shape."""
+def describe_group_tile(kind: str, count: int, rows: int, n: int, k: int, mode: str = "w8a8-mxfp8",
+                        total_m: int = -1, sm_count: int = -1, device: int = -1) -> str:
+    """``describe_tile`` for ``batch_gemm`` / ``group_masked_gemm`` / ``group_contiguous_gemm``
+    (``kind`` = "batch", "masked" or "contiguous"; ``rows`` per group, ``total_m`` rows in all,
+    default ``count * rows``); raises the reference's "No <kind> ... tile" error for an
+    illegal shape."""
     import ctypes
 
     from . import _native
 
     buf = ctypes.create_string_buffer(256)
-    rc = _native.lib().hq_describe_batch_tile(batches, m, n, k, _native.MODE_IDS[mode], sm_count, device, buf,
-                                              len(buf))
+    rc = _native.lib().hq_describe_group_tile(
+        {"batch": 1, "masked": 2, "contiguous": 3}[kind], count, rows, count * rows if total_m < 0 else total_m,
+        n, k, _native.MODE_IDS[mode], sm_count, device, buf, len(buf))
     if rc != 0:
         raise RuntimeError(buf.value.decode())
     return buf.value.decode()

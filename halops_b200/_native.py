@@ -36,7 +36,14 @@ SIGNATURES = {
     "hq_batch_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_int, c_int, c_int,
                               c_int, c_void_p, c_char_p, c_size_t]),
-    "hq_describe_batch_tile": (c_int, [c_i64, c_i64, c_i64, c_i64, c_int, c_int, c_int, c_char_p, c_size_t]),
+    "hq_group_masked_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_int, c_int,
+                                     c_int, c_void_p, c_char_p, c_size_t]),
+    "hq_group_contiguous_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_int,
+                                         c_int, c_int, c_void_p, c_char_p, c_size_t]),
+    "hq_describe_group_tile": (c_int, [c_int, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_int, c_int, c_char_p,
+                                       c_size_t]),
     "hq_sm_count": (c_int, [c_int]),
     "hq_device_status": (c_int, [c_int, c_void_p, ctypes.POINTER(ctypes.c_uint32), c_char_p, c_size_t]),
     "hq_describe_tile": (c_int, [c_i64, c_i64, c_i64, c_int, c_int, c_int, c_char_p, c_size_t]),

@@ -139,42 +139,118 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles
     return {first_m + r % gsz, r / gsz};
 }
 
-// What one persistent-loop iteration of the single-CTA kernel works on.
-struct Work {
-    int a_row0;    // first row of the A box (and 128 * scale-atom row tile)
-    int b_row0;    // first row of the B box
-    int out_row0;  // output row of accumulator row 0 (negative when the tile starts in the previous batch)
-    int out_col0;  // first output (and bias) column
-    int batch;
-    int sfb_tile;  // 128-row scale atom row of the B box
-    int sfb_shift; // 32-row group of the B box inside that atom (BN = 64 only)
+// How the rows of A map to weights.  Dense: one weight.  The grouped kinds stack
+// `count` weights [count, N, K] (scales: every weight starts on its own 128-row atom):
+//   batch       A rows [g * rows, (g + 1) * rows) use weight g; out is [rows, count * N]
+//   masked      the same slots, of which only the first table[g] rows are valid;
+//               out is [count * rows, N]
+//   contiguous  row r uses weight table[r] (sorted, every run of equal ids starts on a
+//               multiple of 64 rows); out is [M, N]
+// Follows the reference's four kernel modes (csrc/kernel/gemm/tile_scheduler.cuh:253-297,
+// 393-460, 575-670).
+enum { kGroupDense = 0, kGroupBatch = 1, kGroupMasked = 2, kGroupContiguous = 3 };
+
+struct GroupParams {
+    int kind;
+    int count;         // number of weights
+    int rows;          // rows per batch / padded rows per expert (batch, masked)
+    const int* table;  // masked: valid rows per expert; contiguous: expert of every row
 };
 
-// Dense: tile -> (row tile, column tile) in grouped raster order.
-// Batch (batches > 0): A is [batches * m, K] with scale atoms over the stacked rows, so
-// tiles are cut on 128-row boundaries of the stacked rows; a tile that straddles two
-// batches is worked once per batch with that batch's weight (the reference's rule,
-// csrc/kernel/gemm/gemm_dispatch.cuh:90-93).  `tiles_m` then counts (batch, row tile)
-// pairs and output rows outside [0, m) belong to the neighbouring batch.
+// What one persistent-loop iteration of the single-CTA kernel works on.
+struct Work {
+    int a_row0;     // first row of the A box (and 128 x its scale-atom row)
+    int b_row0;     // first row of the B box in the stacked weights
+    int sfb_tile;   // 128-row scale atom row of the B box
+    int sfb_shift;  // 32-row group of the B box inside that atom (BN = 64 only)
+    int group;      // weight index: selects alpha and the bias row
+    int row_lo;     // accumulator rows [row_lo, row_hi) belong to this item; the others
+    int row_hi;     //   are padding or belong to the neighbouring group
+    int out_row0;   // output row of accumulator row 0 (negative when a batch starts mid-tile)
+    int out_col0;   // first output column
+    int bias_col0;  // first bias element
+};
+
+// The three warp roles walk the same sequence of work items, each with its own copy
+// of this iterator.  Tiles are cut on 128-row boundaries of the stacked A rows (where
+// the scale atoms are); a tile that holds rows of two groups is worked once per group
+// (the reference's rule for batches, csrc/kernel/gemm/gemm_dispatch.cuh:90-93).
 template <int BN>
-__device__ __forceinline__ Work decode_work(int tile, int tiles_m, int tiles_n, int batches, int m, int n) {
-    if (batches == 0) {
-        const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
-        return {tc.m * kBM, tc.n * BN, tc.m * kBM, tc.n * BN, 0, (tc.n * BN) / 128, ((tc.n * BN) % 128) / 32};
+struct WorkIter {
+    GroupParams g;
+    int M, N, tiles_m, tiles_n;
+    int tile;
+    int pass = 0;        // contiguous: second expert of a tile
+    int walk_group = 0;  // batch / masked: group of the last item and the number of
+    int walk_base = 0;   //   (group, row tile) pairs before it
+
+    __device__ WorkIter(const GroupParams& grp, int m, int n, int tm, int tn)
+        : g(grp), M(m), N(n), tiles_m(tm), tiles_n(tn), tile(blockIdx.x) {}
+
+    __device__ __forceinline__ void set_b(Work& w, int group, int nt) const {
+        w.group = group;
+        w.b_row0 = group * N + nt * BN;
+        w.sfb_tile = group * ((N + 127) / 128) + (nt * BN) / 128;
+        w.sfb_shift = ((nt * BN) % 128) / 32;
+        w.bias_col0 = w.b_row0;
     }
-    int pair = tile / tiles_n;
-    const int nt = tile - pair * tiles_n;
-    int b = 0;
-    for (;; ++b) {
-        const int cnt = ((b + 1) * m - 1) / kBM - (b * m) / kBM + 1;
-        if (pair < cnt) break;
-        pair -= cnt;
+
+    __device__ bool next(Work& w) {
+        if (g.kind == kGroupDense || g.kind == kGroupContiguous) {
+            if (tile >= tiles_m * tiles_n) return false;
+            const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+            w.a_row0 = tc.m * kBM;
+            w.out_row0 = w.a_row0;
+            w.out_col0 = tc.n * BN;
+            w.row_lo = 0;
+            w.row_hi = min(kBM, M - w.a_row0);
+            int group = 0;
+            if (g.kind == kGroupContiguous) {
+                const int e0 = __ldg(g.table + w.a_row0);
+                const int e1 = w.a_row0 + 64 < M ? __ldg(g.table + w.a_row0 + 64) : e0;
+                group = min(max(pass != 0 ? e1 : e0, 0), g.count - 1);
+                if (e1 != e0) {
+                    // two experts meet in the middle of this tile: one pass each
+                    if (pass == 0) {
+                        w.row_hi = 64;
+                    } else {
+                        w.row_lo = 64;
+                    }
+                    pass ^= 1;
+                }
+            }
+            set_b(w, group, tc.n);
+            if (pass == 0) tile += gridDim.x;
+            return true;
+        }
+        // batch / masked: item = (group, j-th row tile that holds valid rows of it, n tile)
+        const int pair = tile / tiles_n;
+        const int nt = tile - pair * tiles_n;
+        int first, valid;
+        for (;;) {
+            if (walk_group >= g.count) return false;
+            first = walk_group * g.rows;
+            valid = g.kind == kGroupMasked ? min(max(__ldg(g.table + walk_group), 0), g.rows) : g.rows;
+            const int cnt = valid > 0 ? (first + valid - 1) / kBM - first / kBM + 1 : 0;
+            if (pair < walk_base + cnt) break;
+            walk_base += cnt;
+            ++walk_group;
+        }
+        w.a_row0 = (first / kBM + (pair - walk_base)) * kBM;
+        w.row_lo = max(0, first - w.a_row0);
+        w.row_hi = min(kBM, first + valid - w.a_row0);
+        set_b(w, walk_group, nt);
+        if (g.kind == kGroupBatch) {
+            w.out_row0 = w.a_row0 - first;
+            w.out_col0 = w.b_row0;
+        } else {
+            w.out_row0 = w.a_row0;
+            w.out_col0 = nt * BN;
+        }
+        tile += gridDim.x;
+        return true;
     }
-    const int mt = (b * m) / kBM + pair;
-    // each batch's weight scales start on their own 128-row atom
-    return {mt * kBM, b * n + nt * BN, mt * kBM - b * m, b * n + nt * BN, b,
-            b * ((n + 127) / 128) + (nt * BN) / 128, ((nt * BN) % 128) / 32};
-}
+};
 
 template <int BN, int KIND>
 __device__ __forceinline__ uint32_t instr_desc(uint32_t sf_id) {
@@ -321,7 +397,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const uint8_t* __restrict__ sfb, const float* __restrict__ alpha,
             const __nv_bfloat16* __restrict__ bias, int epi_op, __nv_bfloat16* __restrict__ out, int64_t ldo,
             int M, int N, int k_tiles, int kq_dim, int tiles_m, int tiles_n, int a_rows, int direct_store,
-            int batches, const SituParams situ) {
+            const GroupParams grp, const SituParams situ) {
     using C = Cfg<BN, KIND>;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle of the operand tiles
@@ -338,7 +414,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int num_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
@@ -374,8 +449,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                const Work wk = decode_work<BN>(tile, tiles_m, tiles_n, batches, M, N);
+            WorkIter<BN> work(grp, M, N, tiles_m, tiles_n);
+            Work wk;
+            while (ok && work.next(wk)) {
                 const int m0 = wk.a_row0;
                 const int n0 = wk.b_row0;
                 const uint8_t* const sfa_row = sfa + int64_t(m0 / kBM) * kq_dim * 512;
@@ -408,8 +484,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             uint32_t it = 0;
             uint32_t t = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++t) {
-                const Work wk = decode_work<BN>(tile, tiles_m, tiles_n, batches, M, N);
+            WorkIter<BN> work(grp, M, N, tiles_m, tiles_n);
+            Work wk;
+            for (; ok && work.next(wk); ++t) {
                 const uint32_t as = t & 1u;
                 const uint32_t aph = (t >> 1) & 1u;
                 ok = wait_bar(ptx::smem_u32(&bars->acc_empty[as]), aph ^ 1u, abort, kStatusMma);
@@ -478,12 +555,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         uint32_t t = 0;
         uint32_t stores = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++t) {
-            const Work wk = decode_work<BN>(tile, tiles_m, tiles_n, batches, M, N);
+        WorkIter<BN> work(grp, M, N, tiles_m, tiles_n);
+        Work wk;
+        const int ar = int(lane_base) + lane;  // accumulator row of this thread
+        for (; ok && work.next(wk); ++t) {
             const int m0 = wk.out_row0;  // output row of accumulator row 0
             const int n0 = wk.out_col0;
-            // per-tensor (dense) or per-batch factor of the NVFP4 recipe
-            const float scale = (KIND == 1 && alpha != nullptr) ? __ldg(alpha + wk.batch) : 1.0f;
+            // this warp's 32 rows are all padding or all belong to a neighbouring group
+            const bool warp_idle = int(lane_base) >= wk.row_hi || int(lane_base) + 32 <= wk.row_lo;
+            const bool row_ok = ar >= wk.row_lo && ar < wk.row_hi;
+            // whole tiles go out through TMA stores (a dense tail is clipped by the tensor map)
+            const bool reg_store =
+                direct_store != 0 || wk.row_lo != 0 || (wk.row_hi != kBM && grp.kind != kGroupDense);
+            // per-tensor (dense) or per-group factor of the NVFP4 recipe
+            const float scale = (KIND == 1 && alpha != nullptr) ? __ldg(alpha + wk.group) : 1.0f;
             const uint32_t as = t & 1u;
             const uint32_t aph = (t >> 1) & 1u;
             ok = wait_bar(ptx::smem_u32(&bars->acc_full[as]), aph, abort, kStatusEpilogue);
@@ -510,15 +595,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[as]));
                     }
-                    if (m0 + int(lane_base) >= M) continue;  // this warp's 32 rows are all padding
+                    if (warp_idle) continue;
                     uint32_t y[16];
                     const __nv_bfloat16* const bc = bias != nullptr ? bias + n0 + 2 * g * kEpiChunk : nullptr;
                     situ_chunk(r0, bc, situ, &y[0]);
                     situ_chunk(r1, bc != nullptr ? bc + kEpiChunk : nullptr, situ, &y[8]);
                     uint4 lo, hi;
                     const uint32_t e = quant32_bf16(y, lo, hi);
-                    const int64_t row = m0 + int(lane_base) + lane;
-                    if (row < M) {
+                    const int64_t row = m0 + ar;
+                    if (row_ok) {
                         const int kb = (n0 >> 6) + g;  // group of 32 output columns
                         uint4* const dst = reinterpret_cast<uint4*>(situ.q + row * situ.ldq + int64_t(kb) * 32);
                         dst[0] = lo;
@@ -547,13 +632,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[as]));
                 }
                 uint32_t p[16];
-                epilogue_chunk(r, p, scale, bias != nullptr ? bias + n0 + c * kEpiChunk : nullptr, epi_op);
-                const int row = m0 + int(lane_base) + lane;
+                epilogue_chunk(r, p, scale, bias != nullptr ? bias + wk.bias_col0 + c * kEpiChunk : nullptr,
+                               epi_op);
+                const int row = m0 + ar;
                 const int col = n0 + c * kEpiChunk;
-                // this warp's 32 rows are all padding (or all belong to a neighbouring batch)
-                if (m0 + int(lane_base) >= M || m0 + int(lane_base) + 31 < 0) continue;
-                if (direct_store || batches != 0) {
-                    if (row >= 0 && row < M) {
+                if (warp_idle) continue;
+                if (reg_store) {
+                    if (row_ok) {
                         uint4* dst = reinterpret_cast<uint4*>(out + int64_t(row) * ldo + col);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
@@ -961,8 +1046,8 @@ struct GemmArgs {
     SituParams situ;
     __nv_bfloat16* out;
     int64_t ldo;
-    int m, n;          // batch mode: rows per batch, columns per batch
-    int batches;       // 0 = dense
+    int m, n;          // rows of A (all groups stacked) and columns per weight
+    GroupParams grp;
     int64_t k_bytes;
     int kq_dim;
     int sm_count;
@@ -988,8 +1073,11 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     // M < 128: the A box holds only the rows that exist (rounded up to the 8-row
     // swizzle period); the other rows of the shared-memory tile keep stale bytes,
     // which only feed accumulator rows that are never stored
-    const int64_t rows_a = g.batches > 0 ? int64_t(g.batches) * g.m : g.m;
-    const int64_t rows_b = g.batches > 0 ? int64_t(g.batches) * g.n : g.n;
+    const int64_t rows_a = g.m;
+    const int64_t rows_b = int64_t(g.grp.kind == kGroupDense ? 1 : g.grp.count) * g.n;
+    // output: [rows, count * N] for batches, else [M, N]
+    const int64_t out_rows = g.grp.kind == kGroupBatch ? g.grp.rows : g.m;
+    const int64_t out_cols = g.grp.kind == kGroupBatch ? rows_b : g.n;
     const int a_rows = rows_a >= kBM ? kBM : int((rows_a + 7) / 8 * 8);
     const bool maps_ok =
         make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.a, uint64_t(g.k_bytes), uint64_t(rows_a),
@@ -998,17 +1086,19 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
                      uint64_t(g.k_bytes), kBKBytes, BN, CU_TENSOR_MAP_SWIZZLE_128B) &&
         // (the quantising epilogue stores from registers; its map only has to be valid)
         make_tmap_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out,
-                     uint64_t(g.epi_op == HQ_EPILOGUE_SITU_QUANT ? g.n / 4 : rows_b), uint64_t(g.m),
+                     uint64_t(g.epi_op == HQ_EPILOGUE_SITU_QUANT ? g.n / 4 : out_cols), uint64_t(out_rows),
                      uint64_t(g.ldo) * 2, kEpiChunk, 32, CU_TENSOR_MAP_SWIZZLE_64B);
     if (!maps_ok) {
         return fail(err, errlen, HQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the GEMM operands");
     }
     int tiles_m = (g.m + kBM - 1) / kBM;
-    if (g.batches > 0) {
-        // (batch, 128-row tile of the stacked rows) pairs; straddling tiles count once per batch
+    if (g.grp.kind == kGroupBatch || g.grp.kind == kGroupMasked) {
+        // (group, 128-row tile) pairs; a straddling tile counts once per group.  For the
+        // masked kind this is the upper bound that sizes the grid: the kernel walks the
+        // valid rows only.
         tiles_m = 0;
-        for (int b = 0; b < g.batches; ++b) {
-            tiles_m += int(((int64_t(b) + 1) * g.m - 1) / kBM - (int64_t(b) * g.m) / kBM + 1);
+        for (int b = 0; b < g.grp.count; ++b) {
+            tiles_m += int(((int64_t(b) + 1) * g.grp.rows - 1) / kBM - (int64_t(b) * g.grp.rows) / kBM + 1);
         }
     }
     const int tiles_n = g.n / BN;
@@ -1016,7 +1106,7 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     const int k_tiles = int(g.k_bytes / kBKBytes);
     HQ_CUDA_TRY(launch(gemm_kernel<BN, KIND>, dim3(grid), dim3(kThreads), size_t(C::kSmemBytes), g.stream,
                        g.pdl, 1, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.bias, g.epi_op, g.out, g.ldo, g.m, g.n, k_tiles,
-                       g.kq_dim, tiles_m, tiles_n, a_rows, g.direct_store ? 1 : 0, g.batches, g.situ));
+                       g.kq_dim, tiles_m, tiles_n, a_rows, g.direct_store ? 1 : 0, g.grp, g.situ));
     return HQ_OK;
 }
 
@@ -1310,7 +1400,7 @@ int dense_gemm_impl(const void* a, const void* b, const void* sfa, const void* s
     g.ldo = ldo;
     g.m = int(m);
     g.n = int(n);
-    g.batches = 0;
+    g.grp = hq::GroupParams{hq::kGroupDense, 1, 0, nullptr};
     g.k_bytes = mode == HQ_MODE_W8A8_MXFP8 ? k : k / 2;
     g.kq_dim = int(sf_k / 4);
     g.sm_count = sm;
@@ -1392,110 +1482,112 @@ extern "C" int hq_dense_gemm_situ_quant(const void* a, const void* b, const void
 
 namespace hq {
 namespace {
-// Batch mode runs in the single-CTA kernel; the waves are sized by the (batch, row
-// tile) pairs, which exceed the stacked row tiles when tiles straddle batches.
-TilePick pick_tile_batch(int64_t batches, int64_t m, int64_t n, int64_t k, int mode, int sm_count) {
-    const int64_t pad = m % kBM != 0 ? (batches - 1) * kBM : 0;
-    TilePick pick = pick_tile(batches * m + pad, n, k, mode, sm_count);
-    if (pick.pair) {
-        // the forced or modelled pair choice has no batch walk: fall back to the same width
-        pick.pair = false;
-    }
+
+const char* group_kind_name(int kind) {
+    return kind == kGroupBatch ? "batch" : kind == kGroupMasked ? "masked" : "contiguous";
+}
+
+// The grouped kinds run in the single-CTA kernel.  `rows` = rows per group (batch,
+// masked) or the mean rows per expert (contiguous), `total_m` = all rows of A.  The
+// waves are sized by the (group, row tile) pairs, which exceed the row tiles of the
+// stacked rows when tiles straddle groups.  Batches take any row count (straddling
+// tiles are worked once per batch); the expert kinds want slots / runs that are
+// multiples of 64 rows, the finest granularity of the reference's tiles
+// (csrc/kernel/gemm/gemm_dispatch.cuh:65-100).
+TilePick pick_tile_grouped(int kind, int64_t count, int64_t rows, int64_t total_m, int64_t n, int64_t k, int mode,
+                           int sm_count) {
+    if (count < 1 || rows < 1) return {0, false};
+    if (kind == kGroupMasked && rows % 64 != 0) return {0, false};
+    if (kind == kGroupContiguous && total_m % 64 != 0) return {0, false};
+    const int64_t pad = kind != kGroupContiguous && rows % kBM != 0 ? (count - 1) * kBM : 0;
+    TilePick pick = pick_tile(total_m + pad, n, k, mode, sm_count);
+    pick.pair = false;  // a forced or modelled pair choice falls back to the same width
     return pick;
 }
-}  // namespace
-}  // namespace hq
 
-extern "C" int hq_describe_batch_tile(int64_t batches, int64_t m, int64_t n, int64_t k, int mode, int sm_count,
-                                      int device, char* buf, size_t buflen) {
-    if (hq_group_size(mode) == 0) return hq::fail(buf, buflen, HQ_ERR_INVALID, "Unsupported mode: %d", mode);
-    const int sm = sm_count > 0 ? sm_count : hq_sm_count(device);
-    const hq::TilePick pick = batches > 0 ? hq::pick_tile_batch(batches, m, n, k, mode, sm > 0 ? sm : 148)
-                                          : hq::TilePick{0, false};
-    if (pick.bn == 0) {
-        return hq::fail(buf, buflen, HQ_ERR_INVALID, "No batch %s tile for M=%lld (grid M=%lld), N=%lld, K=%lld",
-                        hq::mode_name(mode), (long long)m, (long long)(batches * m), (long long)n, (long long)k);
-    }
-    if (buf != nullptr && buflen > 0) {
-        snprintf(buf, buflen, "[gemm] mode=batch kind=%s b=%lld m=%lld n=%lld k=%lld sm=%d -> %dx%d/%d pair=0",
-                 hq::mode_name(mode), (long long)batches, (long long)m, (long long)n, (long long)k, sm, hq::kBM,
-                 pick.bn, mode == HQ_MODE_W8A8_MXFP8 ? 128 : 256);
-    }
-    return HQ_OK;
+int no_group_tile(char* err, size_t errlen, int kind, int mode, int64_t rows, int64_t total_m, int64_t n,
+                  int64_t k) {
+    return fail(err, errlen, HQ_ERR_INVALID, "No %s %s tile for M=%lld (grid M=%lld), N=%lld, K=%lld",
+                group_kind_name(kind), mode_name(mode), (long long)rows, (long long)total_m, (long long)n,
+                (long long)k);
 }
 
-extern "C" int hq_batch_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* out,
-                             const void* bias, const float* alpha, int64_t batches, int64_t m, int64_t n,
-                             int64_t k, int64_t sfa_bytes, int64_t sfb_bytes, int64_t ldo, int mode, int epilogue,
-                             int sm_count, int use_pdl, int device, void* stream, char* err, size_t errlen) {
-    using hq::fail;
+// Shared body of the batch / masked / contiguous entry points.
+int grouped_gemm_impl(int kind, const void* a, const void* b, const void* sfa, const void* sfb, void* out,
+                      const void* bias, const float* alpha, const int* table, int64_t count, int64_t rows,
+                      int64_t total_m, int64_t n, int64_t k, int64_t sfa_bytes, int64_t sfb_bytes, int64_t ldo,
+                      int mode, int epilogue, int sm_count, int use_pdl, int device, void* stream, char* err,
+                      size_t errlen) {
+    const bool batch = kind == kGroupBatch;
+    const char* const per = batch ? "per-batch" : "per-expert";
     const int group = hq_group_size(mode);
     if (group == 0) {
         return fail(err, errlen, HQ_ERR_INVALID,
                     "Unsupported mode: %d. Expected 'w8a8-mxfp8', 'w4a4-nvfp4' or 'w4a4-mxfp4'.", mode);
     }
-    if (batches < 0 || m < 0 || n < 0 || k < 0 || batches * m > INT32_MAX || batches * n > INT32_MAX ||
+    if (count < 0 || rows < 0 || total_m < 0 || n < 0 || k < 0 || total_m > INT32_MAX || count * n > INT32_MAX ||
         k > INT32_MAX) {
-        return fail(err, errlen, HQ_ERR_INVALID, "input must be a 3D tensor of shape [B, M, K]");
+        return fail(err, errlen, HQ_ERR_INVALID, "problem sizes must be non-negative and below 2^31");
     }
     if (epilogue != HQ_EPILOGUE_IDENTITY) {
-        return fail(err, errlen, HQ_ERR_UNSUPPORTED, "Unsupported epilogue %d for %s", epilogue,
-                    hq::mode_name(mode));
+        return fail(err, errlen, HQ_ERR_UNSUPPORTED, "Unsupported epilogue %d for %s", epilogue, mode_name(mode));
     }
     if (bias != nullptr && mode != HQ_MODE_W8A8_MXFP8) {
-        return fail(err, errlen, HQ_ERR_INVALID, "W4A4 batch GEMM does not support bias yet.");
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    batch ? "W4A4 batch GEMM does not support bias yet." : "W4A4 mode does not support bias yet.");
     }
-    if (bias != nullptr && !hq::aligned(bias, 16)) {
+    if (bias != nullptr && !aligned(bias, 16)) {
         return fail(err, errlen, HQ_ERR_INVALID, "bias must be 16-byte aligned");
     }
     if (mode == HQ_MODE_W4A4_MXFP4 && alpha != nullptr) {
         return fail(err, errlen, HQ_ERR_INVALID,
-                    "'w4a4-mxfp4' does not take alpha; the per-batch scaling factor is only used by "
-                    "'w4a4-nvfp4'.");
+                    "'w4a4-mxfp4' does not take alpha; the %s scaling factor is only used by 'w4a4-nvfp4'.", per);
     }
     if (mode == HQ_MODE_W4A4_NVFP4 && alpha == nullptr) {
-        return fail(err, errlen, HQ_ERR_INVALID, "W4A4-nvfp4 mode requires alpha input (per-batch scaling).");
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    batch ? "W4A4-nvfp4 mode requires alpha input (per-batch scaling)."
+                          : "W4A4-nvfp4 mode requires alpha input (per-expert scaling factor).");
     }
-    if (batches == 0 || m == 0 || n == 0) return HQ_OK;
-    const int64_t grid_m = batches * m;
-    if (hq::pick_tile_batch(batches, m, n, k, mode, 148).bn == 0) {
-        return fail(err, errlen, HQ_ERR_INVALID, "No batch %s tile for M=%lld (grid M=%lld), N=%lld, K=%lld",
-                    hq::mode_name(mode), (long long)m, (long long)grid_m, (long long)n, (long long)k);
+    if (count == 0 || total_m == 0 || n == 0) return HQ_OK;
+    if (pick_tile_grouped(kind, count, rows, total_m, n, k, mode, 148).bn == 0) {
+        return no_group_tile(err, errlen, kind, mode, rows, total_m, n, k);
     }
     const int64_t sf_k = k / group;
-    const int64_t need_a = hq_sf_rows(grid_m) * sf_k;
-    const int64_t need_b = batches * hq_sf_rows(n) * sf_k;
+    const int64_t need_a = hq_sf_rows(total_m) * sf_k;
+    const int64_t need_b = count * hq_sf_rows(n) * sf_k;
     if (sfa_bytes < need_a) {
         return fail(err, errlen, HQ_ERR_INVALID,
                     "sfa must hold whole 128-row SfAtoms over the stacked rows: expected at least %lld "
-                    "elements (%lld x %lld) for B*M=%lld, got %lld",
-                    (long long)need_a, (long long)hq_sf_rows(grid_m), (long long)sf_k, (long long)grid_m,
+                    "elements (%lld x %lld) for M=%lld, got %lld",
+                    (long long)need_a, (long long)hq_sf_rows(total_m), (long long)sf_k, (long long)total_m,
                     (long long)sfa_bytes);
     }
     if (sfb_bytes < need_b) {
         return fail(err, errlen, HQ_ERR_INVALID,
-                    "sfb must hold whole 128-row SfAtoms per batch: expected at least %lld elements "
+                    "sfb must hold whole 128-row SfAtoms per weight: expected at least %lld elements "
                     "(%lld x %lld x %lld) for N=%lld, got %lld",
-                    (long long)need_b, (long long)batches, (long long)hq_sf_rows(n), (long long)sf_k,
-                    (long long)n, (long long)sfb_bytes);
+                    (long long)need_b, (long long)count, (long long)hq_sf_rows(n), (long long)sf_k, (long long)n,
+                    (long long)sfb_bytes);
     }
-    const hq::DeviceGuard guard(device);
+    const DeviceGuard guard(device);
     if (!guard.ok()) return fail(err, errlen, HQ_ERR_CUDA, "cannot select CUDA device %d", device);
     const int sm_all = hq_sm_count(device);
     const int sm = sm_count > 0 ? (sm_count < sm_all || sm_all == 0 ? sm_count : sm_all) : sm_all;
     if (sm <= 0) return fail(err, errlen, HQ_ERR_CUDA, "cannot query the SM count of device %d", device);
-    if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || out == nullptr) {
+    if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || out == nullptr ||
+        (!batch && table == nullptr)) {
         return fail(err, errlen, HQ_ERR_INVALID, "null pointer argument");
     }
-    if (!hq::aligned(a, 16) || !hq::aligned(b, 16) || !hq::aligned(sfa, 16) || !hq::aligned(sfb, 16) ||
-        !hq::aligned(out, 16) || ldo < batches * n || ldo % 8 != 0) {
+    const int64_t out_cols = batch ? count * n : n;
+    if (!aligned(a, 16) || !aligned(b, 16) || !aligned(sfa, 16) || !aligned(sfb, 16) || !aligned(out, 16) ||
+        !aligned(table, 4) || ldo < out_cols || ldo % 8 != 0) {
         return fail(err, errlen, HQ_ERR_INVALID,
                     "operands, scales and output must be 16-byte aligned and the output row stride a "
                     "multiple of 8 elements");
     }
-    const hq::TilePick pick = hq::pick_tile_batch(batches, m, n, k, mode, sm);
+    const TilePick pick = pick_tile_grouped(kind, count, rows, total_m, n, k, mode, sm);
 
-    hq::GemmArgs g;
+    GemmArgs g;
     g.a = a;
     g.b = b;
     g.sfa = static_cast<const uint8_t*>(sfa);
@@ -1503,26 +1595,26 @@ extern "C" int hq_batch_gemm(const void* a, const void* b, const void* sfa, cons
     g.alpha = alpha;
     g.bias = static_cast<const __nv_bfloat16*>(bias);
     g.epi_op = epilogue;
-    g.situ = hq::SituParams{};
+    g.situ = SituParams{};
     g.out = static_cast<__nv_bfloat16*>(out);
     g.ldo = ldo;
-    g.m = int(m);
+    g.m = int(total_m);
     g.n = int(n);
-    g.batches = int(batches);
+    g.grp = GroupParams{kind, int(count), int(rows), table};
     g.k_bytes = mode == HQ_MODE_W8A8_MXFP8 ? k : k / 2;
     g.kq_dim = int(sf_k / 4);
     g.sm_count = sm;
     g.pdl = use_pdl != 0;
-    g.direct_store = true;
+    g.direct_store = false;
     g.stream = static_cast<cudaStream_t>(stream);
-#define HQ_DISPATCH(KIND)                                          \
-    switch (pick.bn) {                                             \
-        case 256:                                                  \
-            return hq::launch_tile<256, KIND>(g, err, errlen);     \
-        case 128:                                                  \
-            return hq::launch_tile<128, KIND>(g, err, errlen);     \
-        default:                                                   \
-            return hq::launch_tile<64, KIND>(g, err, errlen);      \
+#define HQ_DISPATCH(KIND)                                      \
+    switch (pick.bn) {                                         \
+        case 256:                                              \
+            return launch_tile<256, KIND>(g, err, errlen);     \
+        case 128:                                              \
+            return launch_tile<128, KIND>(g, err, errlen);     \
+        default:                                               \
+            return launch_tile<64, KIND>(g, err, errlen);      \
     }
     if (mode == HQ_MODE_W8A8_MXFP8) {
         HQ_DISPATCH(0)
@@ -1532,6 +1624,65 @@ extern "C" int hq_batch_gemm(const void* a, const void* b, const void* sfa, cons
         HQ_DISPATCH(2)
     }
 #undef HQ_DISPATCH
+}
+
+}  // namespace
+}  // namespace hq
+
+extern "C" int hq_describe_group_tile(int kind, int64_t count, int64_t rows, int64_t total_m, int64_t n, int64_t k,
+                                      int mode, int sm_count, int device, char* buf, size_t buflen) {
+    if (hq_group_size(mode) == 0) return hq::fail(buf, buflen, HQ_ERR_INVALID, "Unsupported mode: %d", mode);
+    if (kind < hq::kGroupBatch || kind > hq::kGroupContiguous) {
+        return hq::fail(buf, buflen, HQ_ERR_INVALID, "Unsupported group kind: %d", kind);
+    }
+    const int sm = sm_count > 0 ? sm_count : hq_sm_count(device);
+    const hq::TilePick pick = hq::pick_tile_grouped(kind, count, rows, total_m, n, k, mode, sm > 0 ? sm : 148);
+    if (pick.bn == 0) return hq::no_group_tile(buf, buflen, kind, mode, rows, total_m, n, k);
+    if (buf != nullptr && buflen > 0) {
+        snprintf(buf, buflen, "[gemm] mode=%s kind=%s groups=%lld m=%lld grid_m=%lld n=%lld k=%lld sm=%d -> %dx%d/%d pair=0",
+                 hq::group_kind_name(kind), hq::mode_name(mode), (long long)count, (long long)rows,
+                 (long long)total_m, (long long)n, (long long)k, sm, hq::kBM, pick.bn,
+                 mode == HQ_MODE_W8A8_MXFP8 ? 128 : 256);
+    }
+    return HQ_OK;
+}
+
+extern "C" int hq_batch_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* out,
+                             const void* bias, const float* alpha, int64_t batches, int64_t m, int64_t n,
+                             int64_t k, int64_t sfa_bytes, int64_t sfb_bytes, int64_t ldo, int mode, int epilogue,
+                             int sm_count, int use_pdl, int device, void* stream, char* err, size_t errlen) {
+    return hq::grouped_gemm_impl(hq::kGroupBatch, a, b, sfa, sfb, out, bias, alpha, nullptr, batches, m,
+                                 batches * m, n, k, sfa_bytes, sfb_bytes, ldo, mode, epilogue, sm_count, use_pdl,
+                                 device, stream, err, errlen);
+}
+
+extern "C" int hq_group_masked_gemm(const void* a, const void* b, const void* sfa, const void* sfb,
+                                    const int32_t* masked_m, void* out, const void* bias, const float* alpha,
+                                    int64_t num_experts, int64_t max_m_per_expert, int64_t n, int64_t k,
+                                    int64_t sfa_bytes, int64_t sfb_bytes, int64_t ldo, int mode, int sm_count,
+                                    int use_pdl, int device, void* stream, char* err, size_t errlen) {
+    if (max_m_per_expert <= 0) {
+        return hq::fail(err, errlen, HQ_ERR_INVALID, "max_m_per_expert must be greater than 0, got %lld",
+                        (long long)max_m_per_expert);
+    }
+    return hq::grouped_gemm_impl(hq::kGroupMasked, a, b, sfa, sfb, out, bias, alpha, masked_m, num_experts,
+                                 max_m_per_expert, num_experts * max_m_per_expert, n, k, sfa_bytes, sfb_bytes,
+                                 ldo, mode, HQ_EPILOGUE_IDENTITY, sm_count, use_pdl, device, stream, err, errlen);
+}
+
+extern "C" int hq_group_contiguous_gemm(const void* a, const void* b, const void* sfa, const void* sfb,
+                                        const int32_t* expert_ids, void* out, const void* bias,
+                                        const float* alpha, int64_t num_experts, int64_t m, int64_t n, int64_t k,
+                                        int64_t sfa_bytes, int64_t sfb_bytes, int64_t ldo, int mode, int sm_count,
+                                        int use_pdl, int device, void* stream, char* err, size_t errlen) {
+    // the reference sizes its tiles by the mean rows per expert (csrc/kernel/gemm/group_contiguous_gemm.cu:80-87)
+    const int64_t rows = num_experts > 0 ? m / num_experts : 0;
+    if (num_experts > 0 && m > 0 && rows == 0) {
+        return hq::no_group_tile(err, errlen, hq::kGroupContiguous, mode, rows, m, n, k);
+    }
+    return hq::grouped_gemm_impl(hq::kGroupContiguous, a, b, sfa, sfb, out, bias, alpha, expert_ids, num_experts,
+                                 rows, m, n, k, sfa_bytes, sfb_bytes, ldo, mode, HQ_EPILOGUE_IDENTITY, sm_count,
+                                 use_pdl, device, stream, err, errlen);
 }
 
 extern "C" int hq_device_status(int device, void* stream, uint32_t* status, char* err, size_t errlen) {

@@ -104,7 +104,7 @@ def batch_gemm(
     if batches == 0 or m == 0 or n == 0:
         return
     # shape legality ("No batch ... tile") is reported before anything touches a device
-    _native.call("hq_describe_batch_tile", batches, m, n, k, _native.MODE_IDS[mode], 148, -1)
+    _native.call("hq_describe_group_tile", 1, batches, m, batches * m, n, k, _native.MODE_IDS[mode], 148, -1)
     bias_ptr = None
     if bias is not None:
         _check(bias.dtype == torch.bfloat16 and bias.numel() == batches * n and bias.is_contiguous(),

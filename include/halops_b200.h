@@ -171,11 +171,60 @@ int hq_batch_gemm(const void* a, const void* b, const void* sfa, const void* sfb
                   int epilogue, int sm_count, int use_pdl, int device,
                   void* stream, char* err, size_t errlen);
 
-/* hq_describe_tile for the batch GEMM: the tile picked for `batches` problems of
- * [m, n, k], or the reference's "No batch <mode> tile for M=.. (grid M=..), N=.., K=.."
- * text (csrc/kernel/gemm/gemm_dispatch.cuh:65-100) with HQ_ERR_INVALID.  Needs no device. */
-int hq_describe_batch_tile(int64_t batches, int64_t m, int64_t n, int64_t k, int mode,
-                           int sm_count, int device, char* buf, size_t buflen);
+/*
+ * Masked grouped GEMM (MoE, padded slots): expert e owns rows
+ * [e * max_m, (e + 1) * max_m) of A and of out, of which the first masked_m[e] are valid:
+ *   out[e * max_m + i, :] = alpha[e] * (A[e * max_m + i, :] . B[e]^T) + bias[e],  i < masked_m[e].
+ * Rows past masked_m[e] are neither computed nor written.
+ * Replaces halops::GroupMaskedGemm (csrc/kernel/gemm/group_masked_gemm.cu:22-186; Python face
+ * halops/gemm/group_masked_gemm.py:25-116; scheduler csrc/kernel/gemm/tile_scheduler.cuh:393-460).
+ *   a [num_experts * max_m, K or K/2], b [num_experts, N, K or K/2], contiguous
+ *   sfa SfAtom scales over all rows of a; sfb per expert its own atoms (as hq_batch_gemm)
+ *   masked_m [num_experts] int32 on the device, read by the kernel (values are clamped to [0, max_m])
+ *   out [num_experts * max_m, N] bf16, `ldo` elements between rows
+ *   bias NULL or [num_experts, N] bf16 (w8a8-mxfp8 only); alpha NULL or [num_experts] float
+ * max_m must be a multiple of 64.  The 'w4a8-mxfp4' mode of the reference is not built.
+ */
+int hq_group_masked_gemm(const void* a, const void* b, const void* sfa,
+                         const void* sfb, const int32_t* masked_m, void* out,
+                         const void* bias, const float* alpha,
+                         int64_t num_experts, int64_t max_m_per_expert,
+                         int64_t n, int64_t k, int64_t sfa_bytes,
+                         int64_t sfb_bytes, int64_t ldo, int mode, int sm_count,
+                         int use_pdl, int device, void* stream, char* err,
+                         size_t errlen);
+
+/*
+ * Contiguous grouped GEMM (MoE, packed rows): row r of A uses weight expert_ids[r]:
+ *   out[r, :] = alpha[e] * (A[r, :] . B[e]^T) + bias[e],  e = expert_ids[r].
+ * Replaces halops::GroupContiguousGemm (csrc/kernel/gemm/group_contiguous_gemm.cu:22-176;
+ * Python face halops/gemm/group_contiguous_gemm.py:25-105; scheduler
+ * csrc/kernel/gemm/tile_scheduler.cuh:575-670, which reads expert_ids at the first row of
+ * each tile).
+ *   expert_ids [M] int32 on the device, non-decreasing; every run of equal ids must
+ *   start on a multiple of 64 rows (the reference wants runs aligned to the tile it
+ *   picks: 64, 128 or 256 rows); ids are clamped to [0, num_experts).  M % 64 == 0.
+ * Other operands as hq_group_masked_gemm with out [M, N].
+ */
+int hq_group_contiguous_gemm(const void* a, const void* b, const void* sfa,
+                             const void* sfb, const int32_t* expert_ids,
+                             void* out, const void* bias, const float* alpha,
+                             int64_t num_experts, int64_t m, int64_t n,
+                             int64_t k, int64_t sfa_bytes, int64_t sfb_bytes,
+                             int64_t ldo, int mode, int sm_count, int use_pdl,
+                             int device, void* stream, char* err, size_t errlen);
+
+/* Grouped kinds for hq_describe_group_tile. */
+enum { HQ_GROUP_BATCH = 1, HQ_GROUP_MASKED = 2, HQ_GROUP_CONTIGUOUS = 3 };
+
+/* hq_describe_tile for the grouped GEMMs: the tile picked for `count` weights with
+ * `rows` rows each (batch, masked: the slot; contiguous: M / num_experts) and `total_m`
+ * rows of A in all, or the reference's "No <batch|masked|contiguous> <mode> tile for
+ * M=.. (grid M=..), N=.., K=.." text (csrc/kernel/gemm/gemm_dispatch.cuh:65-100) with
+ * HQ_ERR_INVALID.  Needs no device. */
+int hq_describe_group_tile(int kind, int64_t count, int64_t rows, int64_t total_m,
+                           int64_t n, int64_t k, int mode, int sm_count, int device,
+                           char* buf, size_t buflen);
 
 /* Number of SMs of `device`, cached per device.
  * Replaces GetSmCount (csrc/kernel/gemm/gemm_utils.h:29-37), whose cache is

@@ -28,4 +28,4 @@ from .quant import (  # noqa: F401
     ue8m0_from_scale,
     unswizzle_sf,
 )
-from .gemm import batch_gemm_ref, dense_gemm_ref, dequantize  # noqa: F401
+from .gemm import batch_gemm_ref, dense_gemm_ref, dequantize, group_gemm_ref  # noqa: F401

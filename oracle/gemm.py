@@ -92,3 +92,36 @@ def batch_gemm_ref(a_q, b_q, sfa, sfb, mode: str = "w8a8-mxfp8", alpha=None, bia
             acc = acc + bias[b].float().cpu().reshape(1, n)
         out[:, b * n:(b + 1) * n] = acc
     return out.to(out_dtype)
+
+
+def group_gemm_ref(a_q, b_q, sfa, sfb, expert_of_row, mode: str = "w8a8-mxfp8", alpha=None, bias=None,
+                   out_dtype=torch.bfloat16) -> torch.Tensor:
+    """Row-wise expert GEMM: ``out[r] = alpha[e] * (dequant(A[r]) @ dequant(B[e])^T) + bias[e]``
+    with ``e = expert_of_row[r]``; rows whose expert is negative stay zero.
+
+    One model for both MoE layouts of the reference: masked
+    (``tests/test_group_masked_gemm.py:88-146``: expert ``e`` owns a padded slot of which
+    the first ``masked_m[e]`` rows are valid; pass -1 for the padding rows) and contiguous
+    (``tests/test_group_contiguous_gemm.py:60-110``: ``expert_ids`` per row).  ``a_q``
+    [M, K or K/2] with ``sfa`` in SfAtom order over its rows, ``b_q`` [E, N, K or K/2] with
+    ``sfb`` in SfAtom order per expert."""
+    a_q = _np(a_q)
+    b_q = _np(b_q)
+    experts, n = b_q.shape[0], b_q.shape[1]
+    g = GROUP_SIZE[mode]
+    k = a_q.shape[1] * (1 if mode == "w8a8-mxfp8" else 2)
+    a = dequantize(a_q, sfa, mode)
+    sfb = _np(sfb).reshape(experts, -1, k // g)
+    ids = np.asarray(expert_of_row).astype(np.int64)
+    out = torch.zeros([a_q.shape[0], n], dtype=torch.float32)
+    for e in range(experts):
+        rows = torch.from_numpy(np.nonzero(ids == e)[0])
+        if rows.numel() == 0:
+            continue
+        acc = torch.matmul(a[rows], dequantize(b_q[e], sfb[e], mode).T)
+        if alpha is not None:
+            acc = acc * float(alpha[e])
+        if bias is not None:
+            acc = acc + bias[e].float().cpu().reshape(1, n)
+        out[rows] = acc
+    return out.to(out_dtype)

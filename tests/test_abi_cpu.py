@@ -199,7 +199,63 @@ def test_batch_gemm_rules_without_a_device(native):
         hq.batch_gemm(x, w, sfa, sfb, out, mode="w2a2")
     with pytest.raises(RuntimeError, match="no CPU path"):
         hq.batch_gemm(x, w, sfa, sfb, out)
-    assert "mode=batch" in hq.describe_batch_tile(4, 200, 256, 128)
+    assert "mode=batch" in hq.describe_group_tile("batch", 4, 200, 256, 128)
+
+
+def test_group_gemm_rules_without_a_device(native):
+    """Host checks of the masked / contiguous grouped GEMMs (texts of the reference's
+    tests/test_group_masked_gemm.py:840-866 and tests/test_group_contiguous_gemm.py:628-652)."""
+    import halops_b200 as hq
+
+    fake = ctypes.cast(16, ctypes.c_void_p)
+    err = ctypes.create_string_buffer(512)
+    masked = native.lib().hq_group_masked_gemm
+    contiguous = native.lib().hq_group_contiguous_gemm
+    big = 1 << 40
+    assert masked(None, None, None, None, None, None, None, None, 2, 129, 256, 128, big, big, 256, 0, -1, 1, 0, None,
+                  err, len(err)) == 1
+    assert b"No masked w8a8-mxfp8 tile for M=129 (grid M=258), N=256, K=128" in err.value
+    assert masked(None, None, None, None, None, None, None, None, 2, 0, 256, 128, big, big, 256, 0, -1, 1, 0, None,
+                  err, len(err)) == 1
+    assert b"max_m_per_expert must be greater than 0, got 0" in err.value
+    assert masked(None, None, None, None, None, None, fake, fake, 2, 128, 128, 512, big, big, 128, 2, -1, 1, 0, None,
+                  err, len(err)) == 1
+    assert b"W4A4 mode does not support bias yet." in err.value
+    assert masked(None, None, None, None, None, None, None, None, 2, 128, 128, 512, big, big, 128, 2, -1, 1, 0, None,
+                  err, len(err)) == 1
+    assert b"requires alpha input (per-expert scaling factor)" in err.value
+    assert contiguous(None, None, None, None, None, None, None, None, 1, 129, 256, 128, big, big, 256, 0, -1, 1, 0,
+                      None, err, len(err)) == 1
+    assert b"No contiguous w8a8-mxfp8 tile for M=129 (grid M=129), N=256, K=128" in err.value
+    assert contiguous(None, None, None, None, None, None, None, fake, 1, 128, 256, 512, big, big, 256, 1, -1, 1, 0,
+                      None, err, len(err)) == 1
+    assert b"does not take alpha; the per-expert scaling factor" in err.value
+    assert contiguous(None, None, None, None, None, None, None, None, 1, 0, 256, 128, big, big, 256, 0, -1, 1, 0,
+                      None, err, len(err)) == 0  # no rows: nothing to do
+
+    x = torch.empty([256, 128], dtype=torch.float8_e4m3fn)
+    w = torch.empty([2, 256, 128], dtype=torch.float8_e4m3fn)
+    sfa = torch.empty([256, 4], dtype=torch.uint8)
+    sfb = torch.empty([2, 256, 4], dtype=torch.uint8)
+    out = torch.empty([256, 256], dtype=torch.bfloat16)
+    counts = torch.full([2], 128, dtype=torch.int32)
+    ids = torch.zeros([256], dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="masked_m must have dtype torch.int32"):
+        hq.group_masked_gemm(x, w, sfa, sfb, counts.long(), out, None, None, 128)
+    with pytest.raises(RuntimeError, match=re.escape("masked_m shape must be [num_experts], got 1, expected 2")):
+        hq.group_masked_gemm(x, w, sfa, sfb, counts[:1], out, None, None, 128)
+    with pytest.raises(RuntimeError, match="input M must equal num_experts . max_m_per_expert, got 256, expected 128"):
+        hq.group_masked_gemm(x, w, sfa, sfb, counts, out, None, None, 64)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        hq.group_masked_gemm(x, w, sfa, sfb, counts, out, None, None, 128)
+    with pytest.raises(RuntimeError, match="expert_ids must have dtype torch.int32"):
+        hq.group_contiguous_gemm(x, w, sfa, sfb, ids.long(), out)
+    with pytest.raises(RuntimeError, match=re.escape("output shape must be [M, N], got [256, 128], expected [256, 256]")):
+        hq.group_contiguous_gemm(x, w, sfa, sfb, ids, out[:, :128])
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        hq.group_contiguous_gemm(x, w, sfa, sfb, ids, out)
+    assert "mode=masked" in hq.describe_group_tile("masked", 20, 64, 7168, 3584)
+    assert "mode=contiguous" in hq.describe_group_tile("contiguous", 16, 256, 7168, 3584)
 
 
 def test_enum_and_interleave():
