@@ -554,6 +554,82 @@ def run_sweep_next_rows(median_us, dev, peaks):
         print(json.dumps({"config": f"epilogue {label}", "m": m, "n": n, "k": k, "us": round(us, 2),
                           "tflops": round(flops / us / 1e6, 1)}), flush=True)
     assert hq.device_status(dev) == 0
+    run_sweep_grouped(median_us, dev)
+
+
+def run_sweep_grouped(median_us, dev):
+    """Batch / MoE grouped GEMMs on the shapes of the reference's CI baselines
+    (ci/baselines/gemm/group_*.json: 4 experts x 128 rows, N=256, K=512 and 10 experts x
+    4096 rows, N=K=4096) plus a decode-like masked case with partly filled slots."""
+    import halops_b200 as hq
+
+    for mode in ("w8a8-mxfp8", "w4a4-nvfp4"):
+        for experts, rows, n, k in ((4, 128, 256, 512), (10, 4096, 4096, 4096)):
+            m = experts * rows
+            g = torch.Generator(device=dev).manual_seed(12)
+            x = torch.randn([m, k], generator=g, device=dev).to(torch.bfloat16)
+            w = (torch.randn([experts * n, k], generator=g, device=dev) * 0.05).to(torch.bfloat16)
+            xq, sfa = hq.group_wise_quant(x, mode=mode)
+            wq, sfb = hq.group_wise_quant(w, mode=mode)
+            wq, sfb = wq.view(experts, n, -1), sfb.view(experts, n, -1)
+            del x, w
+            alpha = torch.ones([experts], dtype=torch.float32, device=dev) if mode == "w4a4-nvfp4" else None
+            out = torch.empty([m, n], dtype=torch.bfloat16, device=dev)
+            out_b = torch.empty([rows, experts * n], dtype=torch.bfloat16, device=dev)
+            full = torch.full([experts], rows, dtype=torch.int32, device=dev)
+            half = torch.full([experts], rows // 2, dtype=torch.int32, device=dev)
+            ids = (torch.arange(m, device=dev, dtype=torch.int32) // rows).contiguous()
+            cases = (
+                ("group_masked", 1.0, lambda: hq.group_masked_gemm(xq, wq, sfa, sfb, full, out, None, alpha, rows, -1, mode)),
+                ("group_masked half-filled", 0.5,
+                 lambda: hq.group_masked_gemm(xq, wq, sfa, sfb, half, out, None, alpha, rows, -1, mode)),
+                ("group_contiguous", 1.0,
+                 lambda: hq.group_contiguous_gemm(xq, wq, sfa, sfb, ids, out, None, alpha, -1, mode)),
+                ("batch", 1.0, lambda: hq.batch_gemm(xq.view(experts, rows, -1), wq, sfa, sfb, out_b, None, alpha,
+                                                     -1, mode, use_pdl=False)),
+            )
+            for label, filled, fn in cases:
+                us = median_us(fn)
+                print(json.dumps({"config": label, "mode": mode, "experts": experts, "rows_per_expert": rows,
+                                  "n": n, "k": k, "us": round(us, 2),
+                                  "tflops": round(2.0 * m * n * k * filled / us / 1e6, 1)}), flush=True)
+            assert hq.device_status(dev) == 0
+
+
+def run_shape(args):
+    """One dense GEMM shape, GEMM only: MODE,M,N,K.  Prints one JSON line (cold-L2 median);
+    with --kernels-only just 3 warm-up and 3 measured launches, for profiler captures."""
+    import halops_b200 as hq
+
+    mode, m, n, k = args.shape.split(",")
+    m, n, k = int(m), int(n), int(k)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(2026)
+    a = torch.randn([m, k], generator=g, device=dev).to(torch.bfloat16)
+    b = (torch.randn([n, k], generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    aq, sfa = hq.group_wise_quant(a, mode=mode)
+    bq, sfb = hq.group_wise_quant(b, mode=mode)
+    out = torch.empty([m, n], dtype=torch.bfloat16, device=dev)
+    alpha = torch.ones([1], dtype=torch.float32, device=dev) if mode == "w4a4-nvfp4" else None
+    flush = torch.empty([256 << 20], dtype=torch.uint8, device=dev)
+    reps = 3 if args.kernels_only else 30
+    for _ in range(3):
+        hq.dense_gemm(aq, bq, sfa, sfb, out, None, alpha, -1, mode, False)
+    ts = []
+    for _ in range(reps):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        hq.dense_gemm(aq, bq, sfa, sfb, out, None, alpha, -1, mode, False)
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e) * 1e3)
+    assert hq.device_status(dev) == 0
+    ts.sort()
+    us = ts[len(ts) // 2]
+    print(json.dumps({"shape": args.shape, "tile": hq.describe_tile(m, n, k, mode).split("-> ")[1],
+                      "gemm_us": round(us, 2), "gemm_tflops": round(2.0 * m * n * k / us / 1e6, 1)}), flush=True)
 
 
 def main():
@@ -569,8 +645,12 @@ def main():
                     help="time every BASELINE configuration (GEMM only / quantizer only, cold L2) instead")
     ap.add_argument("--c5", action="store_true",
                     help="run config 5 (M=16384, N=57344, K=8192 split over the ranks, strong scaling) instead")
+    ap.add_argument("--shape", default=None, metavar="MODE,M,N,K",
+                    help="time one dense GEMM shape (GEMM only, cold L2) instead, e.g. w8a8-mxfp8,16,24576,1536")
     args = ap.parse_args()
-    if args.sweep:
+    if args.shape:
+        run_shape(args)
+    elif args.sweep:
         run_sweep(args)
     elif args.c5:
         run_c5(args)

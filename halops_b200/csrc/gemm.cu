@@ -29,7 +29,7 @@ namespace {
 
 constexpr int kBM = 128;           // rows of A per CTA tile
 constexpr int kBKBytes = 128;      // bytes of K per stage row: 128 e4m3 or 256 e2m1
-constexpr int kThreads = 192;      // 6 warps
+constexpr int kThreads = 192;      // single-CTA kernel: 6 warps (pair kernel: more, see Cfg2)
 constexpr int kEpiWarps = 4;
 constexpr int kEpiChunk = 32;      // accumulator columns per tcgen05.ld / TMA store
 constexpr int kEpiBufBytes = 32 * kEpiChunk * 2;  // 32 rows x 64 bytes
@@ -40,11 +40,11 @@ constexpr int kSmemBudget = 232448;               // 227 KiB opt-in maximum per 
 __device__ uint32_t g_status[4];
 
 #ifdef HQ_TRACE
-// development aid: %globaltimer stamps of the first k-iterations of cluster 0
+// development aid: SM clock stamps of the first k-iterations of CTA / cluster 0
 __device__ unsigned long long g_trace[3 * 512 * 2];
 #define HQ_STAMP(role, it, slot)                                                      \
     do {                                                                              \
-        if (cluster_id == 0 && (it) < 512u) g_trace[((role)*512 + (it)) * 2 + (slot)] = ptx::globaltimer_ns(); \
+        if (cluster_id == 0 && (it) < 512u) g_trace[((role)*512 + (it)) * 2 + (slot)] = clock64(); \
     } while (0)
 #else
 #define HQ_STAMP(role, it, slot) \
@@ -99,6 +99,8 @@ struct Barriers {
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint64_t overlap_free[2];
+    uint64_t sf_ready[4];  // pair kernel: the scale copies of a k-tile have landed
+    uint64_t turn[2];      // pair kernel: hands the MMA issue from one issuer thread to the other
     uint32_t tmem_base;
     uint32_t abort;
 };
@@ -131,6 +133,7 @@ struct TileCoord {
 // across columns, so one wave of CTAs shares a small set of A and B tiles in L2.
 __device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles_n) {
     constexpr int kGroup = 8;
+    if (tiles_m == 1) return {0, tile};  // decode shapes: no divisions on the way to the first load
     const int per_group = kGroup * tiles_n;
     const int g = tile / per_group;
     const int first_m = g * kGroup;
@@ -564,9 +567,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             // this warp's 32 rows are all padding or all belong to a neighbouring group
             const bool warp_idle = int(lane_base) >= wk.row_hi || int(lane_base) + 32 <= wk.row_lo;
             const bool row_ok = ar >= wk.row_lo && ar < wk.row_hi;
-            // whole tiles go out through TMA stores (a dense tail is clipped by the tensor map)
-            const bool reg_store =
-                direct_store != 0 || wk.row_lo != 0 || (wk.row_hi != kBM && grp.kind != kGroupDense);
+            // whole tiles go out through TMA stores (a dense tail is clipped by the tensor map);
+            // partial tiles are stored from registers, row by row, and so are tiles of at most
+            // 32 rows (one warp, no staging round trip)
+            const bool reg_store = direct_store != 0 || wk.row_lo != 0 || wk.row_hi <= 32 ||
+                                   (wk.row_hi != kBM && grp.kind != kGroupDense);
             // per-tensor (dense) or per-group factor of the NVFP4 recipe
             const float scale = (KIND == 1 && alpha != nullptr) ? __ldg(alpha + wk.group) : 1.0f;
             const uint32_t as = t & 1u;
@@ -716,13 +721,23 @@ struct Cfg2 {
     static constexpr int kStagesFit = (kSmemBudget - kEpiBytes - kBarBytes - 1024) / kStageBytes;
     static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
     static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarBytes + 1024;
-    // Scale columns of one k-iteration and how many such sets rotate in tensor
-    // memory.  With two sets the tcgen05.cp for iteration i + 1 is issued ahead of
-    // the MMAs of iteration i, so that a late stage shows up one iteration before
-    // its MMAs are due.  (Measured: the copies cost the tensor pipe about 30 ns
-    // each whether or not they depend on their neighbours.)
+    // Scale columns of one k-iteration and how many such sets rotate in tensor memory.
+    // The tcgen05.cp copies are issued by other warps than the MMAs: every asynchronous
+    // instruction stalls the thread that issues it (measured per instruction: tcgen05.cp
+    // 60-85 cycles, tcgen05.commit 88, a TMA copy 100-125) and those stalls only overlap
+    // across warps.  One thread issuing 3 copies + 4 MMAs + 2 commits per k-tile spent 850
+    // cycles on them; the MMAs alone take 512.  A set is free again once the MMAs that
+    // read it have completed, so with 4 sets the copies run two k-tiles ahead.
     static constexpr int kSfCols = kSfKAtoms * 4 * (1 + kNAtoms);
-    static constexpr int kSfSets = KIND == 0 ? 2 : 1;
+    static constexpr int kSfSets = BN < 256 ? 4 : (KIND == 0 ? 4 : (KIND == 2 ? 3 : 2));
+    // warps: 0 box loader, 1 MMA issuer, 2-5 epilogue, 6 scale loader, 7.. scale copies
+    static constexpr int kCpWarps = KIND == 0 ? 1 : (KIND == 1 ? 3 : 2);
+    // Two threads (warp 1 and the last warp) issue the MMAs of alternate k-tiles: issuing
+    // 4 MMAs and the 2 commits that release the stage in both CTAs keeps one thread busy
+    // for about 830 cycles, longer than the 512 the MMAs run.  After its MMAs a thread
+    // hands the turn to the other one (tcgen05 fences around an mbarrier arrive), so the
+    // MMAs still reach the tensor core in k order.
+    static constexpr int kThreads = 32 * (8 + kCpWarps);
     static constexpr int kSfRegion = kSfCols * kSfSets;
     static constexpr int kOverlap = BN == 256 ? (kSfRegion + 15) / 16 * 16 : 0;
     static constexpr int kAccStride = BN - kOverlap;
@@ -744,7 +759,7 @@ __device__ __forceinline__ uint32_t instr_desc_pair(uint32_t sf_id) {
 }
 
 template <int BN, int KIND>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((Cfg2<BN, KIND>::kThreads), 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_d, const __grid_constant__ CUtensorMap tm_sfa,
                  const __grid_constant__ CUtensorMap tm_sfb, const float* __restrict__ alpha,
@@ -783,6 +798,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[s]), 2 * kEpiWarps);  // leader's copy is used
             ptx::mbar_init(ptx::smem_u32(&bars->overlap_free[s]), 2 * kEpiWarps);
         }
+        for (int s = 0; s < C::kSfSets; ++s) ptx::mbar_init(ptx::smem_u32(&bars->sf_ready[s]), C::kCpWarps);
+        for (int s = 0; s < 2; ++s) ptx::mbar_init(ptx::smem_u32(&bars->turn[s]), 1);
         bars->abort = 0;
         ptx::fence_mbar_init();
         ptx::prefetch_tmap(&tm_a);
@@ -804,31 +821,50 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
     ptx::pdl_wait();
 
+    const int my_tiles = cluster_id < num_tiles ? (num_tiles - cluster_id + num_clusters - 1) / num_clusters : 0;
+    const uint32_t total_its = uint32_t(my_tiles) * uint32_t(k_tiles);
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer (both CTAs)
+        // ------------------------------------------------------------ box loader (both CTAs)
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
             for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
                 const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
                 const int m0 = tc.m * 256 + int(rank) * kBM;
-                const int n0 = tc.n * BN;
-                const int sfa_atom_row = (tc.m * 2 + int(rank)) * kq_dim;
-                const int sfb_atom_row = (n0 / 128) * kq_dim;
+                const int n0 = tc.n * BN + int(rank) * (BN / 2);
                 for (int kt = 0; kt < k_tiles; ++kt, ++it) {
                     const uint32_t s = it % C::kStages;
-                    const uint32_t ph = (it / C::kStages) & 1u;
                     HQ_STAMP(rank, it, 0);
-                    ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ph ^ 1u, abort, kStatusProducer);
+                    ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ((it / C::kStages) & 1u) ^ 1u, abort,
+                                  kStatusProducer);
                     if (!ok) break;
                     HQ_STAMP(rank, it, 1);
-                    // Bytes of both CTAs are counted on the leader's barrier; only the
-                    // leader registers them (the count may go negative in between).
                     const uint32_t full = ptx::mapa_cluster(ptx::smem_u32(&bars->full[s]), 0);
+                    // Bytes of all four loader threads of the pair are counted on the leader's
+                    // barrier; only this thread registers them (the count may go negative in
+                    // between).
                     if (leader) ptx::mbar_arrive_expect_tx(ptx::smem_u32(&bars->full[s]), 2 * C::kStageBytes);
                     ptx::tma_load_2d_pair(a_base + s * C::kABytes, &tm_a, kt * kBKBytes, m0, full);
-                    ptx::tma_load_2d_pair(b_base + s * C::kBBytes, &tm_b, kt * kBKBytes,
-                                          n0 + int(rank) * (BN / 2), full);
+                    ptx::tma_load_2d_pair(b_base + s * C::kBBytes, &tm_b, kt * kBKBytes, n0, full);
+                }
+            }
+            ptx::pdl_launch_dependents();
+        }
+    } else if (warp == 6) {
+        // ------------------------------------------------------------ scale loader (both CTAs)
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+                const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+                const int sfa_atom_row = (tc.m * 2 + int(rank)) * kq_dim;
+                const int sfb_atom_row = (tc.n * BN / 128) * kq_dim;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % C::kStages;
+                    ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ((it / C::kStages) & 1u) ^ 1u, abort,
+                                  kStatusProducer);
+                    if (!ok) break;
+                    const uint32_t full = ptx::mapa_cluster(ptx::smem_u32(&bars->full[s]), 0);
                     // scale atoms are rows of 128 32-bit words
                     ptx::tma_load_2d_pair(sfa_base + s * C::kSfaBytes, &tm_sfa, 0,
                                           sfa_atom_row + kt * C::kSfKAtoms, full);
@@ -839,58 +875,82 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     }
                 }
             }
-            ptx::pdl_launch_dependents();
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer (leader only)
+    } else if (warp >= 7 && warp < 7 + C::kCpWarps) {
+        // ------------------------------------------------------------ scale copies (leader only)
+        // shared memory -> tensor memory of both CTAs, into scale set it % kSfSets
         if (leader && lane == 0) {
-            const int my_tiles = cluster_id < num_tiles ? (num_tiles - cluster_id + num_clusters - 1) / num_clusters : 0;
-            const uint32_t total_its = uint32_t(my_tiles) * uint32_t(k_tiles);
-            // scales of k-iteration `j` (stage j % kStages) -> tensor-memory set j % kSfSets
-            auto copy_scales = [&](uint32_t j) -> bool {
-                const uint32_t s = j % C::kStages;
-                if (!wait_bar(ptx::smem_u32(&bars->full[s]), (j / C::kStages) & 1u, abort, kStatusMma)) return false;
+            const int cw = warp - 7;
+            bool ok = true;
+            for (uint32_t it = 0; ok && it < total_its; ++it) {
+                const uint32_t s = it % C::kStages;
+                ok = wait_bar(ptx::smem_u32(&bars->full[s]), (it / C::kStages) & 1u, abort, kStatusProducer);
+                if (!ok) break;
+                if (it >= uint32_t(C::kSfSets)) {
+                    // the MMAs of k-tile it - kSfSets read this set: they are done once they
+                    // have released their stage
+                    const uint32_t prev = it - uint32_t(C::kSfSets);
+                    ok = wait_bar(ptx::smem_u32(&bars->empty[prev % C::kStages]), (prev / C::kStages) & 1u, abort,
+                                  kStatusProducer);
+                    if (!ok) break;
+                }
                 ptx::tc_fence_after();
-                const uint32_t set = tmem + C::kSfCol0 + (j % C::kSfSets) * C::kSfCols;
+                const uint32_t set = tmem + C::kSfCol0 + (it % C::kSfSets) * C::kSfCols;
 #pragma unroll
                 for (int a = 0; a < C::kSfKAtoms; ++a) {
-                    ptx::tc_copy_sf<2>(set + a * 4,
-                                       ptx::smem_desc(sfa_base + s * C::kSfaBytes + a * 512, 0, 128, 0));
+                    if ((a * (1 + C::kNAtoms)) % C::kCpWarps == cw) {
+                        ptx::tc_copy_sf<2>(set + a * 4,
+                                           ptx::smem_desc(sfa_base + s * C::kSfaBytes + a * 512, 0, 128, 0));
+                    }
 #pragma unroll
                     for (int j2 = 0; j2 < C::kNAtoms; ++j2) {
-                        ptx::tc_copy_sf<2>(
-                            set + C::kSfKAtoms * 4 + (a * C::kNAtoms + j2) * 4,
-                            ptx::smem_desc(sfb_base + s * C::kSfbBytes + (j2 * C::kSfKAtoms + a) * 512, 0, 128, 0));
+                        if ((a * (1 + C::kNAtoms) + 1 + j2) % C::kCpWarps == cw) {
+                            ptx::tc_copy_sf<2>(
+                                set + C::kSfKAtoms * 4 + (a * C::kNAtoms + j2) * 4,
+                                ptx::smem_desc(sfb_base + s * C::kSfbBytes + (j2 * C::kSfKAtoms + a) * 512, 0, 128,
+                                               0));
+                        }
                     }
                 }
-                return true;
-            };
+                ptx::tc_commit_pair(ptx::mapa_cluster(ptx::smem_u32(&bars->sf_ready[it % C::kSfSets]), 0));
+            }
+        }
+    } else if (warp == 1 || warp == 7 + C::kCpWarps) {
+        // ------------------------------------------------------------ MMA issuers (leader only)
+        if (leader && lane == 0) {
+            const uint32_t me = warp == 1 ? 0u : 1u;  // this thread issues the k-iterations it & 1 == me
             uint32_t it = 0;
             uint32_t t = 0;
-            bool ok = total_its == 0 || copy_scales(0);
+            bool ok = true;
             for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++t) {
                 const uint32_t as = t & 1u;
                 const uint32_t aph = (t >> 1) & 1u;
-                ok = wait_bar(ptx::smem_u32(&bars->acc_empty[as]), aph ^ 1u, abort, kStatusMma);
-                if (!ok) break;
-                if (C::kOverlap != 0 && t > 0) {
-                    ok = wait_bar(ptx::smem_u32(&bars->overlap_free[as ^ 1u]), ((t - 1) >> 1) & 1u, abort,
-                                  kStatusMma);
-                    if (!ok) break;
-                }
-                ptx::tc_fence_after();
                 const uint32_t acc = tmem + as * C::kAccStride;
                 for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    if ((it & 1u) != me) continue;
                     const uint32_t s = it % C::kStages;
+                    if (kt == 0) {
+                        // first k-tile of a tile: the accumulator stage must have been drained
+                        ok = wait_bar(ptx::smem_u32(&bars->acc_empty[as]), aph ^ 1u, abort, kStatusMma);
+                        if (ok && C::kOverlap != 0 && t > 0) {
+                            ok = wait_bar(ptx::smem_u32(&bars->overlap_free[as ^ 1u]), ((t - 1) >> 1) & 1u, abort,
+                                          kStatusMma);
+                        }
+                        if (!ok) break;
+                    }
                     HQ_STAMP(2, it, 0);
-                    // scales of the next k-iteration go ahead of this iteration's MMAs
-                    if (C::kSfSets > 1) {
-                        if (it + 1 < total_its) ok = copy_scales(it + 1);
-                    } else if (it > 0) {
-                        ok = copy_scales(it);
+                    // the scale copies of this k-tile have landed (they waited for the stage);
+                    // the stage's own barrier orders this thread after the TMA writes
+                    ok = wait_bar(ptx::smem_u32(&bars->sf_ready[it % C::kSfSets]), (it / C::kSfSets) & 1u, abort,
+                                  kStatusMma) &&
+                         wait_bar(ptx::smem_u32(&bars->full[s]), (it / C::kStages) & 1u, abort, kStatusMma);
+                    // the other thread has issued the MMAs of the previous k-iteration
+                    if (ok && it > 0u) {
+                        ok = wait_bar(ptx::smem_u32(&bars->turn[me]), ((it - 1u) >> 1) & 1u, abort, kStatusMma);
                     }
                     if (!ok) break;
                     HQ_STAMP(2, it, 1);
+                    ptx::tc_fence_after();
                     const uint32_t set = tmem + C::kSfCol0 + (it % C::kSfSets) * C::kSfCols;
                     const uint64_t adesc = ptx::smem_desc(a_base + s * C::kABytes, 16, 1024, 2);
                     const uint64_t bdesc = ptx::smem_desc(b_base + s * C::kBBytes, 16, 1024, 2);
@@ -912,19 +972,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                             instr_desc_pair<BN, KIND>(sf_id), set + atom * 4,
                             set + C::kSfKAtoms * 4 + atom * C::kNAtoms * 4, (kt > 0 || k > 0) ? 1u : 0u);
                     }
-                    // both producers may refill stage s once these MMAs have read it
+                    // hand the turn over before the (slow) commits
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive(ptx::smem_u32(&bars->turn[me ^ 1u]));
+                    // the loaders of both CTAs may refill stage s once these MMAs have read it;
+                    // MMAs complete in the order they were issued, so the commit after the last
+                    // k-tile also covers the other thread's MMAs
                     const uint32_t empty = ptx::smem_u32(&bars->empty[s]);
                     ptx::tc_commit_pair(ptx::mapa_cluster(empty, 0));
                     ptx::tc_commit_pair(ptx::mapa_cluster(empty, 1));
-                }
-                if (ok) {
-                    const uint32_t accf = ptx::smem_u32(&bars->acc_full[as]);
-                    ptx::tc_commit_pair(ptx::mapa_cluster(accf, 0));
-                    ptx::tc_commit_pair(ptx::mapa_cluster(accf, 1));
+                    if (kt == k_tiles - 1) {
+                        const uint32_t accf = ptx::smem_u32(&bars->acc_full[as]);
+                        ptx::tc_commit_pair(ptx::mapa_cluster(accf, 0));
+                        ptx::tc_commit_pair(ptx::mapa_cluster(accf, 1));
+                    }
                 }
             }
         }
-    } else {
+    } else if (warp < 6) {
         // ------------------------------------------------------------ epilogue (both CTAs)
         const int ew = warp - 2;
         const uint32_t lane_base = (warp & 3) * 32;
@@ -1148,7 +1213,7 @@ int launch_pair(const GemmArgs& g, char* err, size_t errlen) {
     if (max_clusters[dev & 15] == 0) {
         cudaLaunchConfig_t occ = {};
         occ.gridDim = dim3(2 * 74);
-        occ.blockDim = dim3(kThreads);
+        occ.blockDim = dim3(C::kThreads);
         occ.dynamicSmemBytes = size_t(C::kSmemBytes);
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
@@ -1166,7 +1231,7 @@ int launch_pair(const GemmArgs& g, char* err, size_t errlen) {
     }
     const int clusters = min(min(g.sm_count / 2, max_clusters[dev & 15]), tiles_m * tiles_n);
     const int k_tiles = int(g.k_bytes / kBKBytes);
-    HQ_CUDA_TRY(launch(gemm_pair_kernel<BN, KIND>, dim3(2 * clusters), dim3(kThreads), size_t(C::kSmemBytes),
+    HQ_CUDA_TRY(launch(gemm_pair_kernel<BN, KIND>, dim3(2 * clusters), dim3(C::kThreads), size_t(C::kSmemBytes),
                        g.stream, g.pdl, 2, tm_a, tm_b, tm_d, tm_sfa, tm_sfb, g.alpha, g.bias, g.epi_op, k_tiles, g.kq_dim, tiles_m,
                        tiles_n));
     return HQ_OK;
@@ -1225,28 +1290,32 @@ TilePick pick_tile(int64_t m, int64_t n, int64_t k, int mode, int sm_count) {
         }
         return {best, false};
     }
-    // Several rows of tiles: waves x time per tile.  The per-k-tile times are measured
-    // on B200 at M = N = K = 8192 (MXFP8; the FP4 kinds move the same bytes per k-tile):
-    // 128x256 0.457 us (404 us total), 256x256 pair 0.53 us (475 us), 128x128 0.35 us
-    // (620 us), 256x128 pair 0.45 us (807 us); 128x64 is extrapolated.  A tile also
-    // pays about one k-tile of fill and drain.
+    // Several rows of tiles: waves x time per tile.  Fitted to this build's kernels on B200
+    // (MXFP8; M = N = K = 8192 and 8192 x 4096 x 4096): a tile costs its k-tiles plus a
+    // fixed number of k-tile times for fill, drain and the hand-over to the next tile.
+    // 128x256: 0.431 us per k-tile + 3.0 (404 / 105.5 us); 256x256 pair: 0.406 + 5.8
+    // (397 / 107.5 us); 128x128 0.35 (620 us); 256x128 pair 0.348 (633 us); 128x64 is
+    // extrapolated.  The FP4 kinds have four times the scale traffic per k-tile, which the
+    // pair pays twice (both CTAs hold all B scales): measured slower there (163 vs 153 us on
+    // 4096 x 14336 x 4096), so they stay on single-CTA tiles.
     struct Cand {
         int bn;
         bool pair;
         double us_per_ktile;
+        double extra_ktiles;
     };
-    const Cand cands[5] = {{256, false, 0.457}, {256, true, 0.53}, {128, false, 0.35},
-                           {128, true, 0.45},   {64, false, 0.27}};
+    const Cand cands[5] = {{256, false, 0.431, 3.0}, {256, true, 0.406, 5.8}, {128, false, 0.35, 1.0},
+                           {128, true, 0.348, 1.0},  {64, false, 0.27, 1.0}};
     const double k_tiles = double(k) / (fp8 ? 128.0 : 256.0);
     TilePick best = {0, false};
     double best_cost = 0.0;
     for (const Cand& c : cands) {
-        if (n % c.bn != 0 || (c.bn == 64 && !fp8) || (c.pair && m <= kBM)) continue;
+        if (n % c.bn != 0 || (c.bn == 64 && !fp8) || (c.pair && (m <= kBM || !fp8))) continue;
         const int64_t tiles = (c.pair ? tiles_m2 : tiles_m) * (n / c.bn);
         const int64_t units = c.pair ? sm_count / 2 : sm_count;
         if (units < 1) continue;
         const double waves = double((tiles + units - 1) / units);
-        const double cost = waves * (k_tiles + 1.0) * c.us_per_ktile;
+        const double cost = waves * (k_tiles + c.extra_ktiles) * c.us_per_ktile;
         if (best.bn == 0 || cost < best_cost * 0.999) {
             best = {c.bn, c.pair};
             best_cost = cost;
