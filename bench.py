@@ -307,6 +307,7 @@ def run_ours(args):
     gemm_tflops = flops_rank / (gemm_ms * 1e-3) / 1e12
     timed_seconds = total_ms * 1e-3
     fp8_peak = 2.0 * (peaks["bf16"] if timed_seconds < 1.0 else peaks["bf16_sustained"])
+    pair_tile = "pair=1" in hq.describe_tile(M, N_LOCAL, K, MODE, device=local)
     quant_bytes = M * K * (2 + 1 + 1 / 32)
 
     if rank == 0:
@@ -329,11 +330,15 @@ def run_ours(args):
                       "gbs_alone": quant_bytes / (quant_only_ms * 1e-3) / 1e9,
                       "frac_of_hbm": quant_bytes / (quant_only_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                       "bytes_per_element": 3.03125},
-            "roofline": {"kernel": "gemm_kernel<256, mxfp8> (128x256x128 single-CTA tile)", "bound": "tensor", "achieved": gemm_tflops,
+            "roofline": {"kernel": ("gemm_pair_kernel<256, mxfp8> (256x256x128 2-CTA tile)" if pair_tile else
+                                    "gemm_kernel<256, mxfp8> (128x256x128 single-CTA tile)"),
+                         "bound": "tensor", "achieved": gemm_tflops,
                          "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak,
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
-                         # workload (ncu capture summarised in profiles/gemm_kernel_mxfp8_128x256_c2_ncu.md)
-                         "traffic": 605.2e6, "algorithmic_bytes": 64 * 2**20 * 2 + 4 * 2**20 + 128 * 2**20,
+                         # workload (ncu captures summarised in profiles/gemm_pair_kernel_mxfp8_256x256_c2_ncu.md
+                         # and profiles/gemm_kernel_mxfp8_128x256_c2_ncu.md)
+                         "traffic": 475.6e6 if pair_tile else 605.2e6,
+                         "algorithmic_bytes": 64 * 2**20 * 2 + 4 * 2**20 + 128 * 2**20,
                          "peak_source": f"2 x {peaks['source']} cuBLAS bf16 "
                                         f"({'burst' if timed_seconds < 1.0 else 'sustained'}) as the dense fp8 peak"},
             "e2e": {"value": world * flops_rank / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",

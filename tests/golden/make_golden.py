@@ -18,6 +18,11 @@ the top but never call here.  Outputs:
   ``per_token_cast_* / per_block_cast_*`` helpers, swizzled with
   ``reorder_sf_to_cutlass``, and the reference ``ref_gemm`` / ``ref_gemm_w4a4``
   bf16 output.
+* ``batch_<mode>.npz``, ``masked_<mode>.npz``, ``contiguous_w8a8-mxfp8.npz`` - inputs built
+  by the input builders of the reference's ``tests/test_batch_gemm.py``,
+  ``tests/test_group_masked_gemm.py`` and ``tests/test_group_contiguous_gemm.py`` and the
+  outputs of their CPU models (``ref_batch_gemm_fp8 / _fp4``, ``ref_group_masked_gemm`` /
+  ``_w4a4``, ``ref_group_contiguous_gemm``).
 """
 
 from __future__ import annotations
@@ -35,7 +40,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 def _import_reference(root: str):
     stub = types.ModuleType("halops")
-    for name in ("group_wise_quant", "dense_gemm", "interleave_gate_up"):
+    for name in ("group_wise_quant", "dense_gemm", "interleave_gate_up", "batch_gemm", "group_masked_gemm",
+                 "group_contiguous_gemm"):
         setattr(stub, name, None)
 
     class _EpilogueOp:  # only attribute access at import time
@@ -49,6 +55,13 @@ def _import_reference(root: str):
     import tests.utils.gemm_utils as gu  # noqa: E402
     assert os.path.abspath(tq.__file__).startswith(os.path.abspath(root))
     return tq, tdg, gu
+
+
+def _import_grouped():
+    import tests.test_batch_gemm as tbg  # noqa: E402
+    import tests.test_group_contiguous_gemm as tcg  # noqa: E402
+    import tests.test_group_masked_gemm as tmg  # noqa: E402
+    return tbg, tmg, tcg
 
 
 def _bf16_bits(x: torch.Tensor) -> np.ndarray:
@@ -127,6 +140,48 @@ def make_gemm(tdg, gu, out_dir: str) -> None:
         )
 
 
+def _u8(t: torch.Tensor) -> np.ndarray:
+    return (t if t.dtype == torch.uint8 else t.contiguous().view(torch.uint8)).numpy()
+
+
+def make_grouped(out_dir: str) -> None:
+    tbg, tmg, tcg = _import_grouped()
+    torch.manual_seed(2027)
+    # batch, MXFP8 with bias: 100 rows per batch, so 128-row tiles straddle two batches
+    inp = tbg.make_w8a8_mxfp8_inputs(3, 100, 128, 256, add_bias=True)
+    ref = tbg.ref_batch_gemm_fp8(inp["input_fp8"], inp["weight_fp8"], inp["sfa_logical"], inp["sfb_logical"],
+                                 bias=inp["bias"])
+    np.savez_compressed(
+        os.path.join(out_dir, "batch_w8a8-mxfp8.npz"), x=_u8(inp["input_fp8"]), w=_u8(inp["weight_fp8"]),
+        sfa=inp["sfa"].numpy(), sfb=inp["sfb"].numpy(), bias_bits=_bf16_bits(inp["bias"]), out_bits=_bf16_bits(ref))
+    inp = tbg.make_nvfp4_inputs(2, 64, 128, 512)
+    ref = tbg.ref_batch_gemm_fp4(inp["x_fp4_float"], inp["w_fp4_float"])
+    np.savez_compressed(
+        os.path.join(out_dir, "batch_w4a4-nvfp4.npz"), x=inp["input_packed"].numpy(), w=inp["weight_packed"].numpy(),
+        sfa=inp["sfa"].numpy(), sfb=inp["sfb"].numpy(), alpha=inp["alpha"].numpy(), out_bits=_bf16_bits(ref))
+    # masked: partly filled, full and empty slots
+    inp = tmg.make_w8a8_mxfp8_inputs(128, 3, 128, 256, full_x=False, masked_m=[17, 128, 0], add_bias=True)
+    ref = tmg.ref_group_masked_gemm(inp.x, inp.w, inp.sfa_logical, inp.sfb_logical, inp.masked_m, 128, 3,
+                                    bias=inp.bias)
+    np.savez_compressed(
+        os.path.join(out_dir, "masked_w8a8-mxfp8.npz"), x=_u8(inp.x), w=_u8(inp.w), sfa=inp.sfa.numpy(),
+        sfb=inp.sfb.numpy(), masked_m=inp.masked_m.numpy(), bias_bits=_bf16_bits(inp.bias), out_bits=_bf16_bits(ref))
+    inp = tmg.make_nvfp4_inputs(64, 4, 128, 512, full_x=False, masked_m=[64, 5, 0, 33], alpha=[1.0, 0.5, 2.0, 0.25])
+    ref = tmg.ref_group_masked_gemm_w4a4(inp.x_fp4_float, inp.w_fp4_float, inp.masked_m, 64, 4, alpha=inp.alpha)
+    np.savez_compressed(
+        os.path.join(out_dir, "masked_w4a4-nvfp4.npz"), x=inp.x_packed.numpy(), w=inp.w_packed.numpy(),
+        sfa=inp.sfa.numpy(), sfb=inp.sfb.numpy(), masked_m=inp.masked_m.numpy(), alpha=inp.alpha.numpy(),
+        out_bits=_bf16_bits(ref))
+    # contiguous: three experts with 128 rows each, per-expert bias
+    inp = tcg.make_w8a8_mxfp8_inputs(384, 128, 256, 3, 64, add_bias=True)
+    ref = tcg.ref_group_contiguous_gemm(inp.x, inp.w, inp.sfa_logical, inp.sfb_logical, inp.expert_ids,
+                                        inp.num_experts, token_nums=inp.token_nums, bias=inp.bias)
+    np.savez_compressed(
+        os.path.join(out_dir, "contiguous_w8a8-mxfp8.npz"), x=_u8(inp.x), w=_u8(inp.w), sfa=inp.sfa.numpy(),
+        sfb=inp.sfb.numpy(), expert_ids=inp.expert_ids.numpy(), bias_bits=_bf16_bits(inp.bias),
+        out_bits=_bf16_bits(ref))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
@@ -136,6 +191,7 @@ def main() -> None:
     make_quant(tq, args.out)
     make_amax_sweep(tq, args.out)
     make_gemm(tdg, gu, args.out)
+    make_grouped(args.out)
     for f in sorted(os.listdir(args.out)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(args.out, f)))

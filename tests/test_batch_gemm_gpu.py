@@ -181,3 +181,31 @@ def test_quantising_epilogues_raise(hq):
         hq.batch_gemm(x, w, sfa, sfb, out, epilogue=hq.EpilogueOp.Quant)
     with pytest.raises(RuntimeError, match="GateMulQuant epilogues need gate"):
         hq.batch_gemm(x, w, sfa, sfb, out, epilogue=hq.EpilogueOp.GateMulQuant)
+
+
+@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4"])
+def test_golden_fixture(hq, golden_dir, mode):
+    """Inputs and outputs of the reference's own input builders and CPU model
+    (tests/golden/make_golden.py); the MXFP8 case has 100 rows per batch and a bias."""
+    import os
+
+    import numpy as np
+
+    def bf16(bits):
+        return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).view(torch.bfloat16)
+
+    d = np.load(os.path.join(golden_dir, f"batch_{mode}.npz"))
+    x, w = torch.from_numpy(d["x"]).cuda(), torch.from_numpy(d["w"]).cuda()
+    if mode == "w8a8-mxfp8":
+        x, w = x.view(torch.float8_e4m3fn), w.view(torch.float8_e4m3fn)
+    sfa, sfb = torch.from_numpy(d["sfa"]).cuda(), torch.from_numpy(d["sfb"]).cuda()
+    alpha = torch.from_numpy(d["alpha"]).cuda() if "alpha" in d else None
+    bias = bf16(d["bias_bits"]).cuda() if "bias_bits" in d else None
+    out = _run(hq, x, w, sfa, sfb, mode, bias=bias, alpha=alpha)
+    ref = bf16(d["out_bits"]).float()  # [B, M, N]
+    tol = dict(W8A8_TOL if mode == "w8a8-mxfp8" else W4A4_TOL)
+    if bias is not None:
+        tol["atol"] = 1e-2
+    n = w.shape[1]
+    for b in range(x.shape[0]):
+        torch.testing.assert_close(out[:, b * n:(b + 1) * n].float().cpu(), ref[b], **tol)

@@ -256,3 +256,45 @@ def test_contiguous_errors(hq):
         hq.group_contiguous_gemm(x, w, sfa, sfb, ids[:64], out)
     with pytest.raises(RuntimeError, match="Unsupported mode: w2a2"):
         hq.group_contiguous_gemm(x, w, sfa, sfb, ids, out, None, None, -1, "w2a2")
+
+
+def _bf16_from_bits(bits):
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).view(torch.bfloat16)
+
+
+def _golden_operands(d, mode):
+    x, w = torch.from_numpy(d["x"]).cuda(), torch.from_numpy(d["w"]).cuda()
+    if mode == "w8a8-mxfp8":
+        x, w = x.view(torch.float8_e4m3fn), w.view(torch.float8_e4m3fn)
+    alpha = torch.from_numpy(d["alpha"]).cuda() if "alpha" in d else None
+    bias = _bf16_from_bits(d["bias_bits"]).cuda() if "bias_bits" in d else None
+    return x, w, torch.from_numpy(d["sfa"]).cuda(), torch.from_numpy(d["sfb"]).cuda(), alpha, bias
+
+
+@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4"])
+def test_masked_golden_fixture(hq, golden_dir, mode):
+    """Inputs and outputs of the reference's own input builders and CPU model
+    (tests/golden/make_golden.py): partly filled, full and empty slots, per-expert alpha."""
+    import os
+
+    d = np.load(os.path.join(golden_dir, f"masked_{mode}.npz"))
+    x, w, sfa, sfb, alpha, bias = _golden_operands(d, mode)
+    masked = d["masked_m"]
+    max_m = x.shape[0] // masked.size
+    out = torch.full([x.shape[0], w.shape[1]], 3.0, dtype=torch.bfloat16, device="cuda")
+    hq.group_masked_gemm(x, w, sfa, sfb, torch.from_numpy(masked).cuda(), out, bias, alpha, max_m, -1, mode)
+    assert hq.device_status() == 0
+    ref = _bf16_from_bits(d["out_bits"]).float()
+    rows = np.concatenate([np.arange(e * max_m, e * max_m + c) for e, c in enumerate(masked)])
+    _compare(out, ref, rows, mode, bias)
+
+
+def test_contiguous_golden_fixture(hq, golden_dir):
+    import os
+
+    d = np.load(os.path.join(golden_dir, "contiguous_w8a8-mxfp8.npz"))
+    x, w, sfa, sfb, alpha, bias = _golden_operands(d, "w8a8-mxfp8")
+    out = torch.empty([x.shape[0], w.shape[1]], dtype=torch.bfloat16, device="cuda")
+    hq.group_contiguous_gemm(x, w, sfa, sfb, torch.from_numpy(d["expert_ids"]).cuda(), out, bias)
+    assert hq.device_status() == 0
+    _compare(out, _bf16_from_bits(d["out_bits"]).float(), np.arange(x.shape[0]), "w8a8-mxfp8", bias)

@@ -138,3 +138,48 @@ def test_torch_cpu_path_equals_numpy_oracle(golden_dir):
     bq, sfb = quant_mxfp8_torch(b)
     want = oracle.dense_gemm_ref(aq, bq, sfa.numpy(), sfb.numpy(), "w8a8-mxfp8", swizzled=False)
     assert torch.equal(gemm_mxfp8_torch(aq, sfa, bq, sfb), want)
+
+
+def _grouped_fixture(golden_dir, name):
+    d = np.load(os.path.join(golden_dir, name))
+    alpha = torch.from_numpy(d["alpha"]) if "alpha" in d else None
+    bias = _bf16(d["bias_bits"]) if "bias_bits" in d else None
+    return d, alpha, bias, _bf16(d["out_bits"]).float()
+
+
+def _close_to_model(got, ref, bias):
+    """Without a bias the oracle repeats the model's arithmetic exactly; the models add the
+    bias after rounding the product to bfloat16 and round the sum again, the oracle rounds
+    once, which moves a result by at most one bfloat16 step of the larger of the two."""
+    if bias is None:
+        assert torch.equal(got, ref)
+    else:
+        torch.testing.assert_close(got, ref, rtol=2.0 ** -7, atol=2.0 ** -7 * float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4"])
+def test_batch_oracle_matches_reference_model(golden_dir, mode):
+    d, alpha, bias, ref = _grouped_fixture(golden_dir, f"batch_{mode}.npz")  # ref: [B, M, N]
+    got = oracle.batch_gemm_ref(d["x"], d["w"], d["sfa"], d["sfb"], mode, alpha=alpha, bias=bias).float()
+    batches, m, n = ref.shape
+    for b in range(batches):
+        _close_to_model(got[:, b * n:(b + 1) * n], ref[b], bias)
+
+
+@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4"])
+def test_masked_oracle_matches_reference_model(golden_dir, mode):
+    d, alpha, bias, ref = _grouped_fixture(golden_dir, f"masked_{mode}.npz")
+    masked = d["masked_m"]
+    max_m = ref.shape[0] // masked.size
+    ids = np.full(ref.shape[0], -1)
+    for e, cnt in enumerate(masked):
+        ids[e * max_m:e * max_m + cnt] = e
+    got = oracle.group_gemm_ref(d["x"], d["w"], d["sfa"], d["sfb"], ids, mode, alpha=alpha, bias=bias).float()
+    # the alpha of this fixture is a power of two per expert, so it commutes with the rounding
+    _close_to_model(got, ref, bias)
+
+
+def test_contiguous_oracle_matches_reference_model(golden_dir):
+    d, alpha, bias, ref = _grouped_fixture(golden_dir, "contiguous_w8a8-mxfp8.npz")
+    got = oracle.group_gemm_ref(d["x"], d["w"], d["sfa"], d["sfb"], d["expert_ids"], "w8a8-mxfp8", bias=bias).float()
+    _close_to_model(got, ref, bias)
