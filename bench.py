@@ -560,6 +560,7 @@ def run_sweep_next_rows(median_us, dev, peaks):
                           "tflops": round(flops / us / 1e6, 1)}), flush=True)
     assert hq.device_status(dev) == 0
     run_sweep_grouped(median_us, dev)
+    run_sweep_low_latency(median_us, dev, peaks)
 
 
 def run_sweep_grouped(median_us, dev):
@@ -599,6 +600,29 @@ def run_sweep_grouped(median_us, dev):
                                   "n": n, "k": k, "us": round(us, 2),
                                   "tflops": round(2.0 * m * n * k * filled / us / 1e6, 1)}), flush=True)
             assert hq.device_status(dev) == 0
+
+
+def run_sweep_low_latency(median_us, dev, peaks):
+    """low_latency_mma_gemm (M <= 16, plain scales) next to dense_gemm on the same operands."""
+    import halops_b200 as hq
+
+    for m, n, k in ((1, 4096, 4096), (8, 8192, 1024), (16, 7168, 2048), (16, 24576, 1536), (8, 32768, 1024)):
+        g = torch.Generator(device=dev).manual_seed(13)
+        x = torch.randn([m, k], generator=g, device=dev).to(torch.bfloat16)
+        w = (torch.randn([n, k], generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        xq, sfa = hq.group_wise_quant(x, use_swizzle=False)
+        wq, sfb = hq.group_wise_quant(w, use_swizzle=False)
+        _, sfa_sw = hq.group_wise_quant(x)
+        _, sfb_sw = hq.group_wise_quant(w)
+        out = torch.empty([m, n], dtype=torch.bfloat16, device=dev)
+        ll_us = median_us(lambda: hq.low_latency_mma_gemm(xq, wq, sfa, sfb, out, use_pdl=False))
+        dense_us = median_us(lambda: hq.dense_gemm(xq, wq, sfa_sw, sfb_sw, out, None, None, -1, MODE, False))
+        nbytes = n * k * (1 + 1 / 32)
+        print(json.dumps({"config": "low_latency_mma_gemm", "m": m, "n": n, "k": k, "us": round(ll_us, 2),
+                          "weight_gbs": round(nbytes / ll_us / 1e3, 1),
+                          "frac_of_hbm": round(nbytes / ll_us / 1e3 / peaks["hbm_gbs"], 3),
+                          "dense_gemm_us": round(dense_us, 2)}), flush=True)
+    assert hq.device_status(dev) == 0
 
 
 def run_shape(args):

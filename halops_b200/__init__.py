@@ -1,8 +1,8 @@
 """B200-native (sm_100a) block-scaled quantize -> dense GEMM path.
 
 Drop-in for the reference's ``halops.group_wise_quant``, ``halops.dense_gemm``,
-``halops.batch_gemm``, ``halops.group_masked_gemm``, ``halops.group_contiguous_gemm`` and
-``halops.rms_norm_quant`` (plus ``interleave_gate_up`` and ``EpilogueOp``): same
+``halops.batch_gemm``, ``halops.group_masked_gemm``, ``halops.group_contiguous_gemm``,
+``halops.low_latency_mma_gemm`` and ``halops.rms_norm_quant`` (plus ``interleave_gate_up`` and ``EpilogueOp``): same
 Python signatures, executed by hand-written CUDA/PTX kernels through a C-ABI
 shared library.  There is no CPU path and no fallback.
 """
@@ -15,12 +15,13 @@ from .gemm import (
     group_masked_gemm,
     group_wise_quant,
     interleave_gate_up,
+    low_latency_mma_gemm,
     rms_norm_quant,
 )
 from ._native import lib_path
 
 __all__ = ["EpilogueOp", "batch_gemm", "dense_gemm", "group_contiguous_gemm", "group_masked_gemm",
-           "group_wise_quant", "interleave_gate_up", "rms_norm_quant", "device_status", "describe_tile",
+           "group_wise_quant", "interleave_gate_up", "low_latency_mma_gemm", "rms_norm_quant", "device_status", "describe_tile",
            "describe_group_tile", "lib_path"]
 __version__ = "0.1.0"
 

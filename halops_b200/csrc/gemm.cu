@@ -692,6 +692,238 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     }
 }
 
+// ---------------------------------------------------------------------------- M <= 16, plain scales
+//
+// Decode-sized GEMM whose block scales come in the plain row-major [rows, K / 32] layout
+// (what the quantizer writes without the SfAtom swizzle), with the two fused forms of the
+// reference's low-latency GEMM (csrc/kernel/gemm/low_latency_mma_gemm.cu:23-76): concat-K
+// (a second input / weight pair accumulated into the same output) and dual output (a
+// second weight multiplied by the same input).  128 x 64 tiles of the tcgen05 path; the
+// 512-byte scale atoms the MMA wants are assembled in shared memory by a warp of 4-byte
+// cp.async copies, one scale word per row and k-tile, that arrive on the stage's barrier.
+
+struct LlParams {
+    const uint8_t* sfa;   // [m, k1 / 32]
+    const uint8_t* sfb;   // [n, k1 / 32]
+    const uint8_t* sfa2;  // concat-K: [m, k2 / 32]
+    const uint8_t* sfb2;  // concat-K: [n, k2 / 32]; dual output: [n2, k1 / 32]
+    int64_t sfa_stride, sfb_stride, sfa2_stride, sfb2_stride;  // bytes between scale rows
+    __nv_bfloat16* out;   // [m, n]
+    __nv_bfloat16* out2;  // dual output: [m, n2]
+    int64_t ldo, ldo2;
+    int m, n, n2;            // n2 = 0 unless dual output
+    int k_tiles1, k_tiles2;  // k_tiles2 = 0 unless concat-K
+    int a_rows;              // rows of the A box (m rounded up to 8)
+    int sigmoid;             // write sigmoid(bf16(result)) instead
+};
+
+constexpr int kLlThreads = 224;  // loader, MMA issuer, 4 epilogue warps, scale builder
+
+__global__ void __launch_bounds__(kLlThreads, 1)
+ll_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+               const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_b2,
+               const LlParams p) {
+    constexpr int BN = 64;
+    using C = Cfg<BN, 0>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* const smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+    const uint32_t a_base = smem_base;
+    const uint32_t b_base = a_base + C::kStages * C::kABytes;
+    const uint32_t sfa_base = b_base + C::kStages * C::kBBytes;
+    const uint32_t sfb_base = sfa_base + C::kStages * C::kSfaBytes;
+    const uint32_t bar_off = C::kStages * C::kStageBytes + C::kEpiBytes;
+    Barriers* const bars = reinterpret_cast<Barriers*>(smem + bar_off);
+    volatile uint32_t* const abort = &bars->abort;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tiles1 = (p.n + BN - 1) / BN;
+    const int num_tiles = tiles1 + (p.n2 + BN - 1) / BN;
+    const int k_tiles = p.k_tiles1 + p.k_tiles2;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&bars->full[s]), 33);  // the loader + 32 scale-builder lanes
+            ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&bars->acc_full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[s]), kEpiWarps);
+        }
+        bars->abort = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tmap(&tm_a);
+        ptx::prefetch_tmap(&tm_b);
+        ptx::prefetch_tmap(&tm_a2);
+        ptx::prefetch_tmap(&tm_b2);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<1>(ptx::smem_u32(&bars->tmem_base), C::kTmemCols);
+        ptx::tmem_relinquish<1>();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+    ptx::pdl_wait();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ box loader
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                const bool second = tile >= tiles1;  // dual output: a tile of weight2
+                const int n0 = (second ? tile - tiles1 : tile) * BN;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % C::kStages;
+                    ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ((it / C::kStages) & 1u) ^ 1u, abort,
+                                  kStatusProducer);
+                    if (!ok) break;
+                    const uint32_t full = ptx::smem_u32(&bars->full[s]);
+                    ptx::mbar_arrive_expect_tx(full, p.a_rows * kBKBytes + C::kBBytes);
+                    const bool tail = kt >= p.k_tiles1;  // concat-K: the second input / weight pair
+                    const int x = (tail ? kt - p.k_tiles1 : kt) * kBKBytes;
+                    ptx::tma_load_2d(a_base + s * C::kABytes, tail ? &tm_a2 : &tm_a, x, 0, full);
+                    ptx::tma_load_2d(b_base + s * C::kBBytes, (tail || second) ? &tm_b2 : &tm_b, x, n0, full);
+                }
+            }
+            ptx::pdl_launch_dependents();
+        }
+    } else if (warp == 6) {
+        // ------------------------------------------------------------ scale builder
+        // lane r writes the scale words of A row r and of B rows r and r + 32 where the
+        // SfAtom has them: byte (row % 32) * 16 + (row / 32) * 4 of the stage's atom
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+            const bool second = tile >= tiles1;
+            const int n0 = (second ? tile - tiles1 : tile) * BN;
+            const int n_rows = second ? p.n2 : p.n;
+            for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                const uint32_t s = it % C::kStages;
+                ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ((it / C::kStages) & 1u) ^ 1u, abort, kStatusProducer);
+                if (!ok) break;
+                const bool tail = kt >= p.k_tiles1;
+                const int64_t koff = int64_t(tail ? kt - p.k_tiles1 : kt) * 4;
+                const uint8_t* const sa = tail ? p.sfa2 : p.sfa;
+                const int64_t sa_stride = tail ? p.sfa2_stride : p.sfa_stride;
+                const uint8_t* const sb = (tail || second) ? p.sfb2 : p.sfb;
+                const int64_t sb_stride = (tail || second) ? p.sfb2_stride : p.sfb_stride;
+                if (lane < p.m) ptx::cp_async_4(sfa_base + s * C::kSfaBytes + lane * 16, sa + lane * sa_stride + koff);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int row = n0 + lane + 32 * h;
+                    if (row < n_rows) {
+                        ptx::cp_async_4(sfb_base + s * C::kSfbBytes + lane * 16 + h * 4, sb + row * sb_stride + koff);
+                    }
+                }
+                ptx::cp_async_arrive_noinc(ptx::smem_u32(&bars->full[s]));
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0;
+            uint32_t t = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++t) {
+                const uint32_t as = t & 1u;
+                ok = wait_bar(ptx::smem_u32(&bars->acc_empty[as]), ((t >> 1) & 1u) ^ 1u, abort, kStatusMma);
+                if (!ok) break;
+                ptx::tc_fence_after();
+                const uint32_t acc = tmem + as * C::kAccStride;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % C::kStages;
+                    ok = wait_bar(ptx::smem_u32(&bars->full[s]), (it / C::kStages) & 1u, abort, kStatusMma);
+                    if (!ok) break;
+                    // the scale words were written by ordinary asynchronous copies; the
+                    // tensor-memory copy reads them through the async proxy
+                    ptx::fence_proxy_async_smem();
+                    ptx::tc_fence_after();
+                    ptx::tc_copy_sf<1>(tmem + C::kSfaCol, ptx::smem_desc(sfa_base + s * C::kSfaBytes, 0, 128, 0));
+                    ptx::tc_copy_sf<1>(tmem + C::kSfbCol, ptx::smem_desc(sfb_base + s * C::kSfbBytes, 0, 128, 0));
+                    const uint64_t adesc = ptx::smem_desc(a_base + s * C::kABytes, 16, 1024, 2);
+                    const uint64_t bdesc = ptx::smem_desc(b_base + s * C::kBBytes, 16, 1024, 2);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        ptx::tc_mma_block_scaled<1, 0>(acc, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2),
+                                                       instr_desc<BN, 0>(uint32_t(k)), tmem + C::kSfaCol,
+                                                       tmem + C::kSfbCol, (kt > 0 || k > 0) ? 1u : 0u);
+                    }
+                    ptx::tc_commit(ptx::smem_u32(&bars->empty[s]));
+                }
+                if (ok) ptx::tc_commit(ptx::smem_u32(&bars->acc_full[as]));
+            }
+        }
+    } else if (warp < 6) {
+        // ------------------------------------------------------------ epilogue
+        const uint32_t lane_base = (warp & 3) * 32;
+        uint32_t t = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++t) {
+            const bool second = tile >= tiles1;
+            const int n0 = (second ? tile - tiles1 : tile) * BN;
+            const int n_rows = second ? p.n2 : p.n;
+            __nv_bfloat16* const out = second ? p.out2 : p.out;
+            const int64_t ldo = second ? p.ldo2 : p.ldo;
+            const uint32_t as = t & 1u;
+            ok = wait_bar(ptx::smem_u32(&bars->acc_full[as]), (t >> 1) & 1u, abort, kStatusEpilogue);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            if (lane_base == 0) {  // the only 32 accumulator rows that can hold one of the m <= 16 rows
+                const uint32_t acc = tmem + as * C::kAccStride;
+#pragma unroll 1
+                for (int c = 0; c < BN / kEpiChunk; ++c) {
+                    uint32_t r[32];
+                    ptx::tc_load_32x32(acc + c * kEpiChunk, r);
+                    ptx::tc_wait_ld();
+                    if (lane < p.m) {
+                        const int col = n0 + c * kEpiChunk;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                float lo = __uint_as_float(r[8 * j + 2 * i]);
+                                float hi = __uint_as_float(r[8 * j + 2 * i + 1]);
+                                if (p.sigmoid) {
+                                    // sigmoid of the bfloat16 result, as a float computation
+                                    lo = __bfloat162float(__float2bfloat16_rn(lo));
+                                    hi = __bfloat162float(__float2bfloat16_rn(hi));
+                                    lo = __fdiv_rn(1.0f, 1.0f + expf(-lo));
+                                    hi = __fdiv_rn(1.0f, 1.0f + expf(-hi));
+                                }
+                                const __nv_bfloat162 v = __float22bfloat162_rn(make_float2(lo, hi));
+                                w[i] = *reinterpret_cast<const uint32_t*>(&v);
+                            }
+                            // weight rows come in multiples of 8: whole 16-byte pieces
+                            if (col + 8 * j < n_rows) {
+                                *reinterpret_cast<uint4*>(out + int64_t(lane) * ldo + col + 8 * j) =
+                                    make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[as]));
+        }
+    }
+
+    if (*abort != 0u) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc<1>(tmem, C::kTmemCols);
+    }
+}
+
 // ---------------------------------------------------------------------------- 2-CTA tiles
 //
 // Pair kernel: a cluster of two CTAs computes one 256 x BN tile with
@@ -1752,6 +1984,123 @@ extern "C" int hq_group_contiguous_gemm(const void* a, const void* b, const void
     return hq::grouped_gemm_impl(hq::kGroupContiguous, a, b, sfa, sfb, out, bias, alpha, expert_ids, num_experts,
                                  rows, m, n, k, sfa_bytes, sfb_bytes, ldo, mode, HQ_EPILOGUE_IDENTITY, sm_count,
                                  use_pdl, device, stream, err, errlen);
+}
+
+extern "C" int hq_low_latency_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* out,
+                                   const void* a2, const void* b2, const void* sfa2, const void* sfb2, void* out2,
+                                   int64_t m, int64_t n, int64_t n2, int64_t k1, int64_t k2, int64_t sfa_stride,
+                                   int64_t sfb_stride, int64_t sfa2_stride, int64_t sfb2_stride, int64_t ldo,
+                                   int64_t ldo2, int use_sigmoid, int sm_count, int use_pdl, int device,
+                                   void* stream, char* err, size_t errlen) {
+    using hq::fail;
+    const bool concat = a2 != nullptr;
+    const bool dual = out2 != nullptr;
+    const bool second_weight = b2 != nullptr;
+    // same rules and texts as the reference's ResolveLlShapes (csrc/kernel/gemm/low_latency_utils.cuh:222-273)
+    if ((a2 != nullptr) != (sfa2 != nullptr) || second_weight != (sfb2 != nullptr) || second_weight != (concat != dual)) {
+        return fail(err, errlen, HQ_ERR_INVALID, "weight2 / sfb2 must come with either input2 / sfa2 or output2");
+    }
+    if (use_sigmoid && second_weight) {
+        return fail(err, errlen, HQ_ERR_INVALID, "low_latency_mma_gemm use_sigmoid does not support input2 or output2");
+    }
+    if (m < 0 || n < 0 || n2 < 0 || k1 < 0 || k2 < 0 || n > INT32_MAX || n2 > INT32_MAX || k1 > INT32_MAX ||
+        k2 > INT32_MAX) {
+        return fail(err, errlen, HQ_ERR_INVALID, "problem sizes must be non-negative and below 2^31");
+    }
+    if (!dual) n2 = 0;
+    if (!concat) k2 = 0;
+    if (m > 16) return fail(err, errlen, HQ_ERR_INVALID, "low_latency_mma_gemm supports M <= 16, got M=%lld", (long long)m);
+    if (n % 8 != 0 || n2 % 8 != 0) {
+        return fail(err, errlen, HQ_ERR_INVALID, "low_latency_mma_gemm weight rows must be divisible by 8, got %lld and %lld",
+                    (long long)n, (long long)n2);
+    }
+    if ((k1 + k2) % 256 != 0 || k1 % 128 != 0 || k2 % 128 != 0) {
+        return fail(err, errlen, HQ_ERR_INVALID, "low_latency_mma_gemm K must be divisible by 256, got K=%lld",
+                    (long long)(k1 + k2));
+    }
+    if (concat && k1 % 512 != 0) {
+        return fail(err, errlen, HQ_ERR_INVALID, "concat-K K1 must be a multiple of 512, got K1=%lld", (long long)k1);
+    }
+    const int64_t kb2 = dual ? k1 / 32 : k2 / 32;  // scale columns of sfb2
+    if (sfa_stride % 16 != 0 || sfb_stride % 16 != 0 || sfa_stride < k1 / 32 || sfb_stride < k1 / 32 ||
+        (concat && (sfa2_stride % 16 != 0 || sfa2_stride < k2 / 32)) ||
+        (second_weight && (sfb2_stride % 16 != 0 || sfb2_stride < kb2))) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "sfa / sfb / sfa2 / sfb2 must be plain row-major [rows, K / 32] scales "
+                    "(group_wise_quant(..., use_swizzle=False)) with a row stride that is a multiple of 16 bytes; "
+                    "got row strides %lld, %lld, %lld, %lld",
+                    (long long)sfa_stride, (long long)sfb_stride, (long long)sfa2_stride, (long long)sfb2_stride);
+    }
+    if (m == 0 || (n == 0 && n2 == 0) || k1 + k2 == 0) return HQ_OK;
+    const hq::DeviceGuard guard(device);
+    if (!guard.ok()) return fail(err, errlen, HQ_ERR_CUDA, "cannot select CUDA device %d", device);
+    const int sm_all = hq_sm_count(device);
+    const int sm = sm_count > 0 ? (sm_count < sm_all || sm_all == 0 ? sm_count : sm_all) : sm_all;
+    if (sm <= 0) return fail(err, errlen, HQ_ERR_CUDA, "cannot query the SM count of device %d", device);
+    if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || out == nullptr) {
+        return fail(err, errlen, HQ_ERR_INVALID, "null pointer argument");
+    }
+    if (!hq::aligned(out, 16) || (dual && !hq::aligned(out2, 16)) || ldo % 8 != 0 || ldo < n ||
+        (dual && (ldo2 % 8 != 0 || ldo2 < n2)) || !hq::aligned(sfa, 4) || !hq::aligned(sfb, 4) ||
+        !hq::aligned(sfa2, 4) || !hq::aligned(sfb2, 4)) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "outputs must be 16-byte aligned with a row stride that is a multiple of 8 elements, scales "
+                    "4-byte aligned");
+    }
+
+    using C = hq::Cfg<64, 0>;
+    const int a_rows = int((m + 7) / 8 * 8);
+    CUtensorMap tm_a, tm_b, tm_a2, tm_b2;
+    const void* const a_tail = concat ? a2 : a;
+    const int64_t k_tail = concat ? k2 : k1;
+    const void* const b_other = second_weight ? b2 : b;
+    const int64_t rows_other = dual ? n2 : n;
+    const bool maps_ok =
+        hq::make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a, uint64_t(k1), uint64_t(m), uint64_t(k1),
+                         hq::kBKBytes, uint32_t(a_rows), CU_TENSOR_MAP_SWIZZLE_128B) &&
+        hq::make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, b, uint64_t(k1), uint64_t(n > 0 ? n : 8), uint64_t(k1),
+                         hq::kBKBytes, 64, CU_TENSOR_MAP_SWIZZLE_128B) &&
+        hq::make_tmap_2d(&tm_a2, CU_TENSOR_MAP_DATA_TYPE_UINT8, a_tail, uint64_t(k_tail), uint64_t(m), uint64_t(k_tail),
+                         hq::kBKBytes, uint32_t(a_rows), CU_TENSOR_MAP_SWIZZLE_128B) &&
+        hq::make_tmap_2d(&tm_b2, CU_TENSOR_MAP_DATA_TYPE_UINT8, b_other, uint64_t(k_tail), uint64_t(rows_other),
+                         uint64_t(k_tail), hq::kBKBytes, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!maps_ok) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "TMA descriptor encoding failed: input and weight must be 16-byte aligned, contiguous rows");
+    }
+    hq::LlParams p;
+    p.sfa = static_cast<const uint8_t*>(sfa);
+    p.sfb = static_cast<const uint8_t*>(sfb);
+    p.sfa2 = static_cast<const uint8_t*>(concat ? sfa2 : sfa);
+    p.sfb2 = static_cast<const uint8_t*>(second_weight ? sfb2 : sfb);
+    p.sfa_stride = sfa_stride;
+    p.sfb_stride = sfb_stride;
+    p.sfa2_stride = concat ? sfa2_stride : sfa_stride;
+    p.sfb2_stride = second_weight ? sfb2_stride : sfb_stride;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.out2 = static_cast<__nv_bfloat16*>(out2);
+    p.ldo = ldo;
+    p.ldo2 = ldo2;
+    p.m = int(m);
+    p.n = int(n);
+    p.n2 = int(n2);
+    p.k_tiles1 = int(k1 / hq::kBKBytes);
+    p.k_tiles2 = int(k2 / hq::kBKBytes);
+    p.a_rows = a_rows;
+    p.sigmoid = use_sigmoid ? 1 : 0;
+
+    static std::once_flag once[16];
+    int dev = 0;
+    HQ_CUDA_TRY(cudaGetDevice(&dev));
+    cudaError_t attr_err = cudaSuccess;
+    std::call_once(once[dev & 15], [&] {
+        attr_err = cudaFuncSetAttribute(hq::ll_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    });
+    HQ_CUDA_TRY(attr_err);
+    const int tiles = int((n + 63) / 64 + (n2 + 63) / 64);
+    HQ_CUDA_TRY(hq::launch(hq::ll_gemm_kernel, dim3(std::min(sm, tiles)), dim3(hq::kLlThreads), size_t(C::kSmemBytes),
+                           static_cast<cudaStream_t>(stream), use_pdl != 0, 1, tm_a, tm_b, tm_a2, tm_b2, p));
+    return HQ_OK;
 }
 
 extern "C" int hq_device_status(int device, void* stream, uint32_t* status, char* err, size_t errlen) {

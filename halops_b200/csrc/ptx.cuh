@@ -112,6 +112,17 @@ __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
 
+// 4 bytes global -> shared, asynchronous (non-bulk); completion is tracked per thread
+// with cp_async_arrive_noinc.
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+// Arrives on `bar` (as one of its expected arrivals) once every cp.async this thread
+// has issued so far has landed.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 // 2-D tile, global -> shared, completion counted in bytes on `bar`.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, int x, int y,
                                             uint32_t bar) {

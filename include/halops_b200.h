@@ -214,6 +214,30 @@ int hq_group_contiguous_gemm(const void* a, const void* b, const void* sfa,
                              int64_t ldo, int mode, int sm_count, int use_pdl,
                              int device, void* stream, char* err, size_t errlen);
 
+/*
+ * Decode-sized MXFP8 GEMM (M <= 16) on scales in the PLAIN row-major layout
+ * ([rows, K / 32] bytes, row stride a multiple of 16 bytes: what hq_group_wise_quant writes
+ * with use_swizzle = 0), with two fused forms:
+ *   concat-K     (a2, b2, sfa2, sfb2 given, out2 NULL):  out = A . B^T + A2 . B2^T
+ *   dual output  (b2, sfb2, out2 given, a2 / sfa2 NULL): out = A . B^T and out2 = A . B2^T
+ * Replaces halops::LowLatencyMmaGemm (csrc/kernel/gemm/low_latency_mma_gemm.cu:23-76, checks
+ * of csrc/kernel/gemm/low_latency_utils.cuh:222-273; Python face
+ * halops/gemm/low_latency_mma_gemm.py:25-109).
+ *   a [M, K1] e4m3, b [N, K1] e4m3, contiguous, 16-byte aligned; N % 8 == 0; K1 + K2 a multiple
+ *   of 256 (each a multiple of 128); concat-K wants K1 % 512 == 0 as the reference does
+ *   sfa [M, K1/32], sfb [N, K1/32] UE8M0 bytes with the row strides given in bytes
+ *   out [M, N] bf16 (ldo elements between rows, ldo % 8 == 0); out2 [M, N2] likewise
+ *   use_sigmoid: write sigmoid(bf16(result)) instead (not with a2 / out2)
+ * K is not bounded by shared memory here (the reference keeps A resident and rejects large K).
+ */
+int hq_low_latency_gemm(const void* a, const void* b, const void* sfa, const void* sfb,
+                        void* out, const void* a2, const void* b2, const void* sfa2,
+                        const void* sfb2, void* out2, int64_t m, int64_t n, int64_t n2,
+                        int64_t k1, int64_t k2, int64_t sfa_stride, int64_t sfb_stride,
+                        int64_t sfa2_stride, int64_t sfb2_stride, int64_t ldo, int64_t ldo2,
+                        int use_sigmoid, int sm_count, int use_pdl, int device, void* stream,
+                        char* err, size_t errlen);
+
 /* Grouped kinds for hq_describe_group_tile. */
 enum { HQ_GROUP_BATCH = 1, HQ_GROUP_MASKED = 2, HQ_GROUP_CONTIGUOUS = 3 };
 

@@ -258,6 +258,43 @@ def test_group_gemm_rules_without_a_device(native):
     assert "mode=contiguous" in hq.describe_group_tile("contiguous", 16, 256, 7168, 3584)
 
 
+def test_low_latency_rules_without_a_device(native):
+    """Host checks of the plain-scale M <= 16 GEMM (texts of the reference's
+    tests/test_low_latency_mma_gemm.py:297-345)."""
+    import halops_b200 as hq
+
+    fake = ctypes.cast(16, ctypes.c_void_p)
+    f = native.lib().hq_low_latency_gemm
+
+    def rc(m, n, n2, k1, k2, strides=(128, 128, 128, 128), a2=None, b2=None, sfa2=None, sfb2=None, out2=None,
+           sigmoid=0):
+        err = ctypes.create_string_buffer(512)
+        code = f(None, None, None, None, None, a2, b2, sfa2, sfb2, out2, m, n, n2, k1, k2, *strides, n, n2, sigmoid,
+                 -1, 1, 0, None, err, len(err))
+        return code, err.value.decode()
+
+    assert "supports M <= 16, got M=17" in rc(17, 512, 0, 4096, 0)[1]
+    assert "weight rows must be divisible by 8, got 516 and 0" in rc(8, 516, 0, 256, 0, strides=(16, 16, 0, 0))[1]
+    assert "K must be divisible by 256, got K=1152" in rc(8, 512, 0, 1152, 0, strides=(48, 48, 0, 0))[1]
+    assert "plain row-major" in rc(8, 512, 0, 1024, 0, strides=(36, 32, 0, 0))[1]
+    assert "weight2 / sfb2 must come with" in rc(8, 512, 0, 2048, 0, b2=fake, sfb2=fake)[1]
+    assert "does not support input2 or output2" in rc(8, 512, 512, 2048, 0, b2=fake, sfb2=fake, out2=fake, sigmoid=1)[1]
+    assert "K1 must be a multiple of 512, got K1=1920" in rc(8, 512, 0, 1920, 2176, a2=fake, b2=fake, sfa2=fake,
+                                                             sfb2=fake)[1]
+    assert rc(0, 512, 0, 1024, 0, strides=(32, 32, 0, 0))[0] == 0  # no rows: nothing to do
+
+    x = torch.empty([8, 1024], dtype=torch.float8_e4m3fn)
+    w = torch.empty([512, 1024], dtype=torch.float8_e4m3fn)
+    sfa, sfb = torch.empty([8, 32], dtype=torch.uint8), torch.empty([512, 32], dtype=torch.uint8)
+    out = torch.empty([8, 512], dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="plain row-major"):
+        hq.low_latency_mma_gemm(x, w, torch.empty([128, 32], dtype=torch.uint8), sfb, out)
+    with pytest.raises(RuntimeError, match="supports M <= 16"):
+        hq.low_latency_mma_gemm(torch.empty([17, 1024], dtype=torch.float8_e4m3fn), w, sfa, sfb, out)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        hq.low_latency_mma_gemm(x, w, sfa, sfb, out)
+
+
 def test_enum_and_interleave():
     import halops_b200 as hq
 
