@@ -42,6 +42,9 @@ SIGNATURES = {
     "hq_group_contiguous_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_int,
                                          c_int, c_int, c_void_p, c_char_p, c_size_t]),
+    "hq_batch_gemm_quant": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_i64,
+                                    c_void_p, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_int,
+                                    c_int, c_int, c_void_p, c_char_p, c_size_t]),
     "hq_low_latency_gemm": (c_int, [c_void_p] * 10 + [c_i64] * 11 + [c_int, c_int, c_int, c_int, c_void_p, c_char_p,
                                                              c_size_t]),
     "hq_describe_group_tile": (c_int, [c_int, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_int, c_int, c_char_p,

@@ -268,14 +268,16 @@ __device__ __forceinline__ uint32_t instr_desc(uint32_t sf_id) {
 
 // Parameters of the SiTU-GLU quantising epilogue (all zero for the other epilogues).
 struct SituParams {
-    uint8_t* q;       // [M, N/2] e4m3 output
+    uint8_t* q;       // e4m3 output: [M, N/2] (SituQuant) or [M, B * N] (the batch Quant epilogues)
     uint8_t* sf;      // UE8M0 scales of the output, SfAtom order, kb_out scale columns
     int64_t ldq;      // bytes between output rows
-    int kb_out;       // N / 2 / 32
+    int kb_out;       // scale columns of the output: N / 2 / 32 or B * N / 32
     float beta;       // gate soft-cap
     float inv_beta;
     float lin;        // up soft-cap, 0 = none
     float inv_lin;
+    const __nv_bfloat16* gate;  // [M, B * N] multiplier of the GateMulQuant epilogues (logits for the sigmoid form)
+    int64_t gate_ld;            // elements between its rows
 };
 
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -642,6 +644,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 const int row = m0 + ar;
                 const int col = n0 + c * kEpiChunk;
                 if (warp_idle) continue;
+                if (epi_op == HQ_EPILOGUE_QUANT || epi_op == HQ_EPILOGUE_GATE_MUL_QUANT ||
+                    epi_op == HQ_EPILOGUE_SIGMOID_GATE_MUL_QUANT) {
+                    // The bf16 result (times the gate, as a bf16 product) re-quantised to MXFP8 per
+                    // 32 columns: the reference's batch epilogues (csrc/kernel/gemm/epilogue.cuh:990-1051).
+                    if (row_ok) {
+                        if (epi_op != HQ_EPILOGUE_QUANT) {
+                            const uint4* const gp =
+                                reinterpret_cast<const uint4*>(situ.gate + int64_t(row) * situ.gate_ld + col);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint4 gq = __ldg(gp + j);
+                                uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    if (epi_op == HQ_EPILOGUE_SIGMOID_GATE_MUL_QUANT) {
+                                        const float lo = fmaf(0.5f, tanh_fast(0.5f * __uint_as_float(gw[i] << 16)), 0.5f);
+                                        const float hi =
+                                            fmaf(0.5f, tanh_fast(0.5f * __uint_as_float(gw[i] & 0xffff0000u)), 0.5f);
+                                        const __nv_bfloat162 sg = __float22bfloat162_rn(make_float2(lo, hi));
+                                        gw[i] = *reinterpret_cast<const uint32_t*>(&sg);
+                                    }
+                                    const __nv_bfloat162 prod =
+                                        __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&p[4 * j + i]),
+                                                *reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
+                                    p[4 * j + i] = *reinterpret_cast<const uint32_t*>(&prod);
+                                }
+                            }
+                        }
+                        uint4 lo, hi;
+                        const uint32_t e = quant32_bf16(p, lo, hi);
+                        const int kb = col >> 5;
+                        uint4* const dst = reinterpret_cast<uint4*>(situ.q + int64_t(row) * situ.ldq + col);
+                        dst[0] = lo;
+                        dst[1] = hi;
+                        situ.sf[(int64_t(row >> 7) * (situ.kb_out >> 2) + (kb >> 2)) * 512 + (row & 31) * 16 +
+                                ((row >> 5) & 3) * 4 + (kb & 3)] = uint8_t(e);
+                    }
+                    continue;
+                }
                 if (reg_store) {
                     if (row_ok) {
                         uint4* dst = reinterpret_cast<uint4*>(out + int64_t(row) * ldo + col);
@@ -1383,7 +1424,10 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
                      uint64_t(g.k_bytes), kBKBytes, BN, CU_TENSOR_MAP_SWIZZLE_128B) &&
         // (the quantising epilogue stores from registers; its map only has to be valid)
         make_tmap_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out,
-                     uint64_t(g.epi_op == HQ_EPILOGUE_SITU_QUANT ? g.n / 4 : out_cols), uint64_t(out_rows),
+                     uint64_t(g.epi_op == HQ_EPILOGUE_SITU_QUANT ? g.n / 4
+                              : (g.epi_op == HQ_EPILOGUE_IDENTITY || g.epi_op == HQ_EPILOGUE_SIGMOID) ? out_cols
+                                                                                                       : out_cols / 2),
+                     uint64_t(out_rows),
                      uint64_t(g.ldo) * 2, kEpiChunk, 32, CU_TENSOR_MAP_SWIZZLE_64B);
     if (!maps_ok) {
         return fail(err, errlen, HQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the GEMM operands");
@@ -1767,7 +1811,7 @@ extern "C" int hq_dense_gemm_situ_quant(const void* a, const void* b, const void
                         "output_sf must hold whole 128-row SfAtoms: expected at least %lld bytes, got %lld",
                         (long long)(hq_sf_rows(m) * kb_out), (long long)out_sf_bytes);
     }
-    hq::SituParams sp;
+    hq::SituParams sp{};
     sp.q = static_cast<uint8_t*>(out_q);
     sp.sf = static_cast<uint8_t*>(out_sf);
     sp.ldq = n / 2;
@@ -1817,8 +1861,8 @@ int no_group_tile(char* err, size_t errlen, int kind, int mode, int64_t rows, in
 int grouped_gemm_impl(int kind, const void* a, const void* b, const void* sfa, const void* sfb, void* out,
                       const void* bias, const float* alpha, const int* table, int64_t count, int64_t rows,
                       int64_t total_m, int64_t n, int64_t k, int64_t sfa_bytes, int64_t sfb_bytes, int64_t ldo,
-                      int mode, int epilogue, int sm_count, int use_pdl, int device, void* stream, char* err,
-                      size_t errlen) {
+                      int mode, int epilogue, const SituParams* quant, int sm_count, int use_pdl, int device,
+                      void* stream, char* err, size_t errlen) {
     const bool batch = kind == kGroupBatch;
     const char* const per = batch ? "per-batch" : "per-expert";
     const int group = hq_group_size(mode);
@@ -1830,8 +1874,14 @@ int grouped_gemm_impl(int kind, const void* a, const void* b, const void* sfa, c
         k > INT32_MAX) {
         return fail(err, errlen, HQ_ERR_INVALID, "problem sizes must be non-negative and below 2^31");
     }
-    if (epilogue != HQ_EPILOGUE_IDENTITY) {
+    const bool quant_epi = epilogue == HQ_EPILOGUE_QUANT || epilogue == HQ_EPILOGUE_GATE_MUL_QUANT ||
+                           epilogue == HQ_EPILOGUE_SIGMOID_GATE_MUL_QUANT;
+    if (epilogue != HQ_EPILOGUE_IDENTITY && !(quant_epi && quant != nullptr && batch && mode == HQ_MODE_W8A8_MXFP8)) {
         return fail(err, errlen, HQ_ERR_UNSUPPORTED, "Unsupported epilogue %d for %s", epilogue, mode_name(mode));
+    }
+    if (quant_epi) {
+        out = quant->q;
+        ldo = quant->ldq / 2;
     }
     if (bias != nullptr && mode != HQ_MODE_W8A8_MXFP8) {
         return fail(err, errlen, HQ_ERR_INVALID,
@@ -1881,7 +1931,7 @@ int grouped_gemm_impl(int kind, const void* a, const void* b, const void* sfa, c
     }
     const int64_t out_cols = batch ? count * n : n;
     if (!aligned(a, 16) || !aligned(b, 16) || !aligned(sfa, 16) || !aligned(sfb, 16) || !aligned(out, 16) ||
-        !aligned(table, 4) || ldo < out_cols || ldo % 8 != 0) {
+        !aligned(table, 4) || ldo < (quant_epi ? out_cols / 2 : out_cols) || ldo % 8 != 0) {
         return fail(err, errlen, HQ_ERR_INVALID,
                     "operands, scales and output must be 16-byte aligned and the output row stride a "
                     "multiple of 8 elements");
@@ -1896,7 +1946,7 @@ int grouped_gemm_impl(int kind, const void* a, const void* b, const void* sfa, c
     g.alpha = alpha;
     g.bias = static_cast<const __nv_bfloat16*>(bias);
     g.epi_op = epilogue;
-    g.situ = SituParams{};
+    g.situ = quant_epi ? *quant : SituParams{};
     g.out = static_cast<__nv_bfloat16*>(out);
     g.ldo = ldo;
     g.m = int(total_m);
@@ -1953,8 +2003,52 @@ extern "C" int hq_batch_gemm(const void* a, const void* b, const void* sfa, cons
                              int64_t k, int64_t sfa_bytes, int64_t sfb_bytes, int64_t ldo, int mode, int epilogue,
                              int sm_count, int use_pdl, int device, void* stream, char* err, size_t errlen) {
     return hq::grouped_gemm_impl(hq::kGroupBatch, a, b, sfa, sfb, out, bias, alpha, nullptr, batches, m,
-                                 batches * m, n, k, sfa_bytes, sfb_bytes, ldo, mode, epilogue, sm_count, use_pdl,
+                                 batches * m, n, k, sfa_bytes, sfb_bytes, ldo, mode, epilogue, nullptr, sm_count, use_pdl,
                                  device, stream, err, errlen);
+}
+
+extern "C" int hq_batch_gemm_quant(const void* a, const void* b, const void* sfa, const void* sfb, void* out_q,
+                                   void* out_sf, const void* gate, int64_t gate_ld, const void* bias,
+                                   int64_t batches, int64_t m, int64_t n, int64_t k, int64_t sfa_bytes,
+                                   int64_t sfb_bytes, int64_t ldq, int64_t out_sf_bytes, int epilogue, int sm_count,
+                                   int use_pdl, int device, void* stream, char* err, size_t errlen) {
+    using hq::fail;
+    const bool gated = epilogue == HQ_EPILOGUE_GATE_MUL_QUANT || epilogue == HQ_EPILOGUE_SIGMOID_GATE_MUL_QUANT;
+    if (epilogue != HQ_EPILOGUE_QUANT && !gated) {
+        return fail(err, errlen, HQ_ERR_INVALID, "Unsupported epilogue %d for w8a8-mxfp8", epilogue);
+    }
+    if (n % 128 != 0) {
+        return fail(err, errlen, HQ_ERR_INVALID, "quantized output needs N %% 128 == 0, got %lld", (long long)n);
+    }
+    if (gated && gate == nullptr) return fail(err, errlen, HQ_ERR_INVALID, "GateMulQuant epilogues need gate");
+    if (batches < 0 || m < 0 || n < 0 || batches * n > INT32_MAX) {
+        return fail(err, errlen, HQ_ERR_INVALID, "input must be a 3D tensor of shape [B, M, K]");
+    }
+    const int64_t kb_out = batches * n / 32;
+    if (batches > 0 && m > 0 && n > 0) {
+        if (out_q == nullptr || out_sf == nullptr || out_sf_bytes < hq_sf_rows(m) * kb_out) {
+            return fail(err, errlen, HQ_ERR_INVALID,
+                        "output_sf must hold whole 128-row SfAtoms: expected at least %lld bytes, got %lld",
+                        (long long)(hq_sf_rows(m) * kb_out), (long long)out_sf_bytes);
+        }
+        if (ldq % 16 != 0 || ldq < batches * n || !hq::aligned(out_q, 16)) {
+            return fail(err, errlen, HQ_ERR_INVALID,
+                        "the quantized output must be 16-byte aligned with a row stride that is a multiple of 16");
+        }
+        if (gated && (!hq::aligned(gate, 32) || gate_ld * 2 % 32 != 0 || gate_ld < batches * n)) {
+            return fail(err, errlen, HQ_ERR_INVALID, "gate rows must be contiguous and 32-byte aligned");
+        }
+    }
+    hq::SituParams sp{};
+    sp.q = static_cast<uint8_t*>(out_q);
+    sp.sf = static_cast<uint8_t*>(out_sf);
+    sp.ldq = ldq;
+    sp.kb_out = int(kb_out);
+    sp.gate = static_cast<const __nv_bfloat16*>(gate);
+    sp.gate_ld = gate_ld;
+    return hq::grouped_gemm_impl(hq::kGroupBatch, a, b, sfa, sfb, out_q, bias, nullptr, nullptr, batches, m,
+                                 batches * m, n, k, sfa_bytes, sfb_bytes, ldq / 2, HQ_MODE_W8A8_MXFP8, epilogue, &sp,
+                                 sm_count, use_pdl, device, stream, err, errlen);
 }
 
 extern "C" int hq_group_masked_gemm(const void* a, const void* b, const void* sfa, const void* sfb,
@@ -1968,7 +2062,7 @@ extern "C" int hq_group_masked_gemm(const void* a, const void* b, const void* sf
     }
     return hq::grouped_gemm_impl(hq::kGroupMasked, a, b, sfa, sfb, out, bias, alpha, masked_m, num_experts,
                                  max_m_per_expert, num_experts * max_m_per_expert, n, k, sfa_bytes, sfb_bytes,
-                                 ldo, mode, HQ_EPILOGUE_IDENTITY, sm_count, use_pdl, device, stream, err, errlen);
+                                 ldo, mode, HQ_EPILOGUE_IDENTITY, nullptr, sm_count, use_pdl, device, stream, err, errlen);
 }
 
 extern "C" int hq_group_contiguous_gemm(const void* a, const void* b, const void* sfa, const void* sfb,
@@ -1982,7 +2076,7 @@ extern "C" int hq_group_contiguous_gemm(const void* a, const void* b, const void
         return hq::no_group_tile(err, errlen, hq::kGroupContiguous, mode, rows, m, n, k);
     }
     return hq::grouped_gemm_impl(hq::kGroupContiguous, a, b, sfa, sfb, out, bias, alpha, expert_ids, num_experts,
-                                 rows, m, n, k, sfa_bytes, sfb_bytes, ldo, mode, HQ_EPILOGUE_IDENTITY, sm_count,
+                                 rows, m, n, k, sfa_bytes, sfb_bytes, ldo, mode, HQ_EPILOGUE_IDENTITY, nullptr, sm_count,
                                  use_pdl, device, stream, err, errlen);
 }
 

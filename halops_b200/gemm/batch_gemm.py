@@ -2,8 +2,8 @@
 ``halops.batch_gemm`` (``halops/gemm/batch_gemm.py:27-117``; host checks of
 ``csrc/kernel/gemm/batch_gemm.cu:22-188``), executed by this package's tcgen05
 kernel through the C ABI.  Built: the Identity epilogue for ``w8a8-mxfp8``
-(optional per-batch bias), ``w4a4-nvfp4`` (per-batch alpha) and ``w4a4-mxfp4``.
-The quantising epilogues (Quant, GateMulQuant, SigmoidGateMulQuant) raise."""
+(optional per-batch bias), ``w4a4-nvfp4`` (per-batch alpha) and ``w4a4-mxfp4``, and the
+quantising epilogues (Quant, GateMulQuant, SigmoidGateMulQuant) for ``w8a8-mxfp8``."""
 
 from __future__ import annotations
 
@@ -46,13 +46,19 @@ def batch_gemm(
             (``group_wise_quant`` of the ``[B*M, K]`` view).
         sfb: uint8 SfAtom scales per batch, ``[B, N, sf_k]`` with N a multiple of 128
             (``[B, ceil(N/128)*128, sf_k]`` otherwise).
-        output: [M, B*N] bfloat16, written in place; rows may be strided.
+        output: [M, B*N] bfloat16 (float8_e4m3fn for the quantising epilogues), written in
+            place; rows may be strided.
         bias: optional [B, N] bfloat16, ``w8a8-mxfp8`` only.
         alpha: float32 [B]; required for ``w4a4-nvfp4``, rejected for ``w4a4-mxfp4``,
             ignored for ``w8a8-mxfp8``.
         sm_count: SMs to use (-1: all).
-        epilogue: only ``EpilogueOp.Identity`` is built.
-        output_sf, gate: operands of the quantising epilogues; must be None.
+        epilogue: ``EpilogueOp.Identity``, or for ``w8a8-mxfp8`` ``EpilogueOp.Quant``,
+            ``EpilogueOp.GateMulQuant`` or ``EpilogueOp.SigmoidGateMulQuant``: the bfloat16 result
+            (times ``gate``, or times ``bf16(sigmoid(gate))``) re-quantised to MXFP8 per 32 columns.
+        output_sf: UE8M0 SfAtom scales of the quantised output over ``[M, B*N/32]``
+            (``ceil(M/128)*128 * B*N/32`` bytes; N a multiple of 128).
+        gate: [M, B*N] bfloat16 (logits for the sigmoid form); rows may be strided
+            (``stride(1) == 1``, 32-byte aligned row starts).
         use_pdl: launch with programmatic stream serialisation.
     """
     _check(
@@ -95,8 +101,46 @@ def batch_gemm(
         )
         if not mxfp4:
             _check(alpha is not None, "W4A4-nvfp4 mode requires alpha input (per-batch scaling).")
-    _check(epilogue == EpilogueOp.Identity and output_sf is None and gate is None,
+    quant_ops = (EpilogueOp.Quant, EpilogueOp.GateMulQuant, EpilogueOp.SigmoidGateMulQuant)
+    _check(epilogue == EpilogueOp.Identity or (fp8 and epilogue in quant_ops),
            f"Unsupported epilogue {int(epilogue)} for {mode}")
+    if epilogue in quant_ops:
+        _check(n % 128 == 0, f"quantized output needs N % 128 == 0, got {n}")
+        _check(output.dtype == torch.float8_e4m3fn and output.stride(1) == 1,
+               "output must be a float8_e4m3fn tensor with contiguous rows for the quantising epilogues")
+        _check(output_sf is not None and output_sf.dtype == torch.uint8 and output_sf.is_contiguous(),
+               "the quantising epilogues need a contiguous uint8 output_sf")
+        gate_ptr, gate_ld = None, 0
+        if epilogue != EpilogueOp.Quant:
+            _check(gate.dtype == torch.bfloat16 and tuple(gate.shape) == tuple(output.shape),
+                   "gate must be a bfloat16 [M, B * N] tensor")
+            _check(gate.stride(1) == 1 and gate.stride(0) * 2 % 32 == 0 and gate.data_ptr() % 32 == 0,
+                   "gate rows must be contiguous and 32-byte aligned")
+            gate_ptr, gate_ld = gate.data_ptr(), gate.stride(0)
+        _check(input.is_contiguous() and weight.is_contiguous() and sfa.is_contiguous() and sfb.is_contiguous(),
+               "input, weight, sfa and sfb must be contiguous")
+        if batches == 0 or m == 0 or n == 0:
+            return
+        _native.call("hq_describe_group_tile", 1, batches, m, batches * m, n, k, _native.MODE_IDS[mode], 148, -1)
+        bias_ptr = None
+        if bias is not None:
+            _check(bias.dtype == torch.bfloat16 and bias.numel() == batches * n and bias.is_contiguous(),
+                   f"bias must be a contiguous bfloat16 [B, N] tensor of {batches * n} elements")
+            bias_ptr = bias.data_ptr()
+        tensors = [("input", input), ("weight", weight), ("sfa", sfa), ("sfb", sfb), ("output", output),
+                   ("output_sf", output_sf)] + ([("gate", gate)] if gate_ptr else []) \
+            + ([("bias", bias)] if bias is not None else [])
+        for name, t in tensors:
+            _check(t.is_cuda, f"{name} must be a CUDA tensor (this library has no CPU path)")
+        _native.call(
+            "hq_batch_gemm_quant",
+            input.data_ptr(), weight.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), output.data_ptr(),
+            output_sf.data_ptr(), gate_ptr, gate_ld, bias_ptr, batches, m, n, k, sfa.numel(), sfb.numel(),
+            output.stride(0), output_sf.numel(), int(epilogue), int(sm_count), int(bool(use_pdl)),
+            input.device.index, torch.cuda.current_stream(input.device).cuda_stream,
+        )
+        return
+    _check(output_sf is None and gate is None, "output_sf and gate belong to the quantising epilogues")
     _check(output.dtype == torch.bfloat16, "output must be a bfloat16 tensor")
     _check(input.is_contiguous() and weight.is_contiguous() and sfa.is_contiguous() and sfb.is_contiguous(),
            "input, weight, sfa and sfb must be contiguous")

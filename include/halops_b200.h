@@ -162,7 +162,7 @@ int hq_dense_gemm_situ_quant(const void* a, const void* b, const void* sfa,
  * A 128-row tile of the stacked rows that straddles two batches is worked once per
  * batch (csrc/kernel/gemm/gemm_dispatch.cuh:90-93); every output element is written
  * exactly once.  The quantising epilogues of the reference (Quant, GateMulQuant,
- * SigmoidGateMulQuant) return HQ_ERR_UNSUPPORTED.
+ * SigmoidGateMulQuant) have their own entry, hq_batch_gemm_quant.
  */
 int hq_batch_gemm(const void* a, const void* b, const void* sfa, const void* sfb,
                   void* out, const void* bias, const float* alpha,
@@ -240,6 +240,26 @@ int hq_low_latency_gemm(const void* a, const void* b, const void* sfa, const voi
 
 /* Grouped kinds for hq_describe_group_tile. */
 enum { HQ_GROUP_BATCH = 1, HQ_GROUP_MASKED = 2, HQ_GROUP_CONTIGUOUS = 3 };
+
+/*
+ * Batch GEMM with a quantising epilogue (MXFP8 operands): with y = bf16(A[b] . B[b]^T + bias[b]),
+ *   HQ_EPILOGUE_QUANT                   v = y
+ *   HQ_EPILOGUE_GATE_MUL_QUANT          v = y * gate                 (bf16 product)
+ *   HQ_EPILOGUE_SIGMOID_GATE_MUL_QUANT  v = y * bf16(sigmoid(gate))
+ * out_q[M, batches * N] = e4m3(v * 2^(127 - e)) per 32 columns, e = UE8M0 exponent of the group's
+ * bf16 amax (the exact-integer recipe of csrc/common/mx_quant.cuh:60-71), written to out_sf in
+ * SfAtom order over [M, batches * N / 32] (hq_sf_rows(M) * batches * N / 32 bytes; padding rows
+ * are left untouched).  Replaces halops::BatchGemm with those epilogues
+ * (csrc/kernel/gemm/batch_gemm.cu:60-133, csrc/kernel/gemm/epilogue.cuh:990-1051).
+ *   N % 128 == 0; ldq = bytes between rows of out_q (multiple of 16)
+ *   gate [M, batches * N] bf16, gate_ld elements between rows, rows 32-byte aligned; NULL for QUANT
+ */
+int hq_batch_gemm_quant(const void* a, const void* b, const void* sfa, const void* sfb,
+                        void* out_q, void* out_sf, const void* gate, int64_t gate_ld,
+                        const void* bias, int64_t batches, int64_t m, int64_t n, int64_t k,
+                        int64_t sfa_bytes, int64_t sfb_bytes, int64_t ldq,
+                        int64_t out_sf_bytes, int epilogue, int sm_count, int use_pdl,
+                        int device, void* stream, char* err, size_t errlen);
 
 /* hq_describe_tile for the grouped GEMMs: the tile picked for `count` weights with
  * `rows` rows each (batch, masked: the slot; contiguous: M / num_experts) and `total_m`

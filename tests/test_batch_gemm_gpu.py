@@ -175,10 +175,10 @@ def test_fp4_errors(hq):
         hq.batch_gemm(xq, wq, sfa, sfb, out, bias, None, -1, "w4a4-mxfp4")
 
 
-def test_quantising_epilogues_raise(hq):
+def test_other_epilogues_raise(hq):
     x, w, sfa, sfb, out = _empty()
-    with pytest.raises(RuntimeError, match="Unsupported epilogue 1"):
-        hq.batch_gemm(x, w, sfa, sfb, out, epilogue=hq.EpilogueOp.Quant)
+    with pytest.raises(RuntimeError, match="Unsupported epilogue 3"):
+        hq.batch_gemm(x, w, sfa, sfb, out, epilogue=hq.EpilogueOp.Sigmoid)
     with pytest.raises(RuntimeError, match="GateMulQuant epilogues need gate"):
         hq.batch_gemm(x, w, sfa, sfb, out, epilogue=hq.EpilogueOp.GateMulQuant)
 
@@ -209,3 +209,100 @@ def test_golden_fixture(hq, golden_dir, mode):
     n = w.shape[1]
     for b in range(x.shape[0]):
         torch.testing.assert_close(out[:, b * n:(b + 1) * n].float().cpu(), ref[b], **tol)
+
+
+def _ref_quant_e4m3(v):
+    """Per-32-column MXFP8 model of the quantising epilogues: e4m3 codes and UE8M0 exponents
+    (the reference's ``ref_quant_e4m3``, tests/test_batch_gemm.py:389-396)."""
+    g = v.float().unflatten(-1, (-1, 32))
+    amax = g.abs().amax(-1).clamp_min(1e-10)
+    mant, exp = torch.frexp(amax)
+    e = (exp - 9 + (mant > 0.875).int() + 127).clamp(0, 254)
+    q = (g * torch.exp2(127 - e.float())[..., None]).flatten(-2)
+    return q.to(torch.float8_e4m3fn).view(torch.uint8), e.to(torch.uint8)
+
+
+def _quant_run(hq, args, m, cols, op, gate):
+    out = torch.empty([m, cols], dtype=torch.float8_e4m3fn, device="cuda")
+    out_sf = torch.zeros([(m + 127) // 128 * 128 * cols // 32], dtype=torch.uint8, device="cuda")
+    hq.batch_gemm(*args, out, None, None, -1, "w8a8-mxfp8", op, out_sf, gate)
+    assert hq.device_status() == 0
+    return out.view(torch.uint8), out_sf
+
+
+@pytest.mark.parametrize("with_gate", [False, True], ids=["quant", "gate_mul"])
+@pytest.mark.parametrize("b,m,n,k", [(3, 200, 256, 128), (8, 200, 1024, 2048), (2, 128, 128, 256)],
+                         ids=lambda v: str(v))
+def test_e4m3_out(hq, b, m, n, k, with_gate):
+    """The e4m3 output and its scales equal the bf16 output (times gate) quantised per 32
+    columns, bit for bit; scale padding is left untouched (tests/test_batch_gemm.py:399-434)."""
+    import numpy as np
+
+    xq, wq, sfa, sfb = _inputs(hq, b, m, n, k, "w8a8-mxfp8", seed=11)
+    args = (xq, wq, sfa, sfb)
+    y = _run(hq, *args, "w8a8-mxfp8")
+    gate = None
+    if with_gate:
+        gate = (torch.rand([m, b * n], generator=torch.Generator().manual_seed(12)) * 2 - 0.5).to(torch.bfloat16).cuda()
+    ref_q, ref_sf = _ref_quant_e4m3((y * gate if with_gate else y).cpu())
+    op = hq.EpilogueOp.GateMulQuant if with_gate else hq.EpilogueOp.Quant
+    q, sf = _quant_run(hq, args, m, b * n, op, gate)
+    assert torch.equal(q.cpu(), ref_q)
+    idx = torch.from_numpy(oracle.sf_atom_offsets(m, b * n // 32))
+    assert torch.equal(sf.cpu()[idx], ref_sf)
+    pad = torch.ones(sf.numel(), dtype=torch.bool)
+    pad[idx.flatten()] = False
+    assert (sf.cpu()[pad] == 0).all()
+    q2, sf2 = _quant_run(hq, args, m, b * n, op, gate)
+    assert torch.equal(q, q2) and torch.equal(sf, sf2)
+    del np
+
+
+@pytest.mark.parametrize("b,m,n,k", [(3, 200, 256, 128), (8, 200, 1024, 2048)], ids=lambda v: str(v))
+def test_sigmoid_gate_mul_quant(hq, b, m, n, k):
+    """A gate read in place from a column slice of a wider tensor equals its contiguous copy;
+    SigmoidGateMulQuant on logits matches GateMulQuant on bf16(sigmoid(logits)) up to the
+    sigmoid's rounding: codes within 1 where the scale matches, at most 0.1 % of the scales
+    off by one (tests/test_batch_gemm.py:447-482)."""
+    xq, wq, sfa, sfb = _inputs(hq, b, m, n, k, "w8a8-mxfp8", seed=13)
+    args = (xq, wq, sfa, sfb)
+    cols = b * n
+    wide = (torch.randn([m, 3 * cols], generator=torch.Generator().manual_seed(14)) * 3).to(torch.bfloat16).cuda()
+    logits = wide[:, cols:2 * cols]
+    q, sf = _quant_run(hq, args, m, cols, hq.EpilogueOp.GateMulQuant, logits)
+    ref_q, ref_sf = _quant_run(hq, args, m, cols, hq.EpilogueOp.GateMulQuant, logits.contiguous())
+    assert torch.equal(q, ref_q) and torch.equal(sf, ref_sf)
+
+    q, sf = _quant_run(hq, args, m, cols, hq.EpilogueOp.SigmoidGateMulQuant, logits)
+    gate = torch.sigmoid(logits.float()).to(torch.bfloat16)
+    ref_q, ref_sf = _quant_run(hq, args, m, cols, hq.EpilogueOp.GateMulQuant, gate)
+    sf_diff = (sf.int() - ref_sf.int()).abs().cpu()
+    assert sf_diff.max() <= 1 and (sf_diff > 0).float().mean() <= 1e-3
+    idx = torch.from_numpy(oracle.sf_atom_offsets(m, cols // 32))
+    same_scale = (sf_diff[idx] == 0).repeat_interleave(32, -1)
+
+    def ordered(t):
+        i = t.cpu().view(torch.int8).to(torch.int32)
+        return torch.where(i < 0, -(i & 127), i)
+
+    code_diff = (ordered(q) - ordered(ref_q)).abs()
+    assert code_diff[same_scale].max() <= 1
+
+
+def test_quant_epilogue_rules(hq):
+    x, w, sfa, sfb, out = _empty()
+    q = torch.empty([128, 512], dtype=torch.float8_e4m3fn, device="cuda")
+    sf = torch.zeros([128 * 16], dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError, match="float8_e4m3fn"):
+        hq.batch_gemm(x, w, sfa, sfb, out, epilogue=hq.EpilogueOp.Quant, output_sf=sf)
+    with pytest.raises(RuntimeError, match="need a contiguous uint8 output_sf"):
+        hq.batch_gemm(x, w, sfa, sfb, q, epilogue=hq.EpilogueOp.Quant)
+    with pytest.raises(RuntimeError, match="output_sf must hold whole 128-row SfAtoms"):
+        hq.batch_gemm(x, w, sfa, sfb, q, epilogue=hq.EpilogueOp.Quant, output_sf=sf[:100])
+    gate = torch.zeros([128, 512 + 8], dtype=torch.bfloat16, device="cuda")[:, 8:]
+    with pytest.raises(RuntimeError, match="32-byte aligned"):
+        hq.batch_gemm(x, w, sfa, sfb, q, epilogue=hq.EpilogueOp.GateMulQuant, output_sf=sf, gate=gate)
+    xq, wq, sfa4, sfb4 = _inputs(hq, 2, 128, 256, 256, "w4a4-nvfp4")
+    alpha = torch.ones([2], dtype=torch.float32, device="cuda")
+    with pytest.raises(RuntimeError, match="Unsupported epilogue 1 for w4a4-nvfp4"):
+        hq.batch_gemm(xq, wq, sfa4, sfb4, q, None, alpha, -1, "w4a4-nvfp4", hq.EpilogueOp.Quant, sf)
