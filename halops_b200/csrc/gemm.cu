@@ -101,6 +101,7 @@ struct Barriers {
     uint64_t overlap_free[2];
     uint64_t sf_ready[4];  // pair kernel: the scale copies of a k-tile have landed
     uint64_t turn[2];      // pair kernel: hands the MMA issue from one issuer thread to the other
+    uint64_t recv_full;    // split-K: the other CTA's partial sums have landed in this CTA's buffer
     uint32_t tmem_base;
     uint32_t abort;
 };
@@ -187,8 +188,11 @@ struct WorkIter {
     int walk_group = 0;  // batch / masked: group of the last item and the number of
     int walk_base = 0;   //   (group, row tile) pairs before it
 
-    __device__ WorkIter(const GroupParams& grp, int m, int n, int tm, int tn)
-        : g(grp), M(m), N(n), tiles_m(tm), tiles_n(tn), tile(blockIdx.x) {}
+    int stride;          // work items between two items of this CTA (or cluster)
+
+    __device__ WorkIter(const GroupParams& grp, int m, int n, int tm, int tn, int first = blockIdx.x,
+                        int step = gridDim.x)
+        : g(grp), M(m), N(n), tiles_m(tm), tiles_n(tn), tile(first), stride(step) {}
 
     __device__ __forceinline__ void set_b(Work& w, int group, int nt) const {
         w.group = group;
@@ -223,7 +227,7 @@ struct WorkIter {
                 }
             }
             set_b(w, group, tc.n);
-            if (pass == 0) tile += gridDim.x;
+            if (pass == 0) tile += stride;
             return true;
         }
         // batch / masked: item = (group, j-th row tile that holds valid rows of it, n tile)
@@ -250,7 +254,7 @@ struct WorkIter {
             w.out_row0 = w.a_row0;
             w.out_col0 = nt * BN;
         }
-        tile += gridDim.x;
+        tile += stride;
         return true;
     }
 };
@@ -395,7 +399,11 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], uint32_t
     }
 }
 
-template <int BN, int KIND>
+// kSplitK (64-wide tiles, one row of tiles, at most half as many tiles as SMs): a cluster of
+// two CTAs works one tile, each half of the k-tiles; the second CTA sends its fp32 partial
+// sums through distributed shared memory into a 32 KB buffer of the first (carved out of the
+// last two A stages), which adds them to its accumulator before the usual epilogue.
+template <int BN, int KIND, bool kSplitK = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_d, const uint8_t* __restrict__ sfa,
@@ -404,11 +412,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             int M, int N, int k_tiles, int kq_dim, int tiles_m, int tiles_n, int a_rows, int direct_store,
             const GroupParams grp, const SituParams situ) {
     using C = Cfg<BN, KIND>;
+    static_assert(!kSplitK || (BN == 64 && 2 * C::kABytes == kBM * BN * 4 && C::kStages >= 6), "split-K buffer");
+    // stages of the ring; with split-K the last two A stages hold the partial sums received
+    constexpr uint32_t kRing = kSplitK ? C::kStages - 2 : C::kStages;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle of the operand tiles
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* const smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
     const uint32_t a_base = smem_base;
+    const uint32_t recv_base = a_base + kRing * C::kABytes;
+    const uint32_t k_rank = kSplitK ? ptx::cluster_ctarank() : 0u;
+    // this CTA's share of the k-tiles and of the work items
+    const int k_begin = kSplitK ? int(k_rank) * k_tiles / 2 : 0;
+    const int k_end = kSplitK ? (int(k_rank) + 1) * k_tiles / 2 : k_tiles;
+    const int first_item = kSplitK ? blockIdx.x >> 1 : blockIdx.x;
+    const int item_step = kSplitK ? gridDim.x >> 1 : gridDim.x;
     const uint32_t b_base = a_base + C::kStages * C::kABytes;
     const uint32_t sfa_base = b_base + C::kStages * C::kBBytes;
     const uint32_t sfb_base = sfa_base + C::kStages * C::kSfaBytes;
@@ -430,6 +448,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[s]), kEpiWarps);
             ptx::mbar_init(ptx::smem_u32(&bars->overlap_free[s]), kEpiWarps);
         }
+        if (kSplitK) ptx::mbar_init(ptx::smem_u32(&bars->recv_full), kEpiWarps);
         bars->abort = 0;
         ptx::fence_mbar_init();
         ptx::prefetch_tmap(&tm_a);
@@ -442,6 +461,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     }
     ptx::tc_fence_before();
     __syncthreads();
+    // the other CTA's barriers exist before anyone signals across the pair
+    if (kSplitK) ptx::cluster_sync();
     ptx::tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
 
@@ -454,16 +475,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            WorkIter<BN> work(grp, M, N, tiles_m, tiles_n);
+            WorkIter<BN> work(grp, M, N, tiles_m, tiles_n, first_item, item_step);
             Work wk;
             while (ok && work.next(wk)) {
                 const int m0 = wk.a_row0;
                 const int n0 = wk.b_row0;
                 const uint8_t* const sfa_row = sfa + int64_t(m0 / kBM) * kq_dim * 512;
                 const uint8_t* const sfb_row = sfb + int64_t(wk.sfb_tile) * kq_dim * 512;
-                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
-                    const uint32_t s = it % C::kStages;
-                    const uint32_t ph = (it / C::kStages) & 1u;
+                for (int kt = k_begin; kt < k_end; ++kt, ++it) {
+                    const uint32_t s = it % kRing;
+                    const uint32_t ph = (it / kRing) & 1u;
                     ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ph ^ 1u, abort, kStatusProducer);
                     if (!ok) break;
                     const uint32_t full = ptx::smem_u32(&bars->full[s]);
@@ -489,7 +510,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             uint32_t it = 0;
             uint32_t t = 0;
             bool ok = true;
-            WorkIter<BN> work(grp, M, N, tiles_m, tiles_n);
+            WorkIter<BN> work(grp, M, N, tiles_m, tiles_n, first_item, item_step);
             Work wk;
             for (; ok && work.next(wk); ++t) {
                 const uint32_t as = t & 1u;
@@ -506,9 +527,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 const uint32_t acc = tmem + as * C::kAccStride;
                 // a 64-wide tile uses half of a 128-row scale atom
                 const uint32_t sfb_shift = BN == 64 ? uint32_t(wk.sfb_shift) : 0u;
-                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
-                    const uint32_t s = it % C::kStages;
-                    const uint32_t ph = (it / C::kStages) & 1u;
+                for (int kt = k_begin; kt < k_end; ++kt, ++it) {
+                    const uint32_t s = it % kRing;
+                    const uint32_t ph = (it / kRing) & 1u;
                     ok = wait_bar(ptx::smem_u32(&bars->full[s]), ph, abort, kStatusMma);
                     if (!ok) break;
                     ptx::tc_fence_after();
@@ -545,7 +566,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             acc, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2),
                             instr_desc<BN, KIND>(sf_id), tmem + C::kSfaCol + atom * 4,
                             tmem + C::kSfbCol + atom * C::kNAtoms * 4 + sfb_shift,
-                            (kt > 0 || k > 0) ? 1u : 0u);
+                            (kt > k_begin || k > 0) ? 1u : 0u);
                     }
                     // stage s may be refilled once these MMAs have read it
                     ptx::tc_commit(ptx::smem_u32(&bars->empty[s]));
@@ -560,7 +581,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         uint32_t t = 0;
         uint32_t stores = 0;
         bool ok = true;
-        WorkIter<BN> work(grp, M, N, tiles_m, tiles_n);
+        WorkIter<BN> work(grp, M, N, tiles_m, tiles_n, first_item, item_step);
         Work wk;
         const int ar = int(lane_base) + lane;  // accumulator row of this thread
         for (; ok && work.next(wk); ++t) {
@@ -628,6 +649,53 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 uint32_t r[32];
                 ptx::tc_load_32x32(acc + c * kEpiChunk, r);
                 ptx::tc_wait_ld();
+                if constexpr (kSplitK) {
+                    // row `ar`, columns [32 c, 32 c + 32) of the 128 x 64 fp32 buffer
+                    const uint32_t slot = recv_base + uint32_t(ar) * (BN * 4) + uint32_t(c) * (kEpiChunk * 4);
+                    if (k_rank != 0) {
+                        const uint32_t dst = ptx::mapa_cluster(slot, 0);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            ptx::st_cluster_v4(dst + j * 16, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                               __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                        }
+                        if (ci == C::kChunks - 1) {
+                            // every lane's stores are ordered before the warp's one remote arrive
+                            __syncwarp();
+                            if (lane == 0) {
+                                ptx::mbar_arrive_cluster_addr(ptx::mapa_cluster(ptx::smem_u32(&bars->recv_full), 0));
+                            }
+                            ptx::tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[as]));
+                        }
+                        continue;
+                    }
+                    if (ci == 0) {
+                        // this tile's partial sums (one phase of the barrier per tile)
+                        const uint64_t t0 = ptx::globaltimer_ns();
+                        while (!ptx::mbar_try_wait_cluster(ptx::smem_u32(&bars->recv_full), t & 1u)) {
+                            if (*abort != 0u || ptx::globaltimer_ns() - t0 > kTimeoutNs) {
+                                *abort = 1u;
+                                atomicOr(&g_status[0], uint32_t(kStatusEpilogue));
+                                ok = false;
+                                break;
+                            }
+                        }
+                        if (!ok) break;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float4 v;
+                        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                                     : "r"(slot + j * 16));
+                        r[4 * j] = __float_as_uint(__uint_as_float(r[4 * j]) + v.x);
+                        r[4 * j + 1] = __float_as_uint(__uint_as_float(r[4 * j + 1]) + v.y);
+                        r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
+                        r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
+                    }
+                }
                 if (C::kOverlap != 0 && ci == C::kOverlapChunks - 1) {
                     ptx::tc_fence_before();
                     __syncwarp();
@@ -1445,6 +1513,27 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     const int tiles_n = g.n / BN;
     const int grid = min(g.sm_count, tiles_m * tiles_n);
     const int k_tiles = int(g.k_bytes / kBKBytes);
+    if constexpr (BN == 64) {
+        // One row of at most sm_count / 2 tiles and a long K: two CTAs per tile, half of K each.
+        static const bool split_ok = [] {
+            const char* e = getenv("HALOPS_B200_SPLITK");
+            return e == nullptr || e[0] != '0';
+        }();
+        if (split_ok && g.grp.kind == kGroupDense && tiles_m == 1 && 2 * tiles_n <= g.sm_count && k_tiles >= 8 &&
+            (g.epi_op == HQ_EPILOGUE_IDENTITY || g.epi_op == HQ_EPILOGUE_SIGMOID)) {
+            static std::once_flag once_split[16];
+            std::call_once(once_split[dev & 15], [&] {
+                attr_err = cudaFuncSetAttribute(gemm_kernel<BN, KIND, true>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+            });
+            HQ_CUDA_TRY(attr_err);
+            HQ_CUDA_TRY(launch(gemm_kernel<BN, KIND, true>, dim3(2 * tiles_n), dim3(kThreads), size_t(C::kSmemBytes),
+                               g.stream, g.pdl, 2, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.bias, g.epi_op, g.out,
+                               g.ldo, g.m, g.n, k_tiles, g.kq_dim, tiles_m, tiles_n, a_rows,
+                               g.direct_store ? 1 : 0, g.grp, g.situ));
+            return HQ_OK;
+        }
+    }
     HQ_CUDA_TRY(launch(gemm_kernel<BN, KIND>, dim3(grid), dim3(kThreads), size_t(C::kSmemBytes), g.stream,
                        g.pdl, 1, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.bias, g.epi_op, g.out, g.ldo, g.m, g.n, k_tiles,
                        g.kq_dim, tiles_m, tiles_n, a_rows, g.direct_store ? 1 : 0, g.grp, g.situ));

@@ -70,6 +70,29 @@ __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t bar_clust
                  : "memory");
 }
 // One arrival on a barrier given by its shared::cluster address.
+// try_wait that also acquires what another CTA of the cluster released before its
+// (remote) arrive, e.g. stores into this CTA's shared memory.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// 16 bytes to an address of the cluster's shared-memory window (another CTA's shared memory).
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr_cluster, float a, float b, float c, float d) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr_cluster), "f"(a), "f"(b), "f"(c),
+                 "f"(d)
+                 : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive_cluster_addr(uint32_t bar_cluster) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster)
                  : "memory");

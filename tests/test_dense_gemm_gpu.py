@@ -385,3 +385,19 @@ def test_situ_quant_epilogue(hq, m, n, k, with_bias, beta, linear_beta):
     assert (amax <= 448 * s).all()
     nz = ref.abs().reshape(m, kb_out, 32).amax(-1) > 1e-6
     assert (amax[nz] > 448 * s[nz] / 2 * 0.9).all(), "a scale is a step too large"
+
+
+@pytest.mark.parametrize("mode, m, n, k", [
+    ("w8a8-mxfp8", 1, 4096, 4096), ("w8a8-mxfp8", 64, 4096, 8192), ("w8a8-mxfp8", 128, 2048, 1024),
+    ("w8a8-mxfp8", 5, 64, 2048), ("w8a8-mxfp8", 33, 4736, 1152), ("w8a8-mxfp8", 100, 1024, 1024)],
+    ids=lambda v: str(v))
+def test_split_k_shapes(hq, monkeypatch, mode, m, n, k):
+    """One row of at most 74 64-wide tiles and at least 8 k-tiles: two CTAs share a tile, half
+    of K each, partial sums through distributed shared memory.  The result is deterministic
+    and within a bfloat16 rounding of the unsplit kernel."""
+    a, b = _rand(m, k, 21), _rand(n, k, 22, "weight")
+    aq, bq, sfa, sfb = _quantize(hq, a, b, mode)
+    assert "128x64" in hq.describe_tile(m, n, k, mode)
+    out = _gemm(hq, aq, bq, sfa, sfb, mode)
+    _check(out, aq, bq, sfa, sfb, mode)
+    assert torch.equal(out, _gemm(hq, aq, bq, sfa, sfb, mode, use_pdl=True))
