@@ -94,8 +94,8 @@ struct Cfg {
 };
 
 struct Barriers {
-    uint64_t full[8];
-    uint64_t empty[8];
+    uint64_t full[16];
+    uint64_t empty[16];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint64_t overlap_free[2];
@@ -826,7 +826,18 @@ struct LlParams {
     int sigmoid;             // write sigmoid(bf16(result)) instead
 };
 
-constexpr int kLlThreads = 224;  // loader, MMA issuer, 4 epilogue warps, scale builder
+// Warps: 0 loader, 1 MMA issuer 0, 2-5 epilogue, 6 scale builder, 7 scale copies, 8 MMA issuer 1.
+// A stage holds 16 rows of A (the MMA reads 128 rows; what follows in shared memory only
+// reaches accumulator rows that are never stored), so 16 stages fit; the scale copies and
+// every second k-tile's MMAs have threads of their own.  Each of the two changes alone left
+// the k-tile time where it was (one issuing thread needs about 640 cycles per k-tile; 8
+// stages of loads that take about 5000 cycles to arrive allow one k-tile per 625 cycles).
+constexpr int kLlThreads = 288;
+constexpr int kLlStages = 16;
+constexpr int kLlABytes = 16 * kBKBytes;
+constexpr int kLlStageBytes = kLlABytes + 64 * kBKBytes + 512 + 512;
+constexpr int kLlSmemBytes = kLlStages * kLlStageBytes + 1024 + 1024;
+constexpr int kLlSfSets = 4;
 
 __global__ void __launch_bounds__(kLlThreads, 1)
 ll_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -838,10 +849,14 @@ ll_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* const smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
     const uint32_t a_base = smem_base;
-    const uint32_t b_base = a_base + C::kStages * C::kABytes;
-    const uint32_t sfa_base = b_base + C::kStages * C::kBBytes;
-    const uint32_t sfb_base = sfa_base + C::kStages * C::kSfaBytes;
-    const uint32_t bar_off = C::kStages * C::kStageBytes + C::kEpiBytes;
+    const uint32_t b_base = a_base + kLlStages * kLlABytes;
+    const uint32_t sfa_base = b_base + kLlStages * C::kBBytes;
+    const uint32_t sfb_base = sfa_base + kLlStages * C::kSfaBytes;
+    const uint32_t bar_off = kLlStages * kLlStageBytes;
+    static_assert(kLlStages * 64 * kBKBytes >= (kBM - 16) * kBKBytes, "A over-read stays inside the B stages");
+    static_assert(kLlStages <= int(sizeof(Barriers::full) / sizeof(uint64_t)), "one barrier pair per stage");
+    static_assert(sizeof(Barriers) <= 1024, "barrier block");
+    static_assert(C::kSfaCol + kLlSfSets * C::kSfCols <= C::kTmemCols, "scale sets fit the allocation");
     Barriers* const bars = reinterpret_cast<Barriers*>(smem + bar_off);
     volatile uint32_t* const abort = &bars->abort;
 
@@ -852,14 +867,16 @@ ll_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const int k_tiles = p.k_tiles1 + p.k_tiles2;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::kStages; ++s) {
+        for (int s = 0; s < kLlStages; ++s) {
             ptx::mbar_init(ptx::smem_u32(&bars->full[s]), 33);  // the loader + 32 scale-builder lanes
             ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);
         }
         for (int s = 0; s < 2; ++s) {
             ptx::mbar_init(ptx::smem_u32(&bars->acc_full[s]), 1);
             ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[s]), kEpiWarps);
+            ptx::mbar_init(ptx::smem_u32(&bars->turn[s]), 1);
         }
+        for (int s = 0; s < kLlSfSets; ++s) ptx::mbar_init(ptx::smem_u32(&bars->sf_ready[s]), 1);
         bars->abort = 0;
         ptx::fence_mbar_init();
         ptx::prefetch_tmap(&tm_a);
@@ -886,15 +903,15 @@ ll_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 const bool second = tile >= tiles1;  // dual output: a tile of weight2
                 const int n0 = (second ? tile - tiles1 : tile) * BN;
                 for (int kt = 0; kt < k_tiles; ++kt, ++it) {
-                    const uint32_t s = it % C::kStages;
-                    ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ((it / C::kStages) & 1u) ^ 1u, abort,
+                    const uint32_t s = it % kLlStages;
+                    ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ((it / kLlStages) & 1u) ^ 1u, abort,
                                   kStatusProducer);
                     if (!ok) break;
                     const uint32_t full = ptx::smem_u32(&bars->full[s]);
                     ptx::mbar_arrive_expect_tx(full, p.a_rows * kBKBytes + C::kBBytes);
                     const bool tail = kt >= p.k_tiles1;  // concat-K: the second input / weight pair
                     const int x = (tail ? kt - p.k_tiles1 : kt) * kBKBytes;
-                    ptx::tma_load_2d(a_base + s * C::kABytes, tail ? &tm_a2 : &tm_a, x, 0, full);
+                    ptx::tma_load_2d(a_base + s * kLlABytes, tail ? &tm_a2 : &tm_a, x, 0, full);
                     ptx::tma_load_2d(b_base + s * C::kBBytes, (tail || second) ? &tm_b2 : &tm_b, x, n0, full);
                 }
             }
@@ -911,8 +928,8 @@ ll_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const int n0 = (second ? tile - tiles1 : tile) * BN;
             const int n_rows = second ? p.n2 : p.n;
             for (int kt = 0; kt < k_tiles; ++kt, ++it) {
-                const uint32_t s = it % C::kStages;
-                ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ((it / C::kStages) & 1u) ^ 1u, abort, kStatusProducer);
+                const uint32_t s = it % kLlStages;
+                ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ((it / kLlStages) & 1u) ^ 1u, abort, kStatusProducer);
                 if (!ok) break;
                 const bool tail = kt >= p.k_tiles1;
                 const int64_t koff = int64_t(tail ? kt - p.k_tiles1 : kt) * 4;
@@ -931,39 +948,78 @@ ll_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 ptx::cp_async_arrive_noinc(ptx::smem_u32(&bars->full[s]));
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
+    } else if (warp == 7) {
+        // ------------------------------------------------------------ scale copies
+        // shared memory -> tensor memory, into scale set it % kLlSfSets
         if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const uint32_t s = it % kLlStages;
+                    ok = wait_bar(ptx::smem_u32(&bars->full[s]), (it / kLlStages) & 1u, abort, kStatusProducer);
+                    if (!ok) break;
+                    if (it >= uint32_t(kLlSfSets)) {
+                        // the MMAs of k-tile it - kLlSfSets read this set: done once they released their stage
+                        const uint32_t prev = it - uint32_t(kLlSfSets);
+                        ok = wait_bar(ptx::smem_u32(&bars->empty[prev % kLlStages]), (prev / kLlStages) & 1u, abort,
+                                      kStatusProducer);
+                        if (!ok) break;
+                    }
+                    // the scale words were written by ordinary asynchronous copies; the
+                    // tensor-memory copy reads them through the async proxy
+                    ptx::fence_proxy_async_smem();
+                    ptx::tc_fence_after();
+                    const uint32_t set = tmem + (it % kLlSfSets) * C::kSfCols;
+                    ptx::tc_copy_sf<1>(set + C::kSfaCol, ptx::smem_desc(sfa_base + s * C::kSfaBytes, 0, 128, 0));
+                    ptx::tc_copy_sf<1>(set + C::kSfbCol, ptx::smem_desc(sfb_base + s * C::kSfbBytes, 0, 128, 0));
+                    ptx::tc_commit(ptx::smem_u32(&bars->sf_ready[it % kLlSfSets]));
+                }
+            }
+        }
+    } else if (warp == 1 || warp == 8) {
+        // ------------------------------------------------------------ MMA issuers
+        // alternate k-tiles; after its MMAs a thread hands the turn to the other one (tcgen05
+        // fences around an mbarrier arrive), so the MMAs reach the tensor core in k order
+        if (lane == 0) {
+            const uint32_t me = warp == 1 ? 0u : 1u;
             uint32_t it = 0;
             uint32_t t = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++t) {
                 const uint32_t as = t & 1u;
-                ok = wait_bar(ptx::smem_u32(&bars->acc_empty[as]), ((t >> 1) & 1u) ^ 1u, abort, kStatusMma);
-                if (!ok) break;
-                ptx::tc_fence_after();
                 const uint32_t acc = tmem + as * C::kAccStride;
                 for (int kt = 0; kt < k_tiles; ++kt, ++it) {
-                    const uint32_t s = it % C::kStages;
-                    ok = wait_bar(ptx::smem_u32(&bars->full[s]), (it / C::kStages) & 1u, abort, kStatusMma);
+                    if ((it & 1u) != me) continue;
+                    const uint32_t s = it % kLlStages;
+                    if (kt == 0) {
+                        ok = wait_bar(ptx::smem_u32(&bars->acc_empty[as]), ((t >> 1) & 1u) ^ 1u, abort, kStatusMma);
+                        if (!ok) break;
+                    }
+                    ok = wait_bar(ptx::smem_u32(&bars->sf_ready[it % kLlSfSets]), (it / kLlSfSets) & 1u, abort,
+                                  kStatusMma) &&
+                         wait_bar(ptx::smem_u32(&bars->full[s]), (it / kLlStages) & 1u, abort, kStatusMma);
+                    if (ok && it > 0u) {
+                        ok = wait_bar(ptx::smem_u32(&bars->turn[me]), ((it - 1u) >> 1) & 1u, abort, kStatusMma);
+                    }
                     if (!ok) break;
-                    // the scale words were written by ordinary asynchronous copies; the
-                    // tensor-memory copy reads them through the async proxy
-                    ptx::fence_proxy_async_smem();
                     ptx::tc_fence_after();
-                    ptx::tc_copy_sf<1>(tmem + C::kSfaCol, ptx::smem_desc(sfa_base + s * C::kSfaBytes, 0, 128, 0));
-                    ptx::tc_copy_sf<1>(tmem + C::kSfbCol, ptx::smem_desc(sfb_base + s * C::kSfbBytes, 0, 128, 0));
-                    const uint64_t adesc = ptx::smem_desc(a_base + s * C::kABytes, 16, 1024, 2);
+                    const uint32_t set = tmem + (it % kLlSfSets) * C::kSfCols;
+                    const uint64_t adesc = ptx::smem_desc(a_base + s * kLlABytes, 16, 1024, 2);
                     const uint64_t bdesc = ptx::smem_desc(b_base + s * C::kBBytes, 16, 1024, 2);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         ptx::tc_mma_block_scaled<1, 0>(acc, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2),
-                                                       instr_desc<BN, 0>(uint32_t(k)), tmem + C::kSfaCol,
-                                                       tmem + C::kSfbCol, (kt > 0 || k > 0) ? 1u : 0u);
+                                                       instr_desc<BN, 0>(uint32_t(k)), set + C::kSfaCol,
+                                                       set + C::kSfbCol, (kt > 0 || k > 0) ? 1u : 0u);
                     }
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive(ptx::smem_u32(&bars->turn[me ^ 1u]));
+                    // MMAs complete in the order they were issued, so the commit after the last
+                    // k-tile also covers the other thread's MMAs
                     ptx::tc_commit(ptx::smem_u32(&bars->empty[s]));
+                    if (kt == k_tiles - 1) ptx::tc_commit(ptx::smem_u32(&bars->acc_full[as]));
                 }
-                if (ok) ptx::tc_commit(ptx::smem_u32(&bars->acc_full[as]));
             }
         }
     } else if (warp < 6) {
@@ -2277,11 +2333,12 @@ extern "C" int hq_low_latency_gemm(const void* a, const void* b, const void* sfa
     HQ_CUDA_TRY(cudaGetDevice(&dev));
     cudaError_t attr_err = cudaSuccess;
     std::call_once(once[dev & 15], [&] {
-        attr_err = cudaFuncSetAttribute(hq::ll_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        attr_err = cudaFuncSetAttribute(hq::ll_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        hq::kLlSmemBytes);
     });
     HQ_CUDA_TRY(attr_err);
     const int tiles = int((n + 63) / 64 + (n2 + 63) / 64);
-    HQ_CUDA_TRY(hq::launch(hq::ll_gemm_kernel, dim3(std::min(sm, tiles)), dim3(hq::kLlThreads), size_t(C::kSmemBytes),
+    HQ_CUDA_TRY(hq::launch(hq::ll_gemm_kernel, dim3(std::min(sm, tiles)), dim3(hq::kLlThreads), size_t(hq::kLlSmemBytes),
                            static_cast<cudaStream_t>(stream), use_pdl != 0, 1, tm_a, tm_b, tm_a2, tm_b2, p));
     return HQ_OK;
 }
