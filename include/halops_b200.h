@@ -33,8 +33,10 @@ enum {
 enum { HQ_DTYPE_BF16 = 0, HQ_DTYPE_FP16 = 1 };
 
 /* Epilogue selector; values of the reference's EpilogueOp
- * (csrc/kernel/gemm/epilogue_op.h:21-28).  Identity, Sigmoid and SituQuant (through
- * hq_dense_gemm_situ_quant) are implemented. */
+ * (csrc/kernel/gemm/epilogue_op.h:21-28).  hq_dense_gemm takes Identity and Sigmoid,
+ * hq_dense_gemm_situ_quant is SituQuant, hq_batch_gemm takes Identity and
+ * hq_batch_gemm_quant the three Quant forms: the same split as in the reference, whose
+ * dense entry has no Quant forms and whose batch entry has no Sigmoid / SituQuant. */
 enum {
     HQ_EPILOGUE_IDENTITY = 0,
     HQ_EPILOGUE_QUANT = 1,
