@@ -463,7 +463,7 @@ SWEEP = (
 
 
 def run_sweep(args):
-    """GEMM-only and quantizer-only medians for every BASELINE configuration and the
+    """GEMM-only and quantizer-only medians for every benchmark configuration and the
     reference's published shapes, measured the way the reference's benchmark does
     (cold L2: a 256 MiB buffer is zeroed before every timed call; 10 warm-up, 30 timed).
     One JSON object per line; not the driver's contract line."""
@@ -671,7 +671,7 @@ def main():
     ap.add_argument("--kernels-only", action="store_true",
                     help="run only warm-up and the timed steps (for profiler captures)")
     ap.add_argument("--sweep", action="store_true",
-                    help="time every BASELINE configuration (GEMM only / quantizer only, cold L2) instead")
+                    help="time every benchmark configuration (GEMM only / quantizer only, cold L2) instead")
     ap.add_argument("--c5", action="store_true",
                     help="run config 5 (M=16384, N=57344, K=8192 split over the ranks, strong scaling) instead")
     ap.add_argument("--shape", default=None, metavar="MODE,M,N,K",

@@ -242,7 +242,7 @@ def test_strided_input_and_preallocated_outputs(hq, mode, use_swizzle, m):
 
 
 def test_full_size_operand_properties(hq):
-    """BASELINE-sized operand (8192 x 8192): checked through properties that do
+    """Benchmark-sized operand (8192 x 8192): checked through properties that do
     not need the whole oracle - a sampled row block is bit-exact, every scale
     byte is the smallest power of two that keeps the group inside +-448 (or one
     more for the 1.75-mantissa quirk), and dequantisation stays within the
