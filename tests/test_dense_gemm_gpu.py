@@ -401,3 +401,19 @@ def test_split_k_shapes(hq, monkeypatch, mode, m, n, k):
     out = _gemm(hq, aq, bq, sfa, sfb, mode)
     _check(out, aq, bq, sfa, sfb, mode)
     assert torch.equal(out, _gemm(hq, aq, bq, sfa, sfb, mode, use_pdl=True))
+
+
+@pytest.mark.parametrize("mode, m, n, k", [("w8a8-mxfp8", 2048, 2048, 4096), ("w4a4-nvfp4", 1024, 2048, 4096),
+                                           ("w8a8-mxfp8", 1000, 1024, 1024)], ids=lambda v: str(v))
+def test_pair_tile_is_bit_identical_and_deterministic(hq, monkeypatch, mode, m, n, k):
+    """The 2-CTA kernel issues the MMAs of alternate k-tiles from two threads that hand the
+    turn to each other; the MMAs must still reach the tensor core in k order.  Then the
+    result equals the single-CTA tile's bit for bit, run after run."""
+    a, b = _rand(m, k, 31), _rand(n, k, 32)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, mode)
+    monkeypatch.setenv("HALOPS_B200_TILE", "256")
+    single = _gemm(hq, aq, bq, sfa, sfb, mode)
+    monkeypatch.setenv("HALOPS_B200_TILE", "pair256")
+    assert "pair=1" in hq.describe_tile(m, n, k, mode)
+    for _ in range(10):
+        assert torch.equal(single, _gemm(hq, aq, bq, sfa, sfb, mode))
