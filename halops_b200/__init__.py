@@ -52,7 +52,7 @@ def describe_tile(m: int, n: int, k: int, mode: str = "w8a8-mxfp8", sm_count: in
     from . import _native
 
     buf = ctypes.create_string_buffer(256)
-    rc = _native.lib().hq_describe_tile(m, n, k, _native.MODE_IDS[mode], sm_count, device, buf, len(buf))
+    rc = _native.lib().hq_describe_tile(m, n, k, dict(_native.MODE_IDS, **{"w4a8-mxfp4": 3})[mode], sm_count, device, buf, len(buf))
     if rc != 0:
         raise RuntimeError(buf.value.decode())
     return buf.value.decode()
@@ -71,7 +71,7 @@ def describe_group_tile(kind: str, count: int, rows: int, n: int, k: int, mode: 
     buf = ctypes.create_string_buffer(256)
     rc = _native.lib().hq_describe_group_tile(
         {"batch": 1, "masked": 2, "contiguous": 3}[kind], count, rows, count * rows if total_m < 0 else total_m,
-        n, k, _native.MODE_IDS[mode], sm_count, device, buf, len(buf))
+        n, k, dict(_native.MODE_IDS, **{"w4a8-mxfp4": 3})[mode], sm_count, device, buf, len(buf))
     if rc != 0:
         raise RuntimeError(buf.value.decode())
     return buf.value.decode()

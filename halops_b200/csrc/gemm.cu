@@ -64,7 +64,7 @@ struct Cfg {
     static constexpr int kABytes = kBM * kBKBytes;
     static constexpr int kBBytes = BN * kBKBytes;
     // SfAtoms along K that one stage needs per 128 rows: K elements per stage / (4 * group)
-    static constexpr int kSfKAtoms = KIND == 0 ? 1 : (KIND == 1 ? 4 : 2);
+    static constexpr int kSfKAtoms = (KIND == 0 || KIND == 3) ? 1 : (KIND == 1 ? 4 : 2);
     static constexpr int kNAtoms = (BN + 127) / 128;
     static constexpr int kSfaBytes = kSfKAtoms * 512;
     static constexpr int kSfbBytes = kNAtoms * kSfaBytes;
@@ -264,9 +264,12 @@ __device__ __forceinline__ uint32_t instr_desc(uint32_t sf_id) {
     // block-scaled instruction descriptor: [4,6) SFB byte id, [7,10) A format,
     // [10,13) B format, bit 15/16 A/B major (0 = K), [17,23) N >> 3,
     // bit 23 scale format (1 = UE8M0, 0 = UE4M3), [24,29) M >> 4, [29,31) SFA byte id
-    constexpr uint32_t fmt = KIND == 0 ? 0u /* e4m3 */ : 1u /* e2m1 */;
+    // KIND 0: e4m3 x e4m3 (code 0); KIND 1 / 2: e2m1 x e2m1 of the mxf4nvf4 kinds (code 1);
+    // KIND 3: e4m3 x e2m1 of the mxf8f6f4 kind, whose code for e2m1 is 5
+    constexpr uint32_t fmt_a = (KIND == 0 || KIND == 3) ? 0u : 1u;
+    constexpr uint32_t fmt_b = KIND == 0 ? 0u : (KIND == 3 ? 5u : 1u);
     constexpr uint32_t scale_fmt = KIND == 1 ? 0u : 1u;
-    return (sf_id << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(BN >> 3) << 17) | (scale_fmt << 23) |
+    return (sf_id << 4) | (fmt_a << 7) | (fmt_b << 10) | (uint32_t(BN >> 3) << 17) | (scale_fmt << 23) |
            (uint32_t(kBM >> 4) << 24) | (sf_id << 29);
 }
 
@@ -489,7 +492,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     if (!ok) break;
                     const uint32_t full = ptx::smem_u32(&bars->full[s]);
                     // a short activation loads only its own rows (the A box is a_rows tall)
-                    ptx::mbar_arrive_expect_tx(full, C::kStageBytes - (kBM - a_rows) * kBKBytes);
+                    // packed e2m1 weights spread to one byte per value in shared memory, but the
+                    // barrier counts the bytes read from global memory: half of the stage's B bytes
+                    ptx::mbar_arrive_expect_tx(full, C::kStageBytes - (kBM - a_rows) * kBKBytes -
+                                                         (KIND == 3 ? C::kBBytes / 2 : 0));
                     ptx::tma_load_2d(a_base + s * C::kABytes, &tm_a, kt * kBKBytes, m0, full);
                     ptx::tma_load_2d(b_base + s * C::kBBytes, &tm_b, kt * kBKBytes, n0, full);
                     const int64_t koff = int64_t(kt) * C::kSfaBytes;
@@ -552,7 +558,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     for (int k = 0; k < 4; ++k) {
                         // 32 bytes of K per instruction: K = 32 (e4m3) or 64 (e2m1)
                         uint32_t atom, sf_id;
-                        if constexpr (KIND == 0) {
+                        if constexpr (KIND == 0 || KIND == 3) {
                             atom = 0;
                             sf_id = k;
                         } else if constexpr (KIND == 1) {
@@ -1544,8 +1550,14 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     const bool maps_ok =
         make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.a, uint64_t(g.k_bytes), uint64_t(rows_a),
                      uint64_t(g.k_bytes), kBKBytes, uint32_t(a_rows), CU_TENSOR_MAP_SWIZZLE_128B) &&
-        make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes), uint64_t(rows_b),
-                     uint64_t(g.k_bytes), kBKBytes, BN, CU_TENSOR_MAP_SWIZZLE_128B) &&
+        // KIND 3: packed e2m1 weights; the copy spreads every 16 values (8 bytes) over 16 bytes
+        // of shared memory, the form the mxf8f6f4 MMA reads 4-bit operands in, so a box of
+        // 128 values per row fills the same 128 bytes as 128 e4m3 values
+        (KIND == 3 ? make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, g.b, uint64_t(g.k_bytes),
+                                  uint64_t(rows_b), uint64_t(g.k_bytes / 2), kBKBytes, BN,
+                                  CU_TENSOR_MAP_SWIZZLE_128B)
+                   : make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes), uint64_t(rows_b),
+                                  uint64_t(g.k_bytes), kBKBytes, BN, CU_TENSOR_MAP_SWIZZLE_128B)) &&
         // (the quantising epilogue stores from registers; its map only has to be valid)
         make_tmap_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out,
                      uint64_t(g.epi_op == HQ_EPILOGUE_SITU_QUANT ? g.n / 4
@@ -1664,6 +1676,8 @@ const char* mode_name(int mode) {
             return "w8a8-mxfp8";
         case HQ_MODE_W4A4_MXFP4:
             return "w4a4-mxfp4";
+        case HQ_MODE_W4A8_MXFP4:
+            return "w4a8-mxfp4";
         default:
             return "w4a4-nvfp4";
     }
@@ -1682,7 +1696,8 @@ struct TilePick {
 // tile that divides N (most CTAs streaming the weight).  HALOPS_B200_TILE
 // (pair256 | pair128 | 256 | 128 | 64) overrides the choice when it is legal.
 TilePick pick_tile(int64_t m, int64_t n, int64_t k, int mode, int sm_count) {
-    const bool fp8 = mode == HQ_MODE_W8A8_MXFP8;
+    // (FP8 activations x FP4 weights tile like FP8: 128 values of K per k-tile)
+    const bool fp8 = mode == HQ_MODE_W8A8_MXFP8 || mode == HQ_MODE_W4A8_MXFP4;
     if (m < 1 || n < 1 || k < 1) return {0, false};
     if (fp8 ? (k % 128 != 0 || n % 64 != 0) : (k % 256 != 0 || n % 128 != 0)) return {0, false};
     const int64_t tiles_m = (m + kBM - 1) / kBM;
@@ -2010,10 +2025,16 @@ int grouped_gemm_impl(int kind, const void* a, const void* b, const void* sfa, c
                       void* stream, char* err, size_t errlen) {
     const bool batch = kind == kGroupBatch;
     const char* const per = batch ? "per-batch" : "per-expert";
-    const int group = hq_group_size(mode);
+    // FP8 activations x MXFP4 weights (UE8M0 scales per 32 on both): the expert kinds only
+    const bool w4a8 = mode == HQ_MODE_W4A8_MXFP4 && !batch;
+    const int group = w4a8 ? 32 : hq_group_size(mode);
     if (group == 0) {
         return fail(err, errlen, HQ_ERR_INVALID,
-                    "Unsupported mode: %d. Expected 'w8a8-mxfp8', 'w4a4-nvfp4' or 'w4a4-mxfp4'.", mode);
+                    "Unsupported mode: %d. Expected 'w8a8-mxfp8', 'w4a4-nvfp4', 'w4a4-mxfp4' or 'w4a8-mxfp4'.", mode);
+    }
+    if (w4a8 && bias != nullptr) return fail(err, errlen, HQ_ERR_INVALID, "W4A8 mode does not support bias yet.");
+    if (w4a8 && alpha != nullptr) {
+        return fail(err, errlen, HQ_ERR_INVALID, "W4A8 mode does not take alpha; scales are per-group UE8M0.");
     }
     if (count < 0 || rows < 0 || total_m < 0 || n < 0 || k < 0 || total_m > INT32_MAX || count * n > INT32_MAX ||
         k > INT32_MAX) {
@@ -2097,7 +2118,7 @@ int grouped_gemm_impl(int kind, const void* a, const void* b, const void* sfa, c
     g.m = int(total_m);
     g.n = int(n);
     g.grp = GroupParams{kind, int(count), int(rows), table};
-    g.k_bytes = mode == HQ_MODE_W8A8_MXFP8 ? k : k / 2;
+    g.k_bytes = (mode == HQ_MODE_W8A8_MXFP8 || w4a8) ? k : k / 2;  // bytes of one A row
     g.kq_dim = int(sf_k / 4);
     g.sm_count = sm;
     g.pdl = use_pdl != 0;
@@ -2114,6 +2135,8 @@ int grouped_gemm_impl(int kind, const void* a, const void* b, const void* sfa, c
     }
     if (mode == HQ_MODE_W8A8_MXFP8) {
         HQ_DISPATCH(0)
+    } else if (w4a8) {
+        HQ_DISPATCH(3)
     } else if (mode == HQ_MODE_W4A4_NVFP4) {
         HQ_DISPATCH(1)
     } else {
@@ -2127,7 +2150,9 @@ int grouped_gemm_impl(int kind, const void* a, const void* b, const void* sfa, c
 
 extern "C" int hq_describe_group_tile(int kind, int64_t count, int64_t rows, int64_t total_m, int64_t n, int64_t k,
                                       int mode, int sm_count, int device, char* buf, size_t buflen) {
-    if (hq_group_size(mode) == 0) return hq::fail(buf, buflen, HQ_ERR_INVALID, "Unsupported mode: %d", mode);
+    if (hq_group_size(mode) == 0 && !(mode == HQ_MODE_W4A8_MXFP4 && kind != hq::kGroupBatch)) {
+        return hq::fail(buf, buflen, HQ_ERR_INVALID, "Unsupported mode: %d", mode);
+    }
     if (kind < hq::kGroupBatch || kind > hq::kGroupContiguous) {
         return hq::fail(buf, buflen, HQ_ERR_INVALID, "Unsupported group kind: %d", kind);
     }

@@ -246,7 +246,8 @@ __device__ __forceinline__ void tc_copy_sf(uint32_t taddr, uint64_t sdesc) {
 
 // Block-scaled MMA, both operands from shared memory, accumulator and scale
 // factors in tensor memory.  kKind: 0 = mxf8f6f4 (1 scale / 32), 1 = mxf4nvf4
-// with 4 scales per K=64 (NVFP4), 2 = mxf4nvf4 with 2 scales per K=64 (MXFP4).
+// with 4 scales per K=64 (NVFP4), 2 = mxf4nvf4 with 2 scales per K=64 (MXFP4),
+// 3 = mxf8f6f4 again (e4m3 x e2m1; the formats are in the instruction descriptor).
 template <int kCtaGroup, int kKind>
 __device__ __forceinline__ void tc_mma_block_scaled(uint32_t d, uint64_t adesc, uint64_t bdesc,
                                                     uint32_t idesc, uint32_t sfa, uint32_t sfb,
@@ -261,7 +262,7 @@ __device__ __forceinline__ void tc_mma_block_scaled(uint32_t d, uint64_t adesc, 
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)            \
         : "memory")
     if constexpr (kCtaGroup == 1) {
-        if constexpr (kKind == 0) {
+        if constexpr (kKind == 0 || kKind == 3) {
             HQ_MMA_ASM(".cta_group::1.kind::mxf8f6f4.block_scale");
         } else if constexpr (kKind == 1) {
             HQ_MMA_ASM(".cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X");

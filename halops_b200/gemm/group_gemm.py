@@ -4,8 +4,8 @@ error texts as the reference's MoE grouped GEMMs
 host checks of ``csrc/kernel/gemm/group_masked_gemm.cu:22-186`` and
 ``csrc/kernel/gemm/group_contiguous_gemm.cu:22-176``), executed by this package's tcgen05
 kernel through the C ABI.  Built: ``w8a8-mxfp8`` (optional per-expert bias),
-``w4a4-nvfp4`` (per-expert alpha) and ``w4a4-mxfp4``; the reference's ``w4a8-mxfp4``
-mode (FP8 activations x FP4 weights) raises."""
+``w4a4-nvfp4`` (per-expert alpha), ``w4a4-mxfp4`` and ``w4a8-mxfp4`` (float8_e4m3fn
+activations x packed e2m1 weights, UE8M0 scales per 32 on both)."""
 
 from __future__ import annotations
 
@@ -18,6 +18,7 @@ from .. import _native
 __all__ = ["group_masked_gemm", "group_contiguous_gemm"]
 
 _MODES = ("w8a8-mxfp8", "w4a4-nvfp4", "w4a4-mxfp4", "w4a8-mxfp4")
+_MODE_IDS = dict(_native.MODE_IDS, **{"w4a8-mxfp4": 3})  # the last one is a GEMM-only mode
 
 
 def _check(cond: bool, msg: str) -> None:
@@ -28,9 +29,18 @@ def _check(cond: bool, msg: str) -> None:
 def _common(input, weight, sfa, sfb, bias, alpha, mode, num_experts, n):
     """Mode-dependent operand checks shared by both grouped GEMMs; returns
     ``(k, bias_ptr, alpha_ptr)``."""
-    _check(mode != "w4a8-mxfp4", "mode 'w4a8-mxfp4' (FP8 activation x MXFP4 weight) is not built in this library")
     fp8 = mode == "w8a8-mxfp8"
-    if fp8:
+    if mode == "w4a8-mxfp4":
+        k = weight.size(2) * 2
+        _check(input.size(1) == k,
+               f"W4A8 input K (unpacked fp8) must match unpacked weight K, got input K={input.size(1)}, weight K={k}")
+        _check(bias is None, "W4A8 mode does not support bias yet.")
+        _check(alpha is None, "W4A8 mode does not take alpha; scales are per-group UE8M0.")
+        sf_k = k // 32
+        _check(sfa.size(-1) == sf_k and sfb.size(-1) == sf_k,
+               f"W4A8 'w4a8-mxfp4' (UE8M0 per 32) requires SF K = {sf_k}, got sfa K={sfa.size(-1)} and "
+               f"sfb K={sfb.size(-1)}.")
+    elif fp8:
         k = weight.size(2)
         _check(input.size(1) == k, f"input K must match weight K, got input K={input.size(1)}, weight K={k}")
     else:
@@ -125,7 +135,7 @@ def group_masked_gemm(
     _check(output.stride(1) == 1, "output rows must be contiguous")
     if m == 0 or n == 0:
         return
-    _native.call("hq_describe_group_tile", 2, num_experts, max_m_per_expert, m, n, k, _native.MODE_IDS[mode], 148, -1)
+    _native.call("hq_describe_group_tile", 2, num_experts, max_m_per_expert, m, n, k, _MODE_IDS[mode], 148, -1)
     bias_ptr, alpha_ptr = _pointers(bias, alpha, mode == "w8a8-mxfp8", num_experts, n)
     for name, t in (("input", input), ("weight", weight), ("sfa", sfa), ("sfb", sfb), ("masked_m", masked_m),
                     ("output", output)):
@@ -134,7 +144,7 @@ def group_masked_gemm(
         "hq_group_masked_gemm",
         input.data_ptr(), weight.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), masked_m.data_ptr(), output.data_ptr(),
         bias_ptr, alpha_ptr, num_experts, max_m_per_expert, n, k, sfa.numel(), sfb.numel(), output.stride(0),
-        _native.MODE_IDS[mode], int(sm_count), 1, input.device.index,
+        _MODE_IDS[mode], int(sm_count), 1, input.device.index,
         torch.cuda.current_stream(input.device).cuda_stream,
     )
 
@@ -184,7 +194,7 @@ def group_contiguous_gemm(
     _check(output.stride(1) == 1, "output rows must be contiguous")
     if m == 0 or n == 0 or num_experts == 0:
         return
-    _native.call("hq_describe_group_tile", 3, num_experts, m // num_experts, m, n, k, _native.MODE_IDS[mode], 148, -1)
+    _native.call("hq_describe_group_tile", 3, num_experts, m // num_experts, m, n, k, _MODE_IDS[mode], 148, -1)
     bias_ptr, alpha_ptr = _pointers(bias, alpha, mode == "w8a8-mxfp8", num_experts, n)
     for name, t in (("input", input), ("weight", weight), ("sfa", sfa), ("sfb", sfb), ("expert_ids", expert_ids),
                     ("output", output)):
@@ -193,6 +203,6 @@ def group_contiguous_gemm(
         "hq_group_contiguous_gemm",
         input.data_ptr(), weight.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), expert_ids.data_ptr(),
         output.data_ptr(), bias_ptr, alpha_ptr, num_experts, m, n, k, sfa.numel(), sfb.numel(), output.stride(0),
-        _native.MODE_IDS[mode], int(sm_count), 1, input.device.index,
+        _MODE_IDS[mode], int(sm_count), 1, input.device.index,
         torch.cuda.current_stream(input.device).cuda_stream,
     )

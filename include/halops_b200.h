@@ -26,7 +26,11 @@ extern "C" {
 enum {
     HQ_MODE_W8A8_MXFP8 = 0, /* e4m3 values, UE8M0 scale per 32 */
     HQ_MODE_W4A4_MXFP4 = 1, /* packed e2m1 values, UE8M0 scale per 32 */
-    HQ_MODE_W4A4_NVFP4 = 2  /* packed e2m1 values, UE4M3 scale per 16 */
+    HQ_MODE_W4A4_NVFP4 = 2, /* packed e2m1 values, UE4M3 scale per 16 */
+    /* GEMM-only mode of hq_group_masked_gemm / hq_group_contiguous_gemm: e4m3 activations
+     * (quantised as W8A8_MXFP8) x packed e2m1 weights (quantised as W4A4_MXFP4), UE8M0 scales
+     * per 32 on both (csrc/kernel/gemm/group_masked_gemm.cu:96-121); not a quantizer mode. */
+    HQ_MODE_W4A8_MXFP4 = 3
 };
 
 /* Input element type of the quantizer. */
@@ -185,7 +189,8 @@ int hq_batch_gemm(const void* a, const void* b, const void* sfa, const void* sfb
  *   masked_m [num_experts] int32 on the device, read by the kernel (values are clamped to [0, max_m])
  *   out [num_experts * max_m, N] bf16, `ldo` elements between rows
  *   bias NULL or [num_experts, N] bf16 (w8a8-mxfp8 only); alpha NULL or [num_experts] float
- * max_m must be a multiple of 64.  The 'w4a8-mxfp4' mode of the reference is not built.
+ * max_m must be a multiple of 64.  mode may also be HQ_MODE_W4A8_MXFP4 (a [.., K] e4m3, b
+ * [num_experts, N, K/2] packed e2m1, no bias, no alpha).
  */
 int hq_group_masked_gemm(const void* a, const void* b, const void* sfa,
                          const void* sfb, const int32_t* masked_m, void* out,

@@ -108,9 +108,13 @@ def group_gemm_ref(a_q, b_q, sfa, sfb, expert_of_row, mode: str = "w8a8-mxfp8", 
     a_q = _np(a_q)
     b_q = _np(b_q)
     experts, n = b_q.shape[0], b_q.shape[1]
-    g = GROUP_SIZE[mode]
-    k = a_q.shape[1] * (1 if mode == "w8a8-mxfp8" else 2)
-    a = dequantize(a_q, sfa, mode)
+    # "w4a8-mxfp4" (tests/test_group_masked_gemm.py:563-600): e4m3 activations, packed e2m1
+    # weights, UE8M0 scales per 32 on both
+    mode_a, mode_b = ("w8a8-mxfp8", "w4a4-mxfp4") if mode == "w4a8-mxfp4" else (mode, mode)
+    g = GROUP_SIZE[mode_b]
+    k = a_q.shape[1] * (1 if mode_a == "w8a8-mxfp8" else 2)
+    a = dequantize(a_q, sfa, mode_a)
+    mode = mode_b
     sfb = _np(sfb).reshape(experts, -1, k // g)
     ids = np.asarray(expert_of_row).astype(np.int64)
     out = torch.zeros([a_q.shape[0], n], dtype=torch.float32)

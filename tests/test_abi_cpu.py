@@ -232,6 +232,13 @@ def test_group_gemm_rules_without_a_device(native):
     assert b"does not take alpha; the per-expert scaling factor" in err.value
     assert contiguous(None, None, None, None, None, None, None, None, 1, 0, 256, 128, big, big, 256, 0, -1, 1, 0,
                       None, err, len(err)) == 0  # no rows: nothing to do
+    # mode 3: e4m3 activations x packed e2m1 weights (tests/test_group_masked_gemm.py:727-768)
+    assert masked(None, None, None, None, None, None, fake, None, 2, 128, 128, 512, big, big, 128, 3, -1, 1, 0, None,
+                  err, len(err)) == 1
+    assert b"W4A8 mode does not support bias yet." in err.value
+    assert contiguous(None, None, None, None, None, None, None, fake, 1, 128, 256, 512, big, big, 256, 3, -1, 1, 0,
+                      None, err, len(err)) == 1
+    assert b"W4A8 mode does not take alpha" in err.value
 
     x = torch.empty([256, 128], dtype=torch.float8_e4m3fn)
     w = torch.empty([2, 256, 128], dtype=torch.float8_e4m3fn)
@@ -256,6 +263,9 @@ def test_group_gemm_rules_without_a_device(native):
         hq.group_contiguous_gemm(x, w, sfa, sfb, ids, out)
     assert "mode=masked" in hq.describe_group_tile("masked", 20, 64, 7168, 3584)
     assert "mode=contiguous" in hq.describe_group_tile("contiguous", 16, 256, 7168, 3584)
+    assert "w4a8-mxfp4" in hq.describe_group_tile("masked", 8, 128, 7168, 2048, "w4a8-mxfp4", sm_count=148)
+    with pytest.raises(RuntimeError):
+        hq.describe_group_tile("batch", 8, 128, 7168, 2048, "w4a8-mxfp4", sm_count=148)
 
 
 def test_low_latency_rules_without_a_device(native):

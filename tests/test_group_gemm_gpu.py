@@ -212,9 +212,6 @@ def test_masked_errors(hq):
                              128)
     with pytest.raises(RuntimeError, match="input M must equal num_experts"):
         hq.group_masked_gemm(t["x"], t["w"], t["sfa"], t["sfb"], t["masked_m"], t["out"], None, None, 64)
-    with pytest.raises(RuntimeError, match="not built"):
-        hq.group_masked_gemm(t["x"], t["w"], t["sfa"], t["sfb"], t["masked_m"], t["out"], None, None, 128, -1,
-                             "w4a8-mxfp4")
     # W4A4 rules
     experts, max_m, n, k = 2, 128, 128, 512
     x = torch.empty([experts * max_m, k // 2], dtype=torch.uint8, device="cuda")
@@ -298,3 +295,63 @@ def test_contiguous_golden_fixture(hq, golden_dir):
     hq.group_contiguous_gemm(x, w, sfa, sfb, torch.from_numpy(d["expert_ids"]).cuda(), out, bias)
     assert hq.device_status() == 0
     _compare(out, _bf16_from_bits(d["out_bits"]).float(), np.arange(x.shape[0]), "w8a8-mxfp8", bias)
+
+
+def _inputs_w4a8(hq, m, experts, n, k, seed=0):
+    """float8_e4m3fn activations (MXFP8 recipe) x packed e2m1 weights (MXFP4 recipe)."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn([m, k], generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn([experts, n, k], generator=g) * 0.05).to(torch.bfloat16).cuda()
+    xq, sfa = hq.group_wise_quant(x, mode="w8a8-mxfp8")
+    wq, sfb = hq.group_wise_quant(w.view(experts * n, k), mode="w4a4-mxfp4")
+    return xq, wq.view(experts, n, -1), sfa, sfb.view(experts, n, -1)
+
+
+@pytest.mark.parametrize("max_m,experts,n,k,masked", [
+    (128, 2, 256, 256, None), (64, 8, 256, 512, None), (128, 4, 256, 256, [17, 63, 0, 127]),
+    (128, 4, 1024, 2048, None), (256, 3, 512, 1024, [256, 100, 7])],
+    ids=lambda v: str(v) if not isinstance(v, list) else "partial")
+def test_masked_w4a8(hq, max_m, experts, n, k, masked):
+    """tests/test_group_masked_gemm.py:636-680: FP8 activations x MXFP4 weights."""
+    masked = [max_m] * experts if masked is None else masked
+    xq, wq, sfa, sfb = _inputs_w4a8(hq, experts * max_m, experts, n, k)
+    out = torch.full([experts * max_m, n], 3.0, dtype=torch.bfloat16, device="cuda")
+    hq.group_masked_gemm(xq, wq, sfa, sfb, torch.tensor(masked, dtype=torch.int32).cuda(), out, None, None, max_m, -1,
+                         "w4a8-mxfp4")
+    assert hq.device_status() == 0
+    ids = np.full(experts * max_m, -1, dtype=np.int64)
+    for e, cnt in enumerate(masked):
+        ids[e * max_m:e * max_m + cnt] = e
+    ref = oracle.group_gemm_ref(xq, wq, sfa, sfb, ids, "w4a8-mxfp4")
+    _compare(out, ref, np.nonzero(ids >= 0)[0], "w4a4-mxfp4", None)
+    assert torch.all(out.cpu()[torch.from_numpy(np.nonzero(ids < 0)[0])] == 3.0)
+
+
+@pytest.mark.parametrize("counts,n,k", [([128, 128], 256, 256), ([64, 192, 128, 64], 256, 512), ([256] * 4, 512, 1024)],
+                         ids=lambda v: str(v) if not isinstance(v, list) else "runs" + str(len(v)))
+def test_contiguous_w4a8(hq, counts, n, k):
+    ids = _spans(counts)
+    xq, wq, sfa, sfb = _inputs_w4a8(hq, ids.size, len(counts), n, k, seed=3)
+    out = torch.full([ids.size, n], float("nan"), dtype=torch.bfloat16, device="cuda")
+    hq.group_contiguous_gemm(xq, wq, sfa, sfb, torch.from_numpy(ids).cuda(), out, None, None, -1, "w4a8-mxfp4")
+    assert hq.device_status() == 0
+    ref = oracle.group_gemm_ref(xq, wq, sfa, sfb, ids.astype(np.int64), "w4a8-mxfp4")
+    _compare(out, ref, np.arange(ids.size), "w4a4-mxfp4", None)
+
+
+def test_w4a8_rules(hq):
+    """tests/test_group_masked_gemm.py:727-768."""
+    experts, max_m, n, k = 2, 128, 256, 256
+    xq, wq, sfa, sfb = _inputs_w4a8(hq, experts * max_m, experts, n, k)
+    out = torch.empty([experts * max_m, n], dtype=torch.bfloat16, device="cuda")
+    masked = torch.full([experts], max_m, dtype=torch.int32, device="cuda")
+    bias = torch.zeros([experts, n], dtype=torch.bfloat16, device="cuda")
+    alpha = torch.ones([experts], dtype=torch.float32, device="cuda")
+    with pytest.raises(RuntimeError, match="W4A8 mode does not support bias"):
+        hq.group_masked_gemm(xq, wq, sfa, sfb, masked, out, bias, None, max_m, -1, "w4a8-mxfp4")
+    with pytest.raises(RuntimeError, match="W4A8 mode does not take alpha"):
+        hq.group_masked_gemm(xq, wq, sfa, sfb, masked, out, None, alpha, max_m, -1, "w4a8-mxfp4")
+    with pytest.raises(RuntimeError, match="W4A8 input K"):
+        hq.group_masked_gemm(xq[:, :128].contiguous(), wq, sfa, sfb, masked, out, None, None, max_m, -1, "w4a8-mxfp4")
+    with pytest.raises(RuntimeError, match="requires SF K = 8"):
+        hq.group_masked_gemm(xq, wq, sfa, sfb[:, :, :4].contiguous(), masked, out, None, None, max_m, -1, "w4a8-mxfp4")
