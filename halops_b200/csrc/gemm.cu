@@ -29,8 +29,9 @@ namespace {
 
 constexpr int kBM = 128;           // rows of A per CTA tile
 constexpr int kBKBytes = 128;      // bytes of K per stage row: 128 e4m3 or 256 e2m1
-constexpr int kThreads = 192;      // single-CTA kernel: 6 warps (pair kernel: more, see Cfg2)
+constexpr int kThreads = 320;      // single-CTA kernel: 10 warps (pair kernel: see Cfg2)
 constexpr int kEpiWarps = 4;
+constexpr int kSfWarps = 4;        // single-CTA kernel: warps 6-9 move the scales into tensor memory
 constexpr int kEpiChunk = 32;      // accumulator columns per tcgen05.ld / TMA store
 constexpr int kEpiBufBytes = 32 * kEpiChunk * 2;  // 32 rows x 64 bytes
 constexpr uint64_t kTimeoutNs = 2000000000ull;    // bound of every device-side wait
@@ -58,6 +59,9 @@ enum : uint32_t {
     kStatusEpilogue = 0x04,
 };
 
+#ifndef HQ_SF_SETS
+#define HQ_SF_SETS 2
+#endif
 template <int BN, int KIND>
 struct Cfg {
     static_assert(BN == 64 || BN == 128 || BN == 256, "tile widths built");
@@ -76,15 +80,22 @@ struct Cfg {
     static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
     static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarBytes + 1024;
 
-    // tensor memory columns: two accumulator stages of BN columns; when
-    // BN == 256 they overlap by kOverlap columns so that the scale columns
-    // still fit in 512 (the epilogue drains the shared columns first).
+    // Tensor memory columns: two accumulator stages of BN columns, then kSfSets sets of scale
+    // columns (one set = the scales of one k-tile: kSfKAtoms * 4 columns for A, then
+    // kSfKAtoms * kNAtoms * 4 for B).  When BN == 256 the accumulator stages overlap by
+    // kOverlap columns so that everything fits in 512 (the epilogue drains the shared
+    // columns first).  The scales are written by four warps of their own (tcgen05.st, one
+    // warp per lane quarter) into the set it % kSfSets, so they run ahead of the MMAs: a
+    // tcgen05.cp of one 512-byte atom occupies the copy unit for 75-90 cycles whoever issues
+    // it, and NVFP4 needs 12 per k-tile of 512 MMA cycles.
     static constexpr int kSfCols = kSfKAtoms * 4 * (1 + kNAtoms);
-    static constexpr int kOverlap = BN == 256 ? (kSfCols + 15) / 16 * 16 : 0;
+    static constexpr int kSfSets = BN < 256 ? 4 : HQ_SF_SETS;
+    static constexpr int kSfRegion = kSfCols * kSfSets;
+    static constexpr int kOverlap = BN == 256 ? (kSfRegion + 15) / 16 * 16 : 0;
     static constexpr int kAccStride = BN - kOverlap;
-    static constexpr int kSfaCol = kAccStride + BN;
+    static constexpr int kSfaCol = kAccStride + BN;  // set 0
     static constexpr int kSfbCol = kSfaCol + kSfKAtoms * 4;
-    static constexpr int kColsUsed = kSfaCol + kSfCols;
+    static constexpr int kColsUsed = kSfaCol + kSfRegion;
     static constexpr int kTmemCols = kColsUsed <= 32 ? 32 : kColsUsed <= 64 ? 64 : kColsUsed <= 128 ? 128
                                      : kColsUsed <= 256 ? 256 : 512;
     static_assert(kColsUsed <= 512, "tensor memory budget");
@@ -99,7 +110,8 @@ struct Barriers {
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint64_t overlap_free[2];
-    uint64_t sf_ready[4];  // pair kernel: the scale copies of a k-tile have landed
+    uint64_t sf_full[16];  // single-CTA kernel: the scale bytes of a stage have landed
+    uint64_t sf_ready[4];  // the scales of a k-tile are in tensor memory
     uint64_t turn[2];      // pair kernel: hands the MMA issue from one issuer thread to the other
     uint64_t recv_full;    // split-K: the other CTA's partial sums have landed in this CTA's buffer
     uint32_t tmem_base;
@@ -444,6 +456,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
             ptx::mbar_init(ptx::smem_u32(&bars->full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bars->sf_full[s]), 1);
             ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);
         }
         for (int s = 0; s < 2; ++s) {
@@ -451,6 +464,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[s]), kEpiWarps);
             ptx::mbar_init(ptx::smem_u32(&bars->overlap_free[s]), kEpiWarps);
         }
+        for (int s = 0; s < C::kSfSets; ++s) ptx::mbar_init(ptx::smem_u32(&bars->sf_ready[s]), kSfWarps);
         if (kSplitK) ptx::mbar_init(ptx::smem_u32(&bars->recv_full), kEpiWarps);
         bars->abort = 0;
         ptx::fence_mbar_init();
@@ -491,20 +505,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ph ^ 1u, abort, kStatusProducer);
                     if (!ok) break;
                     const uint32_t full = ptx::smem_u32(&bars->full[s]);
-                    // a short activation loads only its own rows (the A box is a_rows tall)
-                    // packed e2m1 weights spread to one byte per value in shared memory, but the
-                    // barrier counts the bytes read from global memory: half of the stage's B bytes
-                    ptx::mbar_arrive_expect_tx(full, C::kStageBytes - (kBM - a_rows) * kBKBytes -
-                                                         (KIND == 3 ? C::kBBytes / 2 : 0));
-                    ptx::tma_load_2d(a_base + s * C::kABytes, &tm_a, kt * kBKBytes, m0, full);
-                    ptx::tma_load_2d(b_base + s * C::kBBytes, &tm_b, kt * kBKBytes, n0, full);
+                    const uint32_t sf_full = ptx::smem_u32(&bars->sf_full[s]);
+                    // The scales have a barrier of their own: they are few bytes and land early,
+                    // so the scale warps are done before the operand tiles arrive.
+                    ptx::mbar_arrive_expect_tx(sf_full, C::kSfaBytes + C::kSfbBytes);
                     const int64_t koff = int64_t(kt) * C::kSfaBytes;
-                    ptx::bulk_load(sfa_base + s * C::kSfaBytes, sfa_row + koff, C::kSfaBytes, full);
+                    ptx::bulk_load(sfa_base + s * C::kSfaBytes, sfa_row + koff, C::kSfaBytes, sf_full);
 #pragma unroll
                     for (int j = 0; j < C::kNAtoms; ++j) {
                         ptx::bulk_load(sfb_base + s * C::kSfbBytes + j * C::kSfaBytes,
-                                       sfb_row + int64_t(j) * kq_dim * 512 + koff, C::kSfaBytes, full);
+                                       sfb_row + int64_t(j) * kq_dim * 512 + koff, C::kSfaBytes, sf_full);
                     }
+                    // a short activation loads only its own rows (the A box is a_rows tall)
+                    // packed e2m1 weights spread to one byte per value in shared memory, but the
+                    // barrier counts the bytes read from global memory: half of the stage's B bytes
+                    ptx::mbar_arrive_expect_tx(full, C::kABytes + C::kBBytes - (kBM - a_rows) * kBKBytes -
+                                                         (KIND == 3 ? C::kBBytes / 2 : 0));
+                    ptx::tma_load_2d(a_base + s * C::kABytes, &tm_a, kt * kBKBytes, m0, full);
+                    ptx::tma_load_2d(b_base + s * C::kBBytes, &tm_b, kt * kBKBytes, n0, full);
                 }
             }
             // let a dependent kernel start its prologue
@@ -536,22 +554,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 for (int kt = k_begin; kt < k_end; ++kt, ++it) {
                     const uint32_t s = it % kRing;
                     const uint32_t ph = (it / kRing) & 1u;
-                    ok = wait_bar(ptx::smem_u32(&bars->full[s]), ph, abort, kStatusMma);
+                    // the scales of this k-tile are in their set (the scale warps waited for the
+                    // stage); the stage's own barrier orders this thread after the TMA writes
+                    ok = wait_bar(ptx::smem_u32(&bars->sf_ready[it % C::kSfSets]), (it / C::kSfSets) & 1u, abort,
+                                  kStatusMma) &&
+                         wait_bar(ptx::smem_u32(&bars->full[s]), ph, abort, kStatusMma);
                     if (!ok) break;
                     ptx::tc_fence_after();
-                    // scales: shared memory -> tensor memory (4 columns per atom)
-#pragma unroll
-                    for (int a = 0; a < C::kSfKAtoms; ++a) {
-                        ptx::tc_copy_sf<1>(tmem + C::kSfaCol + a * 4,
-                                           ptx::smem_desc(sfa_base + s * C::kSfaBytes + a * 512, 0, 128, 0));
-#pragma unroll
-                        for (int j = 0; j < C::kNAtoms; ++j) {
-                            ptx::tc_copy_sf<1>(
-                                tmem + C::kSfbCol + (a * C::kNAtoms + j) * 4,
-                                ptx::smem_desc(sfb_base + s * C::kSfbBytes + (j * C::kSfKAtoms + a) * 512, 0,
-                                               128, 0));
-                        }
-                    }
+                    const uint32_t set = tmem + (it % C::kSfSets) * C::kSfCols;
                     const uint64_t adesc = ptx::smem_desc(a_base + s * C::kABytes, 16, 1024, 2);
                     const uint64_t bdesc = ptx::smem_desc(b_base + s * C::kBBytes, 16, 1024, 2);
 #pragma unroll
@@ -570,14 +580,57 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         }
                         ptx::tc_mma_block_scaled<1, KIND>(
                             acc, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2),
-                            instr_desc<BN, KIND>(sf_id), tmem + C::kSfaCol + atom * 4,
-                            tmem + C::kSfbCol + atom * C::kNAtoms * 4 + sfb_shift,
+                            instr_desc<BN, KIND>(sf_id), set + C::kSfaCol + atom * 4,
+                            set + C::kSfbCol + atom * C::kNAtoms * 4 + sfb_shift,
                             (kt > k_begin || k > 0) ? 1u : 0u);
                     }
                     // stage s may be refilled once these MMAs have read it
                     ptx::tc_commit(ptx::smem_u32(&bars->empty[s]));
                 }
                 if (ok) ptx::tc_commit(ptx::smem_u32(&bars->acc_full[as]));
+            }
+        }
+    } else if (warp >= 2 + kEpiWarps) {
+        // ------------------------------------------------------------ scales -> tensor memory
+        // One SfAtom is 32 rows of 16 bytes; lane l of every lane quarter of tensor memory
+        // holds row l in 4 columns (what tcgen05.cp.32x128b.warpx4 would write).  Each of
+        // the four warps fills its own quarter from the same shared-memory image.
+        const uint32_t quarter = (uint32_t(warp) & 3u) * 32u;
+        uint32_t it = 0;
+        bool ok = true;
+        WorkIter<BN> work(grp, M, N, tiles_m, tiles_n, first_item, item_step);
+        Work wk;
+        while (ok && work.next(wk)) {
+            for (int kt = k_begin; kt < k_end; ++kt, ++it) {
+                const uint32_t s = it % kRing;
+                ok = wait_bar(ptx::smem_u32(&bars->sf_full[s]), (it / kRing) & 1u, abort, kStatusProducer);
+                if (ok && it >= uint32_t(C::kSfSets)) {
+                    // the MMAs of k-tile it - kSfSets read this set: they are done once they
+                    // have released their stage
+                    const uint32_t prev = it - uint32_t(C::kSfSets);
+                    ok = wait_bar(ptx::smem_u32(&bars->empty[prev % kRing]), (prev / kRing) & 1u, abort,
+                                  kStatusProducer);
+                }
+                if (!ok) break;
+                ptx::tc_fence_after();
+                const uint32_t set = tmem + (quarter << 16) + (it % C::kSfSets) * C::kSfCols;
+                const uint32_t src_a = sfa_base + s * C::kSfaBytes + uint32_t(lane) * 16u;
+                const uint32_t src_b = sfb_base + s * C::kSfbBytes + uint32_t(lane) * 16u;
+#pragma unroll
+                for (int a = 0; a < C::kSfKAtoms; ++a) {
+                    uint32_t r0, r1, r2, r3;
+                    ptx::ld_shared_v4(src_a + a * 512, r0, r1, r2, r3);
+                    ptx::tc_store_32x32_x4(set + C::kSfaCol + a * 4, r0, r1, r2, r3);
+#pragma unroll
+                    for (int j = 0; j < C::kNAtoms; ++j) {
+                        ptx::ld_shared_v4(src_b + (j * C::kSfKAtoms + a) * 512, r0, r1, r2, r3);
+                        ptx::tc_store_32x32_x4(set + C::kSfbCol + (a * C::kNAtoms + j) * 4, r0, r1, r2, r3);
+                    }
+                }
+                ptx::tc_wait_st();
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->sf_ready[it % C::kSfSets]));
             }
         }
     } else {

@@ -320,6 +320,23 @@ __device__ __forceinline__ void tc_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Registers -> tensor memory: thread i of the warp writes r[0..3] to columns
+// [col, col + 4) of lane (taddr.lane + i).  A warp may only touch the 32 lanes
+// of its own quarter (warp index % 4).
+__device__ __forceinline__ void tc_store_32x32_x4(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2,
+                                                  uint32_t r3) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r0),
+                 "r"(r1), "r"(r2), "r"(r3)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                             uint32_t& r3) {
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
 // ---- descriptors ------------------------------------------------------------------
 
 // Shared-memory matrix descriptor: start address, leading / stride byte
