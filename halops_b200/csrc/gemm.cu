@@ -701,13 +701,40 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
                 continue;
             }
+            // Several chunks of columns shared with the other accumulator stage (FP4 kinds: the
+            // scale sets take 48-96 columns): read them all into registers first, so that the
+            // next tile's MMAs may start after three tensor-memory loads instead of after two
+            // or three whole chunk iterations (convert, staging buffer, TMA store).
+            constexpr int kPre = C::kOverlapChunks > 1 ? C::kOverlapChunks : 0;
+            uint32_t ro[kPre > 0 ? kPre : 1][32];
+            if constexpr (kPre > 0) {
+#pragma unroll
+                for (int j = 0; j < kPre; ++j) {
+                    const int c = as == 0 ? C::kChunks - 1 - j : j;
+                    ptx::tc_load_32x32(acc + c * kEpiChunk, ro[j]);
+                }
+                ptx::tc_wait_ld();
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->overlap_free[as]));
+            }
 #pragma unroll 1
             for (int ci = 0; ci < C::kChunks; ++ci) {
                 // stage 0 shares its highest columns with stage 1, stage 1 its lowest with stage 0
                 const int c = (C::kOverlap != 0 && as == 0) ? C::kChunks - 1 - ci : ci;
                 uint32_t r[32];
-                ptx::tc_load_32x32(acc + c * kEpiChunk, r);
-                ptx::tc_wait_ld();
+                if (kPre > 0 && ci < kPre) {
+#pragma unroll
+                    for (int j = 0; j < kPre; ++j) {
+                        if (ci == j) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) r[i] = ro[j][i];
+                        }
+                    }
+                } else {
+                    ptx::tc_load_32x32(acc + c * kEpiChunk, r);
+                    ptx::tc_wait_ld();
+                }
                 if constexpr (kSplitK) {
                     // row `ar`, columns [32 c, 32 c + 32) of the 128 x 64 fp32 buffer
                     const uint32_t slot = recv_base + uint32_t(ar) * (BN * 4) + uint32_t(c) * (kEpiChunk * 4);
@@ -755,7 +782,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
                     }
                 }
-                if (C::kOverlap != 0 && ci == C::kOverlapChunks - 1) {
+                if (C::kOverlap != 0 && kPre == 0 && ci == C::kOverlapChunks - 1) {
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->overlap_free[as]));
