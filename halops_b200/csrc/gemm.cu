@@ -1490,24 +1490,53 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             if (!ok) break;
             ptx::tc_fence_after();
             const uint32_t acc = tmem + as * C::kAccStride + (lane_base << 16);
+            // chunks shared with the other accumulator stage are read into registers first (as
+            // in the single-CTA kernel), so that the next tile's MMAs may start early
+            constexpr int kPre = C::kOverlapChunks > 1 ? C::kOverlapChunks : 0;
+            uint32_t ro[kPre > 0 ? kPre : 1][32];
+            if constexpr (kPre > 0) {
+#pragma unroll
+                for (int j = 0; j < kPre; ++j) {
+                    const int c = as == 0 ? C::kChunks - 1 - j : j;
+                    ptx::tc_load_32x32(acc + c * kEpiChunk, ro[j]);
+                }
+                ptx::tc_wait_ld();
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive_cluster_relaxed(ptx::mapa_cluster(ptx::smem_u32(&bars->overlap_free[as]), 0));
+                }
+            }
 #pragma unroll 1
             for (int ci = 0; ci < C::kChunks; ++ci) {
                 const int c = (C::kOverlap != 0 && as == 0) ? C::kChunks - 1 - ci : ci;
                 uint32_t r[32];
-                ptx::tc_load_32x32(acc + c * kEpiChunk, r);
-                ptx::tc_wait_ld();
-                if (C::kOverlap != 0 && ci == C::kOverlapChunks - 1) {
+                if (kPre > 0 && ci < kPre) {
+#pragma unroll
+                    for (int j = 0; j < kPre; ++j) {
+                        if (ci == j) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) r[i] = ro[j][i];
+                        }
+                    }
+                } else {
+                    ptx::tc_load_32x32(acc + c * kEpiChunk, r);
+                    ptx::tc_wait_ld();
+                }
+                // The arrivals below tell the leader's MMA threads that tensor-memory reads have
+                // completed (tcgen05.wait::ld); no shared or global data rides on them.
+                if (C::kOverlap != 0 && kPre == 0 && ci == C::kOverlapChunks - 1) {
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {
-                        ptx::mbar_arrive_cluster_addr(ptx::mapa_cluster(ptx::smem_u32(&bars->overlap_free[as]), 0));
+                        ptx::mbar_arrive_cluster_relaxed(ptx::mapa_cluster(ptx::smem_u32(&bars->overlap_free[as]), 0));
                     }
                 }
                 if (ci == C::kChunks - 1) {
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {
-                        ptx::mbar_arrive_cluster_addr(ptx::mapa_cluster(ptx::smem_u32(&bars->acc_empty[as]), 0));
+                        ptx::mbar_arrive_cluster_relaxed(ptx::mapa_cluster(ptx::smem_u32(&bars->acc_empty[as]), 0));
                     }
                 }
                 uint32_t p[16];
