@@ -1183,8 +1183,9 @@ ll_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 // matching half of the accumulator; both CTAs hold the scales of all BN columns.
 // Every CTA loads its own halves with plain (non-broadcast) TMA copies in the
 // cta_group::2 form, which lets the bytes be counted on the leader's (rank 0)
-// barrier; only the leader issues tcgen05.cp / tcgen05.mma, and it releases a stage
-// or publishes an accumulator with one tcgen05.commit per CTA.  The epilogue warps of
+// barrier; only the leader issues tcgen05.cp / tcgen05.mma.  It releases a stage with
+// one tcgen05.commit to its own barrier, which its loader passes on to the other CTA,
+// and publishes an accumulator with one commit per CTA.  The epilogue warps of
 // both CTAs report to the leader's barriers.  Per CTA this halves the B traffic from
 // L2 and leaves room for 6 stages instead of 4.
 
@@ -1216,8 +1217,8 @@ struct Cfg2 {
     // warps: 0 box loader, 1 MMA issuer, 2-5 epilogue, 6 scale loader, 7.. scale copies
     static constexpr int kCpWarps = KIND == 0 ? 1 : (KIND == 1 ? 3 : 2);
     // Two threads (warp 1 and the last warp) issue the MMAs of alternate k-tiles: issuing
-    // 4 MMAs and the 2 commits that release the stage in both CTAs keeps one thread busy
-    // for about 830 cycles, longer than the 512 the MMAs run.  After its MMAs a thread
+    // 4 MMAs and the commit that releases the stage keeps one thread busy for longer
+    // than the 512 cycles the MMAs run.  After its MMAs a thread
     // hands the turn to the other one (tcgen05 fences around an mbarrier arrive), so the
     // MMAs still reach the tensor core in k order.
     static constexpr int kThreads = 32 * (8 + kCpWarps);
@@ -1322,6 +1323,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                                   kStatusProducer);
                     if (!ok) break;
                     HQ_STAMP(rank, it, 1);
+                    // The MMA threads release a stage with one commit, to the leader's barrier; the
+                    // leader's loader passes it on.  A second commit costs the issuing thread about
+                    // 300 cycles per k-tile, this relaxed arrival about 200 on a thread with slack
+                    // (what it reports, the MMAs' reads of the stage, completed before the commit).
+                    if (leader && it >= uint32_t(C::kStages)) {
+                        ptx::mbar_arrive_cluster_relaxed(ptx::mapa_cluster(ptx::smem_u32(&bars->empty[s]), 1));
+                    }
                     const uint32_t full = ptx::mapa_cluster(ptx::smem_u32(&bars->full[s]), 0);
                     // Bytes of all four loader threads of the pair are counted on the leader's
                     // barrier; only this thread registers them (the count may go negative in
@@ -1461,9 +1469,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     // the loaders of both CTAs may refill stage s once these MMAs have read it;
                     // MMAs complete in the order they were issued, so the commit after the last
                     // k-tile also covers the other thread's MMAs
-                    const uint32_t empty = ptx::smem_u32(&bars->empty[s]);
-                    ptx::tc_commit_pair(ptx::mapa_cluster(empty, 0));
-                    ptx::tc_commit_pair(ptx::mapa_cluster(empty, 1));
+                    // (the leader's loader passes the release on to the other CTA)
+                    ptx::tc_commit_pair(ptx::mapa_cluster(ptx::smem_u32(&bars->empty[s]), 0));
                     if (kt == k_tiles - 1) {
                         const uint32_t accf = ptx::smem_u32(&bars->acc_full[as]);
                         ptx::tc_commit_pair(ptx::mapa_cluster(accf, 0));
