@@ -1430,11 +1430,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         if (!ok) break;
                     }
                     HQ_STAMP(2, it, 0);
-                    // the scale copies of this k-tile have landed (they waited for the stage);
-                    // the stage's own barrier orders this thread after the TMA writes
+                    // The scale copies of this k-tile have landed.  Every copy warp waited for the
+                    // stage's barrier before it copied and committed, so the operand boxes of both
+                    // CTAs have landed too: no second wait here (each one costs this thread, which
+                    // sets the pace, 50-100 cycles).
                     ok = wait_bar(ptx::smem_u32(&bars->sf_ready[it % C::kSfSets]), (it / C::kSfSets) & 1u, abort,
-                                  kStatusMma) &&
-                         wait_bar(ptx::smem_u32(&bars->full[s]), (it / C::kStages) & 1u, abort, kStatusMma);
+                                  kStatusMma);
                     // the other thread has issued the MMAs of the previous k-iteration
                     if (ok && it > 0u) {
                         ok = wait_bar(ptx::smem_u32(&bars->turn[me]), ((it - 1u) >> 1) & 1u, abort, kStatusMma);
