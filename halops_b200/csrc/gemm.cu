@@ -7,12 +7,14 @@
 // with hand-written PTX.  Per CTA (one per SM, persistent over output tiles):
 //   warp 0   TMA producer: A and B tiles (128-byte swizzle) by tensor map, the
 //            512-byte scale atoms by flat bulk copies, into a ring of stages
-//   warp 1   one thread issues tcgen05.cp (scales -> tensor memory) and the
-//            block-scaled tcgen05.mma (fp32 accumulators in tensor memory,
-//            two accumulator stages so the epilogue overlaps the next tile)
+//   warp 1   one thread issues the block-scaled tcgen05.mma (fp32 accumulators
+//            in tensor memory, two accumulator stages so the epilogue overlaps
+//            the next tile)
 //   warps 2-5 epilogue: tcgen05.ld -> * alpha -> bf16 -> swizzled staging in
 //            shared memory -> TMA store (rows >= M are dropped by the tensor
 //            map extent, so neither A nor the output is ever padded)
+//   warps 6-9 scales: shared memory -> registers -> tensor memory (tcgen05.st),
+//            one warp per lane quarter, a few k-tiles ahead of the MMAs
 // Every mbarrier wait is bounded: a role that waits longer than kTimeoutNs
 // records a code in the device status word, raises the CTA's abort flag and
 // all roles leave through the common teardown that frees tensor memory.
@@ -555,7 +557,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     const uint32_t s = it % kRing;
                     const uint32_t ph = (it / kRing) & 1u;
                     // the scales of this k-tile are in their set (the scale warps waited for the
-                    // stage); the stage's own barrier orders this thread after the TMA writes
+                    // scale bytes); the stage's own barrier orders this thread after the TMA writes
                     ok = wait_bar(ptx::smem_u32(&bars->sf_ready[it % C::kSfSets]), (it / C::kSfSets) & 1u, abort,
                                   kStatusMma) &&
                          wait_bar(ptx::smem_u32(&bars->full[s]), ph, abort, kStatusMma);
