@@ -1846,20 +1846,19 @@ TilePick pick_tile(int64_t m, int64_t n, int64_t k, int mode, int sm_count) {
         return {best, false};
     }
     // Several rows of tiles: waves x time per tile.  Fitted to this build's kernels on B200
-    // (MXFP8; M = N = K = 8192 and 8192 x 4096 x 4096): a tile costs its k-tiles plus a
-    // fixed number of k-tile times for fill, drain and the hand-over to the next tile.
-    // 128x256: 0.431 us per k-tile + 3.0 (404 / 105.5 us); 256x256 pair: 0.406 + 5.8
-    // (397 / 107.5 us); 128x128 0.35 (620 us); 256x128 pair 0.348 (633 us); 128x64 is
-    // extrapolated.  The FP4 kinds have four times the scale traffic per k-tile, which the
-    // pair pays twice (both CTAs hold all B scales): measured slower there (163 vs 153 us on
-    // 4096 x 14336 x 4096), so they stay on single-CTA tiles.
+    // (MXFP8; M = N = K = 8192, 8192 x 4096 x 4096 and 4096 x 14336 x 4096): a tile costs its
+    // k-tiles plus a fixed number of k-tile times for fill, drain and the hand-over to the
+    // next tile.  128x256: 0.46 us per k-tile + 2 (425 / 109.5 / 199 us); 256x256 pair:
+    // 0.404 + 3.2 (380 / 99.5 / 173 us); 128x128 0.35 (650 us); 256x128 pair 0.348 (633 us);
+    // 128x64 is extrapolated.  The FP4 kinds stay on single-CTA tiles: the pair measured no
+    // faster there (126 against 113 us on 4096 x 14336 x 4096 with the same scale path).
     struct Cand {
         int bn;
         bool pair;
         double us_per_ktile;
         double extra_ktiles;
     };
-    const Cand cands[5] = {{256, false, 0.431, 3.0}, {256, true, 0.406, 5.8}, {128, false, 0.35, 1.0},
+    const Cand cands[5] = {{256, false, 0.46, 2.0}, {256, true, 0.404, 3.2}, {128, false, 0.35, 1.0},
                            {128, true, 0.348, 1.0},  {64, false, 0.27, 1.0}};
     const double k_tiles = double(k) / (fp8 ? 128.0 : 256.0);
     TilePick best = {0, false};

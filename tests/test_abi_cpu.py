@@ -321,7 +321,9 @@ def test_describe_tile(native):
 
     assert "256x256/128 pair=1" in hq.describe_tile(8192, 8192, 8192, sm_count=148)
     assert "128x256/256 pair=0" in hq.describe_tile(4096, 14336, 4096, "w4a4-nvfp4", sm_count=148)
-    assert "128x256/128 pair=0" in hq.describe_tile(8192, 4096, 4096, sm_count=148)
+    assert "256x256/128 pair=1" in hq.describe_tile(8192, 4096, 4096, sm_count=148)
+    # 144 single-CTA tiles fit one wave, 80 pair tiles need two
+    assert "128x256/128 pair=0" in hq.describe_tile(1152, 4096, 4096, sm_count=148)
     assert "128x64/128" in hq.describe_tile(8, 7168, 2048, sm_count=148)
     with pytest.raises(RuntimeError, match="No dense"):
         hq.describe_tile(128, 96, 128, sm_count=148)
