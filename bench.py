@@ -273,26 +273,58 @@ def run_ours(args):
     a_host = a.cpu().pin_memory()
     b_host = b.cpu().pin_memory()
     out_host = torch.empty([M, N_LOCAL], dtype=torch.bfloat16).pin_memory()
-    a_dev, b_dev = torch.empty_like(a), torch.empty_like(b)
+    # Every step copies its own inputs in and its own result out; consecutive steps overlap on
+    # three streams (copy in / kernels / copy out) with two sets of device buffers, as a serving
+    # loop would: PCIe carries 268 MB in and 134 MB out per step, in both directions at once.
+    a_dev = [torch.empty_like(a) for _ in range(2)]
+    b_dev = [torch.empty_like(b) for _ in range(2)]
+    out_dev = [torch.empty_like(out) for _ in range(2)]
+    s_in, s_run, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    ev_in = [torch.cuda.Event() for _ in range(2)]        # inputs of the step are on the device
+    ev_in_free = [torch.cuda.Event() for _ in range(2)]   # the quantizers have read them
+    ev_run = [torch.cuda.Event() for _ in range(2)]       # the GEMM has written out_dev
+    ev_out = [torch.cuda.Event() for _ in range(2)]       # the result is in host memory
 
-    def e2e_step():
-        a_dev.copy_(a_host, non_blocking=True)
-        b_dev.copy_(b_host, non_blocking=True)
-        xq, xs = hq.group_wise_quant(a_dev, MODE, True, True, aq, sfa)
-        wq, ws = hq.group_wise_quant(b_dev, MODE, True, True, bq, sfb)
-        hq.dense_gemm(xq, wq, xs, ws, out, None, None, -1, MODE, True)
-        out_host.copy_(out, non_blocking=True)
+    def e2e_step(i):
+        j = i & 1
+        s_in.wait_event(ev_in_free[j])
+        with torch.cuda.stream(s_in):
+            a_dev[j].copy_(a_host, non_blocking=True)
+            b_dev[j].copy_(b_host, non_blocking=True)
+            ev_in[j].record(s_in)
+        s_run.wait_event(ev_in[j])
+        s_run.wait_event(ev_out[j])
+        with torch.cuda.stream(s_run):
+            xq, xs = hq.group_wise_quant(a_dev[j], MODE, True, True, aq, sfa)
+            wq, ws = hq.group_wise_quant(b_dev[j], MODE, True, True, bq, sfb)
+            ev_in_free[j].record(s_run)
+            hq.dense_gemm(xq, wq, xs, ws, out_dev[j], None, None, -1, MODE, True)
+            ev_run[j].record(s_run)
+        s_out.wait_event(ev_run[j])
+        with torch.cuda.stream(s_out):
+            out_host.copy_(out_dev[j], non_blocking=True)
+            ev_out[j].record(s_out)
 
-    e2e_steps = max(3, min(steps, 10))
-    e2e_step()
+    e2e_steps = max(4, min(steps, 10))
+    e2e_step(0)
+    e2e_step(1)
+    torch.cuda.synchronize(dev)
     barrier()
+    cur = torch.cuda.current_stream(dev)
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e.record()
+    s.record(cur)
+    for st in (s_in, s_run, s_out):
+        st.wait_event(s)
+    for i in range(e2e_steps):
+        e2e_step(i)
+    for st in (s_in, s_run, s_out):
+        cur.wait_stream(st)
+    e.record(cur)
     barrier()
     e2e_ms = s.elapsed_time(e) / e2e_steps
+    # the bytes that came back are the GEMM's (same operands as the device-resident steps above)
+    torch.cuda.synchronize(dev)
+    assert torch.equal(out_host, out.cpu()), "end-to-end result differs from the device-resident one"
 
     # ---- max over ranks
     times = torch.tensor([total_ms, gemm_ms, quant_ms, gemm_only_ms, quant_only_ms, e2e_ms], device=dev,
@@ -343,7 +375,8 @@ def run_ours(args):
                                         f"({'burst' if timed_seconds < 1.0 else 'sustained'}) as the dense fp8 peak"},
             "e2e": {"value": world * flops_rank / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOPS",
                     "h2d_bytes_per_step": 2 * M * K * 2, "d2h_bytes_per_step": M * N_LOCAL * 2,
-                    "ms_per_step": e2e_ms},
+                    "ms_per_step": e2e_ms,
+                    "overlap": "consecutive steps pipelined over 3 streams (copy in, kernels, copy out), 2 buffer sets"},
             "gpu_launches": 3 * steps,
             "clocks": clocks,
         }
