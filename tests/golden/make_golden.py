@@ -18,7 +18,7 @@ the top but never call here.  Outputs:
   ``per_token_cast_* / per_block_cast_*`` helpers, swizzled with
   ``reorder_sf_to_cutlass``, and the reference ``ref_gemm`` / ``ref_gemm_w4a4``
   bf16 output.
-* ``batch_<mode>.npz``, ``masked_<mode>.npz``, ``contiguous_w8a8-mxfp8.npz`` - inputs built
+* ``batch_<mode>.npz``, ``masked_<mode>.npz`` (also ``w4a8-mxfp4``), ``contiguous_w8a8-mxfp8.npz`` - inputs built
   by the input builders of the reference's ``tests/test_batch_gemm.py``,
   ``tests/test_group_masked_gemm.py`` and ``tests/test_group_contiguous_gemm.py`` and the
   outputs of their CPU models (``ref_batch_gemm_fp8 / _fp4``, ``ref_group_masked_gemm`` /
@@ -180,6 +180,14 @@ def make_grouped(out_dir: str) -> None:
         os.path.join(out_dir, "contiguous_w8a8-mxfp8.npz"), x=_u8(inp.x), w=_u8(inp.w), sfa=inp.sfa.numpy(),
         sfb=inp.sfb.numpy(), expert_ids=inp.expert_ids.numpy(), bias_bits=_bf16_bits(inp.bias),
         out_bits=_bf16_bits(ref))
+    # (after the others, so that their random streams stay as they were)
+    # masked, FP8 activations x packed FP4 weights: the reference's partial case
+    # (tests/test_group_masked_gemm.py:640-650) and its model for it
+    inp = tmg.make_w4a8_mxfp4_inputs(128, 4, 128, 512, full_x=False, masked_m=[11, 37, 89, 128])
+    ref = tmg.ref_group_masked_gemm_w4a4(inp.x_deq_float, inp.w_fp4_float, inp.masked_m, 128, 4)
+    np.savez_compressed(
+        os.path.join(out_dir, "masked_w4a8-mxfp4.npz"), x=_u8(inp.x), w=inp.w_packed.numpy(),
+        sfa=inp.sfa.numpy(), sfb=inp.sfb.numpy(), masked_m=inp.masked_m.numpy(), out_bits=_bf16_bits(ref))
 
 
 def main() -> None:

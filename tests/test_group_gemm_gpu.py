@@ -263,12 +263,14 @@ def _golden_operands(d, mode):
     x, w = torch.from_numpy(d["x"]).cuda(), torch.from_numpy(d["w"]).cuda()
     if mode == "w8a8-mxfp8":
         x, w = x.view(torch.float8_e4m3fn), w.view(torch.float8_e4m3fn)
+    elif mode == "w4a8-mxfp4":
+        x = x.view(torch.float8_e4m3fn)
     alpha = torch.from_numpy(d["alpha"]).cuda() if "alpha" in d else None
     bias = _bf16_from_bits(d["bias_bits"]).cuda() if "bias_bits" in d else None
     return x, w, torch.from_numpy(d["sfa"]).cuda(), torch.from_numpy(d["sfb"]).cuda(), alpha, bias
 
 
-@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4"])
+@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4", "w4a8-mxfp4"])
 def test_masked_golden_fixture(hq, golden_dir, mode):
     """Inputs and outputs of the reference's own input builders and CPU model
     (tests/golden/make_golden.py): partly filled, full and empty slots, per-expert alpha."""
@@ -283,7 +285,7 @@ def test_masked_golden_fixture(hq, golden_dir, mode):
     assert hq.device_status() == 0
     ref = _bf16_from_bits(d["out_bits"]).float()
     rows = np.concatenate([np.arange(e * max_m, e * max_m + c) for e, c in enumerate(masked)])
-    _compare(out, ref, rows, mode, bias)
+    _compare(out, ref, rows, "w4a4-mxfp4" if mode == "w4a8-mxfp4" else mode, bias)
 
 
 def test_contiguous_golden_fixture(hq, golden_dir):

@@ -166,7 +166,7 @@ def test_batch_oracle_matches_reference_model(golden_dir, mode):
         _close_to_model(got[:, b * n:(b + 1) * n], ref[b], bias)
 
 
-@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4"])
+@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4", "w4a8-mxfp4"])
 def test_masked_oracle_matches_reference_model(golden_dir, mode):
     d, alpha, bias, ref = _grouped_fixture(golden_dir, f"masked_{mode}.npz")
     masked = d["masked_m"]
