@@ -18,7 +18,7 @@ the top but never call here.  Outputs:
   ``per_token_cast_* / per_block_cast_*`` helpers, swizzled with
   ``reorder_sf_to_cutlass``, and the reference ``ref_gemm`` / ``ref_gemm_w4a4``
   bf16 output.
-* ``batch_<mode>.npz``, ``masked_<mode>.npz`` (also ``w4a8-mxfp4``), ``contiguous_w8a8-mxfp8.npz`` - inputs built
+* ``batch_<mode>.npz``, ``masked_<mode>.npz``, ``contiguous_<mode>.npz`` (also ``w4a8-mxfp4``) - inputs built
   by the input builders of the reference's ``tests/test_batch_gemm.py``,
   ``tests/test_group_masked_gemm.py`` and ``tests/test_group_contiguous_gemm.py`` and the
   outputs of their CPU models (``ref_batch_gemm_fp8 / _fp4``, ``ref_group_masked_gemm`` /
@@ -188,6 +188,18 @@ def make_grouped(out_dir: str) -> None:
     np.savez_compressed(
         os.path.join(out_dir, "masked_w4a8-mxfp4.npz"), x=_u8(inp.x), w=inp.w_packed.numpy(),
         sfa=inp.sfa.numpy(), sfb=inp.sfb.numpy(), masked_m=inp.masked_m.numpy(), out_bits=_bf16_bits(ref))
+    # contiguous in the FP4 modes and the mixed one (tests/test_group_contiguous_gemm.py:223-470)
+    for mode, make in (("w4a4-nvfp4", tcg.make_nvfp4_inputs), ("w4a4-mxfp4", tcg.make_mxfp4_inputs),
+                       ("w4a8-mxfp4", tcg.make_w4a8_mxfp4_inputs)):
+        inp = make(384, 128, 512, 3, 64)
+        mixed = mode == "w4a8-mxfp4"
+        ref = tcg.ref_group_contiguous_gemm_w4a4(inp.x_deq_float if mixed else inp.x_fp4_float, inp.w_fp4_float,
+                                                 inp.expert_ids, inp.num_experts)
+        extra = {"alpha": inp.alpha.numpy()} if mode == "w4a4-nvfp4" else {}
+        np.savez_compressed(
+            os.path.join(out_dir, f"contiguous_{mode}.npz"), x=_u8(inp.x) if mixed else inp.x_packed.numpy(),
+            w=inp.w_packed.numpy(), sfa=inp.sfa.numpy(), sfb=inp.sfb.numpy(), expert_ids=inp.expert_ids.numpy(),
+            out_bits=_bf16_bits(ref), **extra)
 
 
 def main() -> None:

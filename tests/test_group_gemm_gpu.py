@@ -288,15 +288,17 @@ def test_masked_golden_fixture(hq, golden_dir, mode):
     _compare(out, ref, rows, "w4a4-mxfp4" if mode == "w4a8-mxfp4" else mode, bias)
 
 
-def test_contiguous_golden_fixture(hq, golden_dir):
+@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4", "w4a4-mxfp4", "w4a8-mxfp4"])
+def test_contiguous_golden_fixture(hq, golden_dir, mode):
     import os
 
-    d = np.load(os.path.join(golden_dir, "contiguous_w8a8-mxfp8.npz"))
-    x, w, sfa, sfb, alpha, bias = _golden_operands(d, "w8a8-mxfp8")
+    d = np.load(os.path.join(golden_dir, f"contiguous_{mode}.npz"))
+    x, w, sfa, sfb, alpha, bias = _golden_operands(d, mode)
     out = torch.empty([x.shape[0], w.shape[1]], dtype=torch.bfloat16, device="cuda")
-    hq.group_contiguous_gemm(x, w, sfa, sfb, torch.from_numpy(d["expert_ids"]).cuda(), out, bias)
+    hq.group_contiguous_gemm(x, w, sfa, sfb, torch.from_numpy(d["expert_ids"]).cuda(), out, bias, alpha, -1, mode)
     assert hq.device_status() == 0
-    _compare(out, _bf16_from_bits(d["out_bits"]).float(), np.arange(x.shape[0]), "w8a8-mxfp8", bias)
+    _compare(out, _bf16_from_bits(d["out_bits"]).float(), np.arange(x.shape[0]),
+             "w4a4-mxfp4" if mode == "w4a8-mxfp4" else mode, bias)
 
 
 def _inputs_w4a8(hq, m, experts, n, k, seed=0):

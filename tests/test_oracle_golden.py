@@ -179,7 +179,9 @@ def test_masked_oracle_matches_reference_model(golden_dir, mode):
     _close_to_model(got, ref, bias)
 
 
-def test_contiguous_oracle_matches_reference_model(golden_dir):
-    d, alpha, bias, ref = _grouped_fixture(golden_dir, "contiguous_w8a8-mxfp8.npz")
-    got = oracle.group_gemm_ref(d["x"], d["w"], d["sfa"], d["sfb"], d["expert_ids"], "w8a8-mxfp8", bias=bias).float()
+@pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4", "w4a4-mxfp4", "w4a8-mxfp4"])
+def test_contiguous_oracle_matches_reference_model(golden_dir, mode):
+    d, alpha, bias, ref = _grouped_fixture(golden_dir, f"contiguous_{mode}.npz")
+    got = oracle.group_gemm_ref(d["x"], d["w"], d["sfa"], d["sfb"], d["expert_ids"], mode, alpha=alpha,
+                                bias=bias).float()
     _close_to_model(got, ref, bias)
