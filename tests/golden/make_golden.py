@@ -23,6 +23,8 @@ the top but never call here.  Outputs:
   ``tests/test_group_masked_gemm.py`` and ``tests/test_group_contiguous_gemm.py`` and the
   outputs of their CPU models (``ref_batch_gemm_fp8 / _fp4``, ``ref_group_masked_gemm`` /
   ``_w4a4``, ``ref_group_contiguous_gemm``).
+* ``rms_norm.npz``, ``low_latency_w8a8-mxfp8.npz`` - inputs and CPU models of
+  ``tests/test_rms_norm_quant.py`` and ``tests/test_low_latency_mma_gemm.py``.
 """
 
 from __future__ import annotations
@@ -41,7 +43,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 def _import_reference(root: str):
     stub = types.ModuleType("halops")
     for name in ("group_wise_quant", "dense_gemm", "interleave_gate_up", "batch_gemm", "group_masked_gemm",
-                 "group_contiguous_gemm"):
+                 "group_contiguous_gemm", "low_latency_mma_gemm", "rms_norm_quant"):
         setattr(stub, name, None)
 
     class _EpilogueOp:  # only attribute access at import time
@@ -200,6 +202,21 @@ def make_grouped(out_dir: str) -> None:
             os.path.join(out_dir, f"contiguous_{mode}.npz"), x=_u8(inp.x) if mixed else inp.x_packed.numpy(),
             w=inp.w_packed.numpy(), sfa=inp.sfa.numpy(), sfb=inp.sfb.numpy(), expert_ids=inp.expert_ids.numpy(),
             out_bits=_bf16_bits(ref), **extra)
+    # rms_norm_quant: the reference's inputs and its fp32 RMSNorm rounded to bf16
+    # (tests/test_rms_norm_quant.py:38-48); the quantizer that follows is pinned above
+    import tests.test_rms_norm_quant as trn  # noqa: E402
+    x, w = trn.make_inputs(40, 1024)
+    np.savez_compressed(os.path.join(out_dir, "rms_norm.npz"), x_bits=_bf16_bits(x), w_bits=_bf16_bits(w),
+                        y_bits=_bf16_bits(trn.ref_rms_norm(x, w)), eps=np.float32(trn.EPS))
+    # low_latency_mma_gemm: operands with a power of two per (row, k-group) as the reference
+    # builds them (tests/test_low_latency_mma_gemm.py:31-43), quantised by its CPU recipe, plain
+    # row-major scales, and its dequantise-then-matmul model (:67-75)
+    import tests.test_low_latency_mma_gemm as tll  # noqa: E402
+    import tests.utils.gemm_utils as gu  # noqa: E402
+    aq, sfa = gu.per_token_cast_to_fp8(tll.make_bf16(5, 1280, 0.1), 32)
+    bq, sfb = gu.per_token_cast_to_fp8(tll.make_bf16(136, 1280, 1280 ** -0.5), 32)
+    np.savez_compressed(os.path.join(out_dir, "low_latency_w8a8-mxfp8.npz"), x=_u8(aq), w=_u8(bq), sfa=sfa.numpy(),
+                        sfb=sfb.numpy(), out=tll.reference(aq, sfa, bq, sfb).numpy())
 
 
 def main() -> None:

@@ -157,3 +157,18 @@ def test_rejects(hq):
     xq, sfa, wq, sfb = _operands(hq, 8, 512, 1920)
     x2q, sfa2, w2q, sfb2 = _operands(hq, 8, 512, 2176)
     raises("K1 must be a multiple of 512", args(xq, sfa, wq, sfb, input2=x2q, weight2=w2q, sfa2=sfa2, sfb2=sfb2))
+
+
+def test_golden_fixture(hq, golden_dir):
+    """Operands built by the reference's own recipe (a power of two per row and k-group,
+    its CPU quantizer, plain scales) and the output of its dequantise-then-matmul model
+    (tests/golden/make_golden.py); N = 136 is 8-aligned but no multiple of the tile."""
+    import os
+
+    import numpy as np
+
+    d = np.load(os.path.join(golden_dir, "low_latency_w8a8-mxfp8.npz"))
+    xq = torch.from_numpy(d["x"]).cuda().view(torch.float8_e4m3fn)
+    wq = torch.from_numpy(d["w"]).cuda().view(torch.float8_e4m3fn)
+    sfa, sfb = _pad_scale_rows(torch.from_numpy(d["sfa"]).cuda()), _pad_scale_rows(torch.from_numpy(d["sfb"]).cuda())
+    _check(_run(hq, xq, wq, sfa, sfb), torch.from_numpy(d["out"]))

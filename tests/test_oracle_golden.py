@@ -185,3 +185,20 @@ def test_contiguous_oracle_matches_reference_model(golden_dir, mode):
     got = oracle.group_gemm_ref(d["x"], d["w"], d["sfa"], d["sfb"], d["expert_ids"], mode, alpha=alpha,
                                 bias=bias).float()
     _close_to_model(got, ref, bias)
+
+
+def test_rms_norm_oracle_matches_reference_model(golden_dir):
+    """The reference's fp32 RMSNorm rounded to bf16 on its own inputs
+    (tests/test_rms_norm_quant.py:38-48); the quantizer applied to it is pinned above."""
+    d = np.load(os.path.join(golden_dir, "rms_norm.npz"))
+    got = oracle.rms_norm_ref(_bf16(d["x_bits"]), _bf16(d["w_bits"]), float(d["eps"]))
+    assert torch.equal(got, _bf16(d["y_bits"]))
+
+
+def test_plain_scale_dequantize_matches_reference_model(golden_dir):
+    """Dequantise-then-matmul with plain row-major scales, the model of the reference's
+    low-latency GEMM test (tests/test_low_latency_mma_gemm.py:62-75)."""
+    d = np.load(os.path.join(golden_dir, "low_latency_w8a8-mxfp8.npz"))
+    a = oracle.dequantize(d["x"], d["sfa"], "w8a8-mxfp8", swizzled=False)
+    b = oracle.dequantize(d["w"], d["sfb"], "w8a8-mxfp8", swizzled=False)
+    assert torch.equal(a @ b.T, torch.from_numpy(d["out"]))

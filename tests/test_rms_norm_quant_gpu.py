@@ -107,3 +107,20 @@ def test_feeds_dense_gemm(hq):
     ref = oracle.rms_norm_ref(x, w, EPS).float() @ wt.float().cpu().T
     rel = (out.float().cpu() - ref).norm() / ref.norm()
     assert rel < 0.05
+
+
+def test_golden_fixture(hq, golden_dir):
+    """Inputs of the reference's own builder and its fp32 RMSNorm rounded to bf16
+    (tests/golden/make_golden.py), quantised by the pinned oracle: same bound as above."""
+    import os
+
+    d = np.load(os.path.join(golden_dir, "rms_norm.npz"))
+    bf16 = lambda bits: torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).view(torch.bfloat16)  # noqa: E731
+    x, w, y = bf16(d["x_bits"]), bf16(d["w_bits"]), bf16(d["y_bits"])
+    q, sf = hq.rms_norm_quant(x.cuda(), w.cuda(), float(d["eps"]), use_swizzle=False)
+    ref_q, ref_sf = oracle.quant_group_wise(y, "w8a8-mxfp8", False)
+    q, sf = q.view(torch.uint8).cpu().numpy(), sf.cpu().numpy()
+    sf_diff = np.abs(sf.astype(np.int32) - ref_sf.astype(np.int32))
+    assert sf_diff.max() <= 1 and (sf_diff > 0).mean() <= 1e-3
+    same = np.repeat(sf_diff == 0, 32, axis=1)
+    assert _ulp_diff(q, ref_q)[same].max() <= 1
