@@ -21,7 +21,7 @@ from .gemm import (
 from ._native import lib_path
 
 __all__ = ["EpilogueOp", "batch_gemm", "dense_gemm", "group_contiguous_gemm", "group_masked_gemm",
-           "group_wise_quant", "interleave_gate_up", "low_latency_mma_gemm", "rms_norm_quant", "device_status", "describe_tile",
+           "group_wise_quant", "interleave_gate_up", "low_latency_mma_gemm", "rms_norm_quant", "device_status", "selftest_bounded_wait", "describe_tile",
            "describe_group_tile", "lib_path"]
 __version__ = "0.1.0"
 
@@ -41,6 +41,18 @@ def device_status(device=None) -> int:
     _native.call("hq_device_status", dev.index, torch.cuda.current_stream(dev).cuda_stream,
                  ctypes.byref(status))
     return int(status.value)
+
+
+def selftest_bounded_wait(limit_us: int = 1000, device=None) -> None:
+    """Launches the one-CTA kernel whose wait on a barrier nobody arrives on gives up after
+    ``limit_us`` microseconds.  The next ``device_status`` raises (status 0x02), the one
+    after it returns 0: the path a GEMM role takes when one of its waits times out."""
+    import torch
+
+    from . import _native
+
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _native.call("hq_selftest_bounded_wait", int(limit_us), dev.index, torch.cuda.current_stream(dev).cuda_stream)
 
 
 def describe_tile(m: int, n: int, k: int, mode: str = "w8a8-mxfp8", sm_count: int = -1, device: int = -1) -> str:

@@ -42,28 +42,12 @@ constexpr int kSmemBudget = 232448;               // 227 KiB opt-in maximum per 
 // device status word: non-zero when a kernel gave up on a bounded wait
 __device__ uint32_t g_status[4];
 
-#ifdef HQ_TRACE
-// development aid: SM clock stamps of the first k-iterations of CTA / cluster 0
-__device__ unsigned long long g_trace[3 * 512 * 2];
-#define HQ_STAMP(role, it, slot)                                                      \
-    do {                                                                              \
-        if (cluster_id == 0 && (it) < 512u) g_trace[((role)*512 + (it)) * 2 + (slot)] = clock64(); \
-    } while (0)
-#else
-#define HQ_STAMP(role, it, slot) \
-    do {                         \
-    } while (0)
-#endif
-
 enum : uint32_t {
     kStatusProducer = 0x01,
     kStatusMma = 0x02,
     kStatusEpilogue = 0x04,
 };
 
-#ifndef HQ_SF_SETS
-#define HQ_SF_SETS 2
-#endif
 template <int BN, int KIND>
 struct Cfg {
     static_assert(BN == 64 || BN == 128 || BN == 256, "tile widths built");
@@ -91,7 +75,7 @@ struct Cfg {
     // tcgen05.cp of one 512-byte atom occupies the copy unit for 75-90 cycles whoever issues
     // it, and NVFP4 needs 12 per k-tile of 512 MMA cycles.
     static constexpr int kSfCols = kSfKAtoms * 4 * (1 + kNAtoms);
-    static constexpr int kSfSets = BN < 256 ? 4 : HQ_SF_SETS;
+    static constexpr int kSfSets = BN < 256 ? 4 : 2;
     static constexpr int kSfRegion = kSfCols * kSfSets;
     static constexpr int kOverlap = BN == 256 ? (kSfRegion + 15) / 16 * 16 : 0;
     static constexpr int kAccStride = BN - kOverlap;
@@ -122,14 +106,14 @@ struct Barriers {
 
 // Bounded mbarrier wait.  Returns false when the CTA is aborting.
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile uint32_t* abort,
-                                         uint32_t code) {
+                                         uint32_t code, uint64_t limit_ns = kTimeoutNs) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = ptx::globaltimer_ns();
     uint32_t spins = 0;
     while (!ptx::mbar_try_wait(bar, parity)) {
         if ((++spins & 31u) == 0u) {
             if (*abort != 0u) return false;
-            if (ptx::globaltimer_ns() - t0 > kTimeoutNs) {
+            if (ptx::globaltimer_ns() - t0 > limit_ns) {
                 *abort = 1u;
                 atomicOr(&g_status[0], code);
                 return false;
@@ -299,7 +283,22 @@ struct SituParams {
     float inv_lin;
     const __nv_bfloat16* gate;  // [M, B * N] multiplier of the GateMulQuant epilogues (logits for the sigmoid form)
     int64_t gate_ld;            // elements between its rows
+    int valid_rows;             // rows of the quantised output; `sf` covers them rounded up to 128
 };
+
+// The quantising epilogues store a scale byte for every row that exists.  The rows that pad
+// the last 128-row SfAtom get zero bytes here (what group_wise_quant writes there), so a
+// caller need not clear `sf` first.  Called by the 128 epilogue threads of every CTA.
+__device__ __forceinline__ void zero_sf_padding(const SituParams& sp, int tid) {
+    const int pad_rows = (128 - (sp.valid_rows & 127)) & 127;
+    const int total = pad_rows * sp.kb_out;
+    for (int i = int(blockIdx.x) * 128 + tid; i < total; i += int(gridDim.x) * 128) {
+        const int row = sp.valid_rows + i / sp.kb_out;
+        const int kb = i % sp.kb_out;
+        sp.sf[(int64_t(row >> 7) * (sp.kb_out >> 2) + (kb >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 +
+              (kb & 3)] = 0;
+    }
+}
 
 __device__ __forceinline__ float tanh_fast(float x) {
     float t;
@@ -645,6 +644,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         WorkIter<BN> work(grp, M, N, tiles_m, tiles_n, first_item, item_step);
         Work wk;
         const int ar = int(lane_base) + lane;  // accumulator row of this thread
+        if (situ.sf != nullptr) zero_sf_padding(situ, (warp - 2) * 32 + lane);
         for (; ok && work.next(wk); ++t) {
             const int m0 = wk.out_row0;  // output row of accumulator row 0
             const int n0 = wk.out_col0;
@@ -741,6 +741,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     // row `ar`, columns [32 c, 32 c + 32) of the 128 x 64 fp32 buffer
                     const uint32_t slot = recv_base + uint32_t(ar) * (BN * 4) + uint32_t(c) * (kEpiChunk * 4);
                     if (k_rank != 0) {
+                        // an aborting CTA sends nothing more across the pair
+                        if (*abort != 0u) {
+                            ok = false;
+                            break;
+                        }
                         const uint32_t dst = ptx::mapa_cluster(slot, 0);
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
@@ -883,10 +888,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     }
     ptx::tc_fence_before();
     __syncthreads();
+    // split-K: neither CTA of the pair leaves while the other may still store partial sums
+    // into its shared memory or arrive on its barrier (every wait above is bounded, so both
+    // get here)
+    if (kSplitK) ptx::cluster_sync();
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc<1>(tmem, C::kTmemCols);
     }
+}
+
+// Self-test of the bounded wait and of the way a timeout spreads: thread 0 waits, with a
+// short limit, on a barrier that nothing ever arrives on; thread 32 waits on the same
+// barrier with the ordinary limit and must leave as soon as it sees the abort flag thread
+// 0 raises.  Nothing is in flight when the waits give up: no copies, no MMAs, no tensor
+// memory.  What the host then reads through hq_device_status is what it would read after a
+// GEMM role had timed out.
+__global__ void __launch_bounds__(64, 1) wait_selftest_kernel(uint64_t limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        wait_bar(ptx::smem_u32(&bar), 0, &abort_flag, kStatusMma, limit_ns);
+    } else if (threadIdx.x == 32) {
+        // sees the flag within 32 polls of its being raised; its own limit never runs out
+        if (wait_bar(ptx::smem_u32(&bar), 0, &abort_flag, kStatusEpilogue)) atomicOr(&g_status[0], 0x80u);
+    }
+    __syncwarp();
+    __syncthreads();
 }
 
 // ---------------------------------------------------------------------------- M <= 16, plain scales
@@ -1320,11 +1354,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 const int n0 = tc.n * BN + int(rank) * (BN / 2);
                 for (int kt = 0; kt < k_tiles; ++kt, ++it) {
                     const uint32_t s = it % C::kStages;
-                    HQ_STAMP(rank, it, 0);
                     ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ((it / C::kStages) & 1u) ^ 1u, abort,
                                   kStatusProducer);
                     if (!ok) break;
-                    HQ_STAMP(rank, it, 1);
                     // The MMA threads release a stage with one commit, to the leader's barrier; the
                     // leader's loader passes it on.  A second commit costs the issuing thread about
                     // 300 cycles per k-tile, this relaxed arrival about 200 on a thread with slack
@@ -1431,7 +1463,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         }
                         if (!ok) break;
                     }
-                    HQ_STAMP(2, it, 0);
                     // The scale copies of this k-tile have landed.  Every copy warp waited for the
                     // stage's barrier before it copied and committed, so the operand boxes of both
                     // CTAs have landed too: no second wait here (each one costs this thread, which
@@ -1443,7 +1474,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         ok = wait_bar(ptx::smem_u32(&bars->turn[me]), ((it - 1u) >> 1) & 1u, abort, kStatusMma);
                     }
                     if (!ok) break;
-                    HQ_STAMP(2, it, 1);
                     ptx::tc_fence_after();
                     const uint32_t set = tmem + C::kSfCol0 + (it % C::kSfSets) * C::kSfCols;
                     const uint64_t adesc = ptx::smem_desc(a_base + s * C::kABytes, 16, 1024, 2);
@@ -1622,6 +1652,25 @@ bool make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, const void* base,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Per-device, once: the opt-in to more than 48 KB of dynamic shared memory for one kernel.
+// A failed attempt is not remembered, so the next call tries (and reports) again.
+struct SmemOptIn {
+    std::mutex mu;
+    bool done[64] = {};
+    template <typename Kernel>
+    cudaError_t ensure(Kernel kernel, int bytes, int* dev_out = nullptr) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev_out != nullptr) *dev_out = dev;
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e == cudaSuccess && dev >= 0 && dev < 64) done[dev] = true;
+        return e;
+    }
+};
+
 struct GemmArgs {
     const void* a;
     const void* b;
@@ -1643,18 +1692,20 @@ struct GemmArgs {
     cudaStream_t stream;
 };
 
+// Split-K is taken for a dense problem with one row of at most sm_count / 2 64-wide tiles and
+// at least 8 k-tiles (HALOPS_B200_SPLITK=0 turns it off; read on every call).
+bool split_k_chosen(int group_kind, int tiles_m, int tiles_n, int k_tiles, int sm_count, int epi_op) {
+    const char* e = getenv("HALOPS_B200_SPLITK");
+    if (e != nullptr && e[0] == '0') return false;
+    return group_kind == kGroupDense && tiles_m == 1 && 2 * tiles_n <= sm_count && k_tiles >= 8 &&
+           (epi_op == HQ_EPILOGUE_IDENTITY || epi_op == HQ_EPILOGUE_SIGMOID);
+}
+
 template <int BN, int KIND>
 int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     using C = Cfg<BN, KIND>;
-    static std::once_flag once[16];
-    int dev = 0;
-    HQ_CUDA_TRY(cudaGetDevice(&dev));
-    cudaError_t attr_err = cudaSuccess;
-    std::call_once(once[dev & 15], [&] {
-        attr_err = cudaFuncSetAttribute(gemm_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        C::kSmemBytes);
-    });
-    HQ_CUDA_TRY(attr_err);
+    static SmemOptIn opt_in;
+    HQ_CUDA_TRY(opt_in.ensure(gemm_kernel<BN, KIND>, C::kSmemBytes));
 
     CUtensorMap tm_a, tm_b, tm_d;
     // M < 128: the A box holds only the rows that exist (rounded up to the 8-row
@@ -1702,18 +1753,9 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     const int k_tiles = int(g.k_bytes / kBKBytes);
     if constexpr (BN == 64) {
         // One row of at most sm_count / 2 tiles and a long K: two CTAs per tile, half of K each.
-        static const bool split_ok = [] {
-            const char* e = getenv("HALOPS_B200_SPLITK");
-            return e == nullptr || e[0] != '0';
-        }();
-        if (split_ok && g.grp.kind == kGroupDense && tiles_m == 1 && 2 * tiles_n <= g.sm_count && k_tiles >= 8 &&
-            (g.epi_op == HQ_EPILOGUE_IDENTITY || g.epi_op == HQ_EPILOGUE_SIGMOID)) {
-            static std::once_flag once_split[16];
-            std::call_once(once_split[dev & 15], [&] {
-                attr_err = cudaFuncSetAttribute(gemm_kernel<BN, KIND, true>,
-                                                cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-            });
-            HQ_CUDA_TRY(attr_err);
+        if (split_k_chosen(g.grp.kind, tiles_m, tiles_n, k_tiles, g.sm_count, g.epi_op)) {
+            static SmemOptIn opt_in_split;
+            HQ_CUDA_TRY(opt_in_split.ensure(gemm_kernel<BN, KIND, true>, C::kSmemBytes));
             HQ_CUDA_TRY(launch(gemm_kernel<BN, KIND, true>, dim3(2 * tiles_n), dim3(kThreads), size_t(C::kSmemBytes),
                                g.stream, g.pdl, 2, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.bias, g.epi_op, g.out,
                                g.ldo, g.m, g.n, k_tiles, g.kq_dim, tiles_m, tiles_n, a_rows,
@@ -1730,15 +1772,9 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
 template <int BN, int KIND>
 int launch_pair(const GemmArgs& g, char* err, size_t errlen) {
     using C = Cfg2<BN, KIND>;
-    static std::once_flag once[16];
+    static SmemOptIn opt_in;
     int dev = 0;
-    HQ_CUDA_TRY(cudaGetDevice(&dev));
-    cudaError_t attr_err = cudaSuccess;
-    std::call_once(once[dev & 15], [&] {
-        attr_err = cudaFuncSetAttribute(gemm_pair_kernel<BN, KIND>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    });
-    HQ_CUDA_TRY(attr_err);
+    HQ_CUDA_TRY(opt_in.ensure(gemm_pair_kernel<BN, KIND>, C::kSmemBytes, &dev));
 
     const uint64_t atoms_a = uint64_t((g.m + 127) / 128) * uint64_t(g.kq_dim);
     const uint64_t atoms_b = uint64_t((g.n + 127) / 128) * uint64_t(g.kq_dim);
@@ -1761,8 +1797,11 @@ int launch_pair(const GemmArgs& g, char* err, size_t errlen) {
     const int tiles_m = (g.m + 255) / 256;
     const int tiles_n = g.n / BN;
     // persistent grid: no more clusters than can be resident at once
-    static int max_clusters[16];
-    if (max_clusters[dev & 15] == 0) {
+    static int max_clusters[64];
+    static std::mutex max_clusters_mutex;
+    std::lock_guard<std::mutex> max_clusters_lock(max_clusters_mutex);
+    const int slot = dev >= 0 && dev < 64 ? dev : 63;
+    if (max_clusters[slot] == 0 || dev != slot) {
         cudaLaunchConfig_t occ = {};
         occ.gridDim = dim3(2 * 74);
         occ.blockDim = dim3(C::kThreads);
@@ -1776,12 +1815,9 @@ int launch_pair(const GemmArgs& g, char* err, size_t errlen) {
         occ.numAttrs = 1;
         int n = 0;
         HQ_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<BN, KIND>, &occ));
-        max_clusters[dev & 15] = n > 0 ? n : 1;
-        if (getenv("HALOPS_B200_TRACE") != nullptr) {
-            fprintf(stderr, "[gemm] pair tile %d: max active clusters %d\n", BN, n);
-        }
+        max_clusters[slot] = n > 0 ? n : 1;
     }
-    const int clusters = min(min(g.sm_count / 2, max_clusters[dev & 15]), tiles_m * tiles_n);
+    const int clusters = min(min(g.sm_count / 2, max_clusters[slot]), tiles_m * tiles_n);
     const int k_tiles = int(g.k_bytes / kBKBytes);
     HQ_CUDA_TRY(launch(gemm_pair_kernel<BN, KIND>, dim3(2 * clusters), dim3(C::kThreads), size_t(C::kSmemBytes),
                        g.stream, g.pdl, 2, tm_a, tm_b, tm_d, tm_sfa, tm_sfb, g.alpha, g.bias, g.epi_op, k_tiles, g.kq_dim, tiles_m,
@@ -1909,9 +1945,13 @@ extern "C" int hq_describe_tile(int64_t m, int64_t n, int64_t k, int mode, int s
                         (long long)k);
     }
     if (buf != nullptr && buflen > 0) {
-        snprintf(buf, buflen, "[gemm] mode=dense kind=%s m=%lld n=%lld k=%lld sm=%d -> %dx%d/%d pair=%d",
+        // (the Identity epilogue is assumed for the split-K note)
+        const bool split = pick.bn == 64 && !pick.pair &&
+                           hq::split_k_chosen(hq::kGroupDense, int((m + hq::kBM - 1) / hq::kBM), int(n / 64),
+                                              int(k / 128), sm > 0 ? sm : 148, HQ_EPILOGUE_IDENTITY);
+        snprintf(buf, buflen, "[gemm] mode=dense kind=%s m=%lld n=%lld k=%lld sm=%d -> %dx%d/%d pair=%d splitk=%d",
                  hq::mode_name(mode), (long long)m, (long long)n, (long long)k, sm, pick.pair ? 256 : hq::kBM,
-                 pick.bn, mode == HQ_MODE_W8A8_MXFP8 ? 128 : 256, pick.pair ? 1 : 0);
+                 pick.bn, mode == HQ_MODE_W8A8_MXFP8 ? 128 : 256, pick.pair ? 1 : 0, split ? 1 : 0);
     }
     return HQ_OK;
 }
@@ -2028,11 +2068,11 @@ int dense_gemm_impl(const void* a, const void* b, const void* sfa, const void* s
     g.kq_dim = int(sf_k / 4);
     g.sm_count = sm;
     g.pdl = use_pdl != 0;
-    static const bool direct = [] {
+    {
+        // test switch, read on every call: store every tile from registers
         const char* e = getenv("HALOPS_B200_EPILOGUE");
-        return e != nullptr && strcmp(e, "direct") == 0;
-    }();
-    g.direct_store = direct;
+        g.direct_store = e != nullptr && strcmp(e, "direct") == 0;
+    }
     g.stream = static_cast<cudaStream_t>(stream);
 
 #define HQ_DISPATCH(KIND)                                                            \
@@ -2098,6 +2138,7 @@ extern "C" int hq_dense_gemm_situ_quant(const void* a, const void* b, const void
     sp.inv_beta = 1.0f / situ_beta;
     sp.lin = situ_linear_beta;
     sp.inv_lin = situ_linear_beta != 0.0f ? 1.0f / situ_linear_beta : 0.0f;
+    sp.valid_rows = int(m);
     return hq::dense_gemm_impl(a, b, sfa, sfb, out_q, bias, nullptr, m, n, k, sfa_bytes, sfb_bytes, n / 4,
                                HQ_MODE_W8A8_MXFP8, HQ_EPILOGUE_SITU_QUANT, &sp, sm_count, use_pdl, device, stream,
                                err, errlen);
@@ -2334,6 +2375,7 @@ extern "C" int hq_batch_gemm_quant(const void* a, const void* b, const void* sfa
     sp.kb_out = int(kb_out);
     sp.gate = static_cast<const __nv_bfloat16*>(gate);
     sp.gate_ld = gate_ld;
+    sp.valid_rows = int(m);
     return hq::grouped_gemm_impl(hq::kGroupBatch, a, b, sfa, sfb, out_q, bias, nullptr, nullptr, batches, m,
                                  batches * m, n, k, sfa_bytes, sfb_bytes, ldq / 2, HQ_MODE_W8A8_MXFP8, epilogue, &sp,
                                  sm_count, use_pdl, device, stream, err, errlen);
@@ -2471,15 +2513,8 @@ extern "C" int hq_low_latency_gemm(const void* a, const void* b, const void* sfa
     p.a_rows = a_rows;
     p.sigmoid = use_sigmoid ? 1 : 0;
 
-    static std::once_flag once[16];
-    int dev = 0;
-    HQ_CUDA_TRY(cudaGetDevice(&dev));
-    cudaError_t attr_err = cudaSuccess;
-    std::call_once(once[dev & 15], [&] {
-        attr_err = cudaFuncSetAttribute(hq::ll_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        hq::kLlSmemBytes);
-    });
-    HQ_CUDA_TRY(attr_err);
+    static hq::SmemOptIn opt_in;
+    HQ_CUDA_TRY(opt_in.ensure(hq::ll_gemm_kernel, hq::kLlSmemBytes));
     const int tiles = int((n + 63) / 64 + (n2 + 63) / 64);
     HQ_CUDA_TRY(hq::launch(hq::ll_gemm_kernel, dim3(std::min(sm, tiles)), dim3(hq::kLlThreads), size_t(hq::kLlSmemBytes),
                            static_cast<cudaStream_t>(stream), use_pdl != 0, 1, tm_a, tm_b, tm_a2, tm_b2, p));
@@ -2505,10 +2540,15 @@ extern "C" int hq_device_status(int device, void* stream, uint32_t* status, char
     return HQ_OK;
 }
 
-#ifdef HQ_TRACE
-extern "C" int hq_debug_trace(unsigned long long* host, int n) {
-    return cudaMemcpyFromSymbol(host, hq::g_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : 1;
+extern "C" int hq_selftest_bounded_wait(uint32_t limit_us, int device, void* stream, char* err, size_t errlen) {
+    if (limit_us == 0 || limit_us > 100000u) {
+        return hq::fail(err, errlen, HQ_ERR_INVALID, "limit_us must be in [1, 100000], got %u", limit_us);
+    }
+    const hq::DeviceGuard guard(device);
+    if (!guard.ok()) return hq::fail(err, errlen, HQ_ERR_CUDA, "cannot select CUDA device %d", device);
+    HQ_CUDA_TRY(hq::launch(hq::wait_selftest_kernel, dim3(1), dim3(64), size_t(0), static_cast<cudaStream_t>(stream),
+                           false, 1, uint64_t(limit_us) * 1000ull));
+    return HQ_OK;
 }
-#endif
 
 extern "C" const char* hq_version(void) { return "halops_b200 0.1 (sm_100a)"; }

@@ -34,8 +34,13 @@ def interleave_gate_up(t: torch.Tensor) -> torch.Tensor:
     """Reorder ``[gate; up]`` rows into alternating blocks of 16 rows (gate rows
     ``16i..16i+15``, then up rows ``16i..16i+15``), the row order the
     reference's SituQuant epilogue expects (``halops/gemm/dense_gemm.py:30-41``)."""
-    gate, up = t.view(2, -1, _GLU_INTERLEAVE, *t.shape[1:]).unbind(0)
-    return torch.stack([gate, up], 1).flatten(0, 2)
+    half = t.size(0) // 2
+    if t.size(0) != 2 * half or half % _GLU_INTERLEAVE != 0:
+        raise RuntimeError(f"interleave_gate_up needs 2 * I rows with I a multiple of {_GLU_INTERLEAVE}, "
+                           f"got {t.size(0)}")
+    # output block 2i is gate block i, output block 2i + 1 is up block i
+    blocks = t.reshape(2, half // _GLU_INTERLEAVE, _GLU_INTERLEAVE, *t.shape[1:])
+    return blocks.transpose(0, 1).reshape(t.shape)
 
 
 def _check(cond: bool, msg: str) -> None:
@@ -74,14 +79,18 @@ def dense_gemm(
         use_pdl: launch with programmatic stream serialisation.
         bias: optional [N] bfloat16 vector, ``w8a8-mxfp8`` only, M a multiple of 256
             (the reference's rule).
-        epilogue: ``EpilogueOp.Identity``, ``EpilogueOp.Sigmoid``
-            (``sigmoid(alpha * input @ weight^T + bias)``) or ``EpilogueOp.SituQuant``
-            (``w8a8-mxfp8`` SiTU-GLU: with ``y = input @ weight^T + bias`` and the
-            ``[gate; up]`` rows of weight, sfb and bias reordered by ``interleave_gate_up``,
-            ``output`` [M, N/2] float8_e4m3fn holds ``situ_beta * tanh(gate / situ_beta) *
-            sigmoid(gate) * situ_linear_beta * tanh(up / situ_linear_beta)`` (``up`` as is
-            when ``situ_linear_beta`` is None) with UE8M0 scales per 32 columns in
-            ``output_sf``).
+        epilogue: what happens to ``y = alpha * input @ weight^T + bias`` before it is stored.
+            ``EpilogueOp.Identity`` stores ``bf16(y)``; ``EpilogueOp.Sigmoid`` stores
+            ``bf16(sigmoid(y))``.  ``EpilogueOp.SituQuant`` (``w8a8-mxfp8`` only) is the fused
+            SiTU-GLU activation plus re-quantisation: the weight holds a gate and an up
+            projection whose rows (and those of sfb and bias) were put in
+            ``interleave_gate_up`` order, so every 32 accumulator columns carry 16 gate
+            values ``g`` and the 16 matching up values ``u``.  The kernel forms
+            ``z = situ_beta * tanh(g / situ_beta) * sigmoid(g) * c(u)`` with
+            ``c(u) = situ_linear_beta * tanh(u / situ_linear_beta)``, or ``c(u) = u`` when
+            ``situ_linear_beta`` is None, and writes ``z`` as MXFP8: ``output`` is then
+            ``[M, N/2]`` float8_e4m3fn and ``output_sf`` receives one UE8M0 scale per 32
+            output columns.
         output_sf: SfAtom scales of the quantised output ([ceil(M/128)*128, N/64] uint8).
         situ_beta / situ_linear_beta: gate and up soft-caps.
     """

@@ -292,6 +292,19 @@ int hq_sm_count(int device);
 int hq_device_status(int device, void* stream, uint32_t* status, char* err,
                      size_t errlen);
 
+/*
+ * Launches a one-CTA kernel whose bounded wait runs out after `limit_us`
+ * microseconds (1..100000): a thread waits on an mbarrier that nothing arrives
+ * on, gives up, records the "MMA role" code 0x02 in the status word and raises
+ * the CTA's abort flag, on which a second waiting thread leaves.  The next
+ * hq_device_status on the same stream therefore returns HQ_ERR_DEVICE with
+ * status 0x02, and the one after it 0.  This exercises, with nothing in
+ * flight, the code every GEMM role runs when a wait times out.  The reference
+ * has no counterpart (its waits are unbounded, csrc/common/ptx.cuh:131-139).
+ */
+int hq_selftest_bounded_wait(uint32_t limit_us, int device, void* stream,
+                             char* err, size_t errlen);
+
 /* Human-readable description of the tile the GEMM dispatch picks for a shape
  * (what the reference prints under IR_GEMM_TRACE,
  * csrc/kernel/gemm/gemm_dispatch.cuh:389-416).  Returns 0 and fills `buf`, or

@@ -72,8 +72,9 @@ def batch_gemm_ref(a_q, b_q, sfa, sfb, mode: str = "w8a8-mxfp8", alpha=None, bia
     ``ref_batch_gemm_fp4``) and the token-major output of ``assert_close_per_batch``
     there: ``a_q`` [B, M, K or K/2] with ``sfa`` in SfAtom order over the stacked
     ``B * M`` rows, ``b_q`` [B, N, K or K/2] with ``sfb`` in SfAtom order per batch.
-    The bias is added to the float32 product (the reference model adds it after a
-    bfloat16 rounding; the difference is below the comparison tolerance)."""
+    As in the reference model, the product is rounded to bfloat16 first and the bias is
+    added to that in bfloat16 arithmetic; with ``out_dtype=torch.float32`` nothing is
+    rounded and the bias is added to the float32 product."""
     a_q = _np(a_q)
     b_q = _np(b_q)
     batches, m = a_q.shape[0], a_q.shape[1]
@@ -89,7 +90,11 @@ def batch_gemm_ref(a_q, b_q, sfa, sfb, mode: str = "w8a8-mxfp8", alpha=None, bia
         if alpha is not None:
             acc = acc * float(alpha[b])
         if bias is not None:
-            acc = acc + bias[b].float().cpu().reshape(1, n)
+            row = bias[b].cpu().reshape(1, n)
+            if out_dtype == torch.bfloat16:
+                acc = (acc.to(torch.bfloat16) + row.to(torch.bfloat16)).float()
+            else:
+                acc = acc + row.float()
         out[:, b * n:(b + 1) * n] = acc
     return out.to(out_dtype)
 
@@ -126,6 +131,11 @@ def group_gemm_ref(a_q, b_q, sfa, sfb, expert_of_row, mode: str = "w8a8-mxfp8", 
         if alpha is not None:
             acc = acc * float(alpha[e])
         if bias is not None:
-            acc = acc + bias[e].float().cpu().reshape(1, n)
+            # the reference models round the product to bfloat16 and add the bias in bfloat16
+            row = bias[e].cpu().reshape(1, n)
+            if out_dtype == torch.bfloat16:
+                acc = (acc.to(torch.bfloat16) + row.to(torch.bfloat16)).float()
+            else:
+                acc = acc + row.float()
         out[rows] = acc
     return out.to(out_dtype)

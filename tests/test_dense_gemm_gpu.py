@@ -369,10 +369,14 @@ def test_situ_quant_epilogue(hq, m, n, k, with_bias, beta, linear_beta):
     q = torch.empty([m, n // 2], dtype=torch.float8_e4m3fn, device="cuda")
     kb_out = n // 2 // 32
     m_sf = (m + 127) // 128 * 128
-    sf = torch.zeros([m_sf * kb_out], dtype=torch.uint8, device="cuda")
+    # not cleared by the caller: the kernel writes the zero bytes of the padding rows itself
+    sf = torch.full([m_sf * kb_out], 0xAB, dtype=torch.uint8, device="cuda")
     hq.dense_gemm(aq, wq, sfa, sfb, q, b_il, None, -1, "w8a8-mxfp8", True, hq.EpilogueOp.SituQuant, sf, beta,
                   linear_beta)
     assert hq.device_status() == 0
+    pad = torch.ones(sf.numel(), dtype=torch.bool)
+    pad[torch.from_numpy(oracle.sf_atom_offsets(m, kb_out)).flatten()] = False
+    assert (sf.cpu()[pad] == 0).all(), "padding rows of output_sf must be zero bytes"
     sf_log = torch.from_numpy(oracle.unswizzle_sf(sf.cpu().numpy().reshape(m_sf, kb_out), m))
     scale = torch.exp2(sf_log.float() - 127).repeat_interleave(32, 1)
     deq = q.float().cpu() * scale
@@ -394,13 +398,39 @@ def test_situ_quant_epilogue(hq, m, n, k, with_bias, beta, linear_beta):
 def test_split_k_shapes(hq, monkeypatch, mode, m, n, k):
     """One row of at most 74 64-wide tiles and at least 8 k-tiles: two CTAs share a tile, half
     of K each, partial sums through distributed shared memory.  The result is deterministic
-    and within a bfloat16 rounding of the unsplit kernel."""
+    and within a bfloat16 rounding of the unsplit kernel's (the two halves of K are summed in
+    float32 in another order)."""
     a, b = _rand(m, k, 21), _rand(n, k, 22, "weight")
     aq, bq, sfa, sfb = _quantize(hq, a, b, mode)
-    assert "128x64" in hq.describe_tile(m, n, k, mode)
+    monkeypatch.setenv("HALOPS_B200_TILE", "64")
+    monkeypatch.setenv("HALOPS_B200_SPLITK", "0")
+    assert "128x64" in hq.describe_tile(m, n, k, mode) and "splitk=0" in hq.describe_tile(m, n, k, mode)
+    unsplit = _gemm(hq, aq, bq, sfa, sfb, mode)
+    monkeypatch.delenv("HALOPS_B200_SPLITK")
+    assert "splitk=1" in hq.describe_tile(m, n, k, mode)
     out = _gemm(hq, aq, bq, sfa, sfb, mode)
     _check(out, aq, bq, sfa, sfb, mode)
     assert torch.equal(out, _gemm(hq, aq, bq, sfa, sfb, mode, use_pdl=True))
+    # one bfloat16 step (2^-8 relative) plus the float32 reordering noise near zero
+    diff = (out.float() - unsplit.float()).abs()
+    assert (diff <= unsplit.float().abs() * 2 ** -7 + 1e-3 * unsplit.float().abs().max()).all()
+
+
+@pytest.mark.parametrize("mode, m, n, k", [("w8a8-mxfp8", 256, 512, 1024), ("w8a8-mxfp8", 100, 256, 512),
+                                           ("w4a4-nvfp4", 384, 256, 512), ("w8a8-mxfp8", 1024, 2048, 1024)],
+                         ids=lambda v: str(v))
+def test_register_store_epilogue_equals_tma_store(hq, monkeypatch, mode, m, n, k):
+    """HALOPS_B200_EPILOGUE=direct stores every tile of the single-CTA kernel from registers,
+    row by row, instead of through the staging buffers and TMA stores: same bits."""
+    a, b = _rand(m, k, 23), _rand(n, k, 24)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, mode)
+    monkeypatch.setenv("HALOPS_B200_TILE", "128")
+    staged = _gemm(hq, aq, bq, sfa, sfb, mode)
+    monkeypatch.setenv("HALOPS_B200_EPILOGUE", "direct")
+    direct = _gemm(hq, aq, bq, sfa, sfb, mode)
+    assert hq.device_status() == 0
+    assert torch.equal(staged, direct)
+    _check(direct, aq, bq, sfa, sfb, mode)
 
 
 @pytest.mark.parametrize("mode, m, n, k", [("w8a8-mxfp8", 2048, 2048, 4096), ("w4a4-nvfp4", 1024, 2048, 4096),

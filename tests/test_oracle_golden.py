@@ -148,13 +148,10 @@ def _grouped_fixture(golden_dir, name):
 
 
 def _close_to_model(got, ref, bias):
-    """Without a bias the oracle repeats the model's arithmetic exactly; the models add the
-    bias after rounding the product to bfloat16 and round the sum again, the oracle rounds
-    once, which moves a result by at most one bfloat16 step of the larger of the two."""
-    if bias is None:
-        assert torch.equal(got, ref)
-    else:
-        torch.testing.assert_close(got, ref, rtol=2.0 ** -7, atol=2.0 ** -7 * float(ref.abs().max()))
+    """The oracle repeats the model's arithmetic exactly, with a bias too: the product is
+    rounded to bfloat16 and the bias added to that in bfloat16."""
+    del bias
+    assert torch.equal(got, ref)
 
 
 @pytest.mark.parametrize("mode", ["w8a8-mxfp8", "w4a4-nvfp4"])
