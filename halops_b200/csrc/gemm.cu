@@ -994,7 +994,7 @@ ll_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);
         }
         for (int s = 0; s < 2; ++s) {
-            ptx::mbar_init(ptx::smem_u32(&bars->acc_full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bars->acc_full[s]), 2);  // one commit per MMA-issuing thread
             ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[s]), kEpiWarps);
             ptx::mbar_init(ptx::smem_u32(&bars->turn[s]), 1);
         }
@@ -1137,10 +1137,11 @@ ll_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                     ptx::tc_fence_before();
                     ptx::mbar_arrive(ptx::smem_u32(&bars->turn[me ^ 1u]));
-                    // MMAs complete in the order they were issued, so the commit after the last
-                    // k-tile also covers the other thread's MMAs
                     ptx::tc_commit(ptx::smem_u32(&bars->empty[s]));
-                    if (kt == k_tiles - 1) ptx::tc_commit(ptx::smem_u32(&bars->acc_full[as]));
+                    // a commit tracks the executing thread's operations: each of the two threads
+                    // commits the accumulator after its own last k-tile (K is a multiple of 256,
+                    // so every tile has k-tiles of both)
+                    if (kt >= k_tiles - 2) ptx::tc_commit(ptx::smem_u32(&bars->acc_full[as]));
                 }
             }
         }
@@ -1314,7 +1315,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);  // one tcgen05.commit
         }
         for (int s = 0; s < 2; ++s) {
-            ptx::mbar_init(ptx::smem_u32(&bars->acc_full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bars->acc_full[s]), 2);  // one commit per MMA-issuing thread
             ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[s]), 2 * kEpiWarps);  // leader's copy is used
             ptx::mbar_init(ptx::smem_u32(&bars->overlap_free[s]), 2 * kEpiWarps);
         }
@@ -1452,7 +1453,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 const uint32_t aph = (t >> 1) & 1u;
                 const uint32_t acc = tmem + as * C::kAccStride;
                 for (int kt = 0; kt < k_tiles; ++kt, ++it) {
-                    if ((it & 1u) != me) continue;
+                    if ((it & 1u) != me) {
+                        if (k_tiles == 1) {
+                            // A tile of one k-tile has nothing for this thread, but the accumulator's
+                            // barrier expects both threads.  The arrival may not run ahead of the
+                            // previous use of this accumulator stage, hence the same wait the
+                            // issuing thread makes.
+                            ok = wait_bar(ptx::smem_u32(&bars->acc_empty[as]), aph ^ 1u, abort, kStatusMma);
+                            if (!ok) break;
+                            const uint32_t accf = ptx::smem_u32(&bars->acc_full[as]);
+                            ptx::mbar_arrive(accf);
+                            ptx::mbar_arrive_cluster_relaxed(ptx::mapa_cluster(accf, 1));
+                        }
+                        continue;
+                    }
                     const uint32_t s = it % C::kStages;
                     if (kt == 0) {
                         // first k-tile of a tile: the accumulator stage must have been drained
@@ -1499,12 +1513,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     // hand the turn over before the (slow) commits
                     ptx::tc_fence_before();
                     ptx::mbar_arrive(ptx::smem_u32(&bars->turn[me ^ 1u]));
-                    // the loaders of both CTAs may refill stage s once these MMAs have read it;
-                    // MMAs complete in the order they were issued, so the commit after the last
-                    // k-tile also covers the other thread's MMAs
+                    // the loaders of both CTAs may refill stage s once these MMAs have read it
                     // (the leader's loader passes the release on to the other CTA)
                     ptx::tc_commit_pair(ptx::mapa_cluster(ptx::smem_u32(&bars->empty[s]), 0));
-                    if (kt == k_tiles - 1) {
+                    // A commit tracks the operations of the thread that executes it, so each of
+                    // the two threads commits the accumulator after its own last k-tile of the
+                    // tile; the epilogue starts when both have completed.
+                    if (kt >= k_tiles - 2) {
                         const uint32_t accf = ptx::smem_u32(&bars->acc_full[as]);
                         ptx::tc_commit_pair(ptx::mapa_cluster(accf, 0));
                         ptx::tc_commit_pair(ptx::mapa_cluster(accf, 1));

@@ -8,7 +8,10 @@ with no data-path collective.  ``N/w`` must be a multiple of 128 so that every
 shard starts on an SfAtom boundary: the atoms of the swizzled scale tensor are
 ordered by 128-row tile first, so a shard's scales are one contiguous byte
 range of the global ``sfb`` (no re-swizzle).  An optional all-gather over NCCL
-assembles the full ``[M, N]`` output on every rank.
+assembles the full ``[M, N]`` output on every rank; ``gathered`` overlaps it
+with the GEMM by working on blocks of rows: while NCCL moves block ``i`` on a
+second stream, the GEMM computes block ``i + 1`` on a grid that leaves a few SMs
+to NCCL's kernels.
 
 One process per GPU (``torch.distributed``); the kernels run on each rank's
 current stream.
@@ -83,6 +86,8 @@ class ColumnParallelDenseGemm:
             raise RuntimeError("a weight shard must have a multiple of 128 rows")
         self.alpha = None
         self._staging = None
+        self._blocks = None
+        self._comm_stream = None
 
     def set_alpha(self, alpha: torch.Tensor) -> None:
         """Per-tensor float32 ``[1]`` factor of the NVFP4 recipe."""
@@ -113,12 +118,85 @@ class ColumnParallelDenseGemm:
                                           out_local.contiguous(), group=self.group)
         return self._staging
 
+    # ------------------------------------------------------------------ overlapped all-gather
+
+    @staticmethod
+    def default_comm_sms(world: int) -> int:
+        """SMs the GEMM leaves free while an all-gather runs beside it.  NCCL's kernels need
+        SMs of their own: the GEMM is persistent with one CTA per SM that takes all of the
+        SM's shared memory, so nothing else becomes resident next to it."""
+        return 0 if world <= 1 else (8 if world == 2 else 16)
+
+    def gathered(self, xq: torch.Tensor, sfa: torch.Tensor, blocks: int = 8,
+                 comm_sms: Optional[int] = None) -> torch.Tensor:
+        """GEMM and all-gather overlapped.  The rows of the activation are cut into
+        ``blocks`` blocks (each a multiple of 128 rows, so a block's scales are a contiguous
+        byte range of ``sfa``); the GEMM of block ``i + 1`` runs on the current stream while
+        NCCL gathers block ``i`` on a second one.  Returns ``[blocks, world, M / blocks, N/w]``:
+        entry ``[b, r]`` holds rows ``[b M / blocks, (b + 1) M / blocks)`` of rank ``r``'s
+        columns.  ``gathered_as_matrix`` turns it into ``[M, N]`` with one copy.  The current
+        stream waits for the last gather before this returns control to later work on it."""
+        m = xq.size(0)
+        while blocks > 1 and (m % blocks != 0 or (m // blocks) % 128 != 0):
+            blocks -= 1
+        rows = m // blocks
+        shape = [blocks, self.world, rows, self.n_local]
+        if self._blocks is None or list(self._blocks.shape) != shape or self._blocks.device != xq.device:
+            self._blocks = torch.empty(shape, dtype=torch.bfloat16, device=xq.device)
+        staging = self._blocks
+        kb_dim = sfa.numel() // ((m + 127) // 128 * 128)
+        sfa_flat = sfa.reshape(-1)
+        on_gpu = xq.is_cuda
+        sms = -1
+        comm = cur = None
+        if on_gpu and self.world > 1:
+            comm_sms = self.default_comm_sms(self.world) if comm_sms is None else comm_sms
+            total = torch.cuda.get_device_properties(xq.device).multi_processor_count
+            sms = max(2, total - comm_sms)
+            if self._comm_stream is None or self._comm_stream.device != xq.device:
+                self._comm_stream = torch.cuda.Stream(xq.device, priority=-1)
+            comm = self._comm_stream
+            cur = torch.cuda.current_stream(xq.device)
+            # the previous call's gathers have been waited for by its last line; this one
+            # only has to keep the comm stream behind everything queued on the current one
+            comm.wait_stream(cur)
+        for b in range(blocks):
+            mine = staging[b, self.rank]
+            # (a single block may have any number of rows: it takes the whole, padded scale tensor)
+            block_sfa = sfa if blocks == 1 else sfa_flat[b * rows * kb_dim:(b + 1) * rows * kb_dim].view(rows, kb_dim)
+            self._gemm(xq[b * rows:(b + 1) * rows], self.wq, block_sfa, self.sfb, mine, None, self.alpha, sms,
+                       self.mode)
+            if self.world == 1:
+                continue
+            flat = staging[b].view(self.world * rows, self.n_local)
+            if comm is None:
+                self._dist.all_gather_into_tensor(flat, mine, group=self.group)
+            else:
+                done = torch.cuda.Event()
+                done.record(cur)
+                comm.wait_event(done)
+                with torch.cuda.stream(comm):
+                    # in place: rank r's input is block r of the output
+                    self._dist.all_gather_into_tensor(flat, mine, group=self.group)
+        if comm is not None:
+            cur.wait_stream(comm)
+        return staging
+
+    @staticmethod
+    def gathered_as_matrix(staging: torch.Tensor) -> torch.Tensor:
+        """``[blocks, world, rows, N/w]`` -> ``[M, N]`` (one copy)."""
+        b, w, rows, nl = staging.shape
+        return staging.permute(0, 2, 1, 3).reshape(b * rows, w * nl)
+
     @staticmethod
     def as_matrix(gathered: torch.Tensor) -> torch.Tensor:
         """``[world, M, N/w]`` -> ``[M, N]`` (one copy)."""
         w, m, nl = gathered.shape
         return gathered.permute(1, 0, 2).reshape(m, w * nl)
 
-    def __call__(self, x: torch.Tensor, gather: bool = False) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, gather: bool = False, overlap: bool = False) -> torch.Tensor:
+        if gather and overlap:
+            xq, sfa = self._quant(x, mode=self.mode)
+            return self.gathered_as_matrix(self.gathered(xq, sfa))
         out = self.local(x)
         return self.as_matrix(self.gather(out)) if gather else out

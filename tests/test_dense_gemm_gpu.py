@@ -171,6 +171,45 @@ def test_config2_large_square_sample_and_linearity(hq):
     assert torch.equal(out2.float(), out.float() * 2)
 
 
+def test_config5_shard_sample_and_linearity(hq):
+    """The N-sharded configuration, one rank's share of 8: M=16384, N=7168, K=8192,
+    activation ~ N(0,1), weight ~ N(0,0.02), on the tile the dispatch picks for it (the
+    2-CTA 256x256 one).  A row sample is checked against the oracle; the whole output
+    through the exact-doubling property of the block scales."""
+    m, n, k = 16384, 7168, 8192
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = torch.randn([m, k], generator=g, device="cuda").to(torch.bfloat16)
+    b = (torch.randn([n, k], generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, "w8a8-mxfp8")
+    assert "pair=1" in hq.describe_tile(m, n, k, "w8a8-mxfp8")
+    out = _gemm(hq, aq, bq, sfa, sfb, "w8a8-mxfp8")
+    _check(out, aq, bq, sfa, sfb, "w8a8-mxfp8", rows=torch.arange(0, m, 128) + torch.arange(128) % 128)
+    out2 = _gemm(hq, aq, bq, sfa + 1, sfb, "w8a8-mxfp8")
+    assert torch.equal(out2.float(), out.float() * 2)
+
+
+@pytest.mark.parametrize("m,n,k", [(8192, 8192, 8192), (16384, 7168, 8192)], ids=lambda v: str(v))
+def test_pair_tile_at_benchmark_sizes_200_runs(hq, monkeypatch, m, n, k):
+    """At the sizes the dispatch uses it for, the 2-CTA kernel (two MMA-issuing threads taking
+    turns per k-tile) gives the single-CTA tile's bits, 200 runs in a row."""
+    g = torch.Generator(device="cuda").manual_seed(6)
+    a = torch.randn([m, k], generator=g, device="cuda").to(torch.bfloat16)
+    b = (torch.randn([n, k], generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    aq, bq, sfa, sfb = _quantize(hq, a, b, "w8a8-mxfp8")
+    monkeypatch.setenv("HALOPS_B200_TILE", "256")
+    assert "pair=0" in hq.describe_tile(m, n, k, "w8a8-mxfp8")
+    single = _gemm(hq, aq, bq, sfa, sfb, "w8a8-mxfp8")
+    monkeypatch.setenv("HALOPS_B200_TILE", "pair256")
+    assert "pair=1" in hq.describe_tile(m, n, k, "w8a8-mxfp8")
+    out = torch.empty_like(single)
+    different = torch.zeros([], dtype=torch.int64, device="cuda")
+    for _ in range(200):
+        hq.dense_gemm(aq, bq, sfa, sfb, out, None, None, -1, "w8a8-mxfp8", True)
+        different += (out.view(torch.int16) != single.view(torch.int16)).any()
+    assert hq.device_status() == 0
+    assert int(different) == 0, f"{int(different)} of 200 runs differ from the single-CTA tile"
+
+
 @pytest.mark.parametrize("m,n,k", [(1344, 16384, 1024), (100, 7168, 512)])
 def test_no_out_of_bounds_write(hq, m, n, k):
     """The output is a view of a larger sentinel-filled buffer; bytes past the

@@ -46,6 +46,11 @@ def _worker():
             layer.set_alpha(alpha)
         got = layer(x, gather=True)
         assert torch.equal(got, want), f"rank {rank} {mode}: gathered output differs"
+        # the same with the gather overlapped block by block (3 blocks of 128 rows here),
+        # twice in a row on the same staging buffer
+        for _ in range(2):
+            got = layer(x, gather=True, overlap=True)
+            assert torch.equal(got, want), f"rank {rank} {mode}: block-wise gathered output differs"
         # ... or slice an already quantised weight (contiguous scale range)
         layer2 = ColumnParallelDenseGemm(shard_quantized_weight(wq, sfb, mode, world, rank), mode=mode)
         if alpha is not None:

@@ -81,6 +81,18 @@ def test_large_scale_case(hq):
     _assert_equal(sf, osf, "scales")
 
 
+@pytest.mark.parametrize("m,k,kind", [(16384, 8192, "normal"), (7168, 8192, "weight")], ids=lambda v: str(v))
+def test_sharded_config_operands(hq, m, k, kind):
+    """The operands of the N-sharded configuration at full size, bit for bit: the
+    replicated 16384 x 8192 activation (N(0,1)) and one rank's 7168 x 8192 weight shard
+    (N(0,0.02)) of 57344 rows over 8 GPUs."""
+    x = _rand(m, k, seed=13, kind=kind)
+    q, sf = _run(hq, x, "w8a8-mxfp8")
+    oq, osf = oracle.quant_group_wise(x, "w8a8-mxfp8")
+    _assert_equal(q, oq, "codes")
+    _assert_equal(sf, osf, "scales")
+
+
 @pytest.mark.parametrize("mode", MODES)
 @pytest.mark.parametrize("kind", ["weight", "student_t"])
 def test_benchmark_distributions(hq, mode, kind):
