@@ -13,7 +13,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libhalops_b200.so")
 SOURCES = ("quant.cu", "gemm.cu")
-HEADERS = ("common.cuh", "ptx.cuh", os.path.join("..", "..", "include", "halops_b200.h"))
+HEADERS = ("common.cuh", "ptx.cuh", "decode.cuh", os.path.join("..", "..", "include", "halops_b200.h"))
 
 
 def _nvcc() -> str:

@@ -100,6 +100,7 @@ struct Barriers {
     uint64_t sf_ready[4];  // the scales of a k-tile are in tensor memory
     uint64_t turn[2];      // pair kernel: hands the MMA issue from one issuer thread to the other
     uint64_t recv_full;    // split-K: the other CTA's partial sums have landed in this CTA's buffer
+    uint64_t epi_sync;     // small-M kernel: rendezvous of the four epilogue warps (a bounded wait, unlike bar.sync)
     uint32_t tmem_base;
     uint32_t abort;
 };
@@ -1632,6 +1633,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
 }
 
+// ---------------------------------------------------------------------------- small M
+#include "decode.cuh"
+
 // ---------------------------------------------------------------------------- host
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -1840,6 +1844,89 @@ int launch_pair(const GemmArgs& g, char* err, size_t errlen) {
     return HQ_OK;
 }
 
+// Switches of the small-M kernel, for experiments and tests (HALOPS_B200_DECODE, a comma-separated
+// list read on every call): "off" sends small M to the 128 x 64 tile instead, "nosplit" keeps
+// every CTA on whole tiles, "split" deals every tile to several CTAs whatever the estimate says,
+// "wide" also takes 65 to 128 activation rows.
+struct DecodeSwitches {
+    bool off = false, nosplit = false, split = false, wide = false;
+};
+DecodeSwitches decode_switches() {
+    DecodeSwitches d;
+    const char* e = getenv("HALOPS_B200_DECODE");
+    if (e == nullptr) return d;
+    d.off = strstr(e, "off") != nullptr;
+    d.nosplit = strstr(e, "nosplit") != nullptr;
+    d.split = !d.nosplit && strstr(e, "split") != nullptr;
+    d.wide = strstr(e, "wide") != nullptr;
+    return d;
+}
+
+// Small M goes to the operand-swapped kernel: dense MXFP8 without bias, plain or sigmoid
+// epilogue, no forced tile.
+bool decode_eligible(int64_t m, int64_t n, int64_t k, int mode, int epi_op, bool has_bias) {
+    const char* forced = getenv("HALOPS_B200_TILE");
+    if (forced != nullptr && forced[0] != '\0') return false;
+    if ((n / 128 + 1) * (k / 256 + 1) >= (int64_t(1) << 31)) return false;
+    // Up to 64 activation rows by default.  With 65 to 128 a stage is half activations, the
+    // weight in flight per CTA halves, and the 128 x 64 tile is faster (18.8 against 16.9 us on
+    // 128 x 8192 x 4096); HALOPS_B200_DECODE=wide sends them here all the same.
+    const DecodeSwitches sw = decode_switches();
+    const int64_t m_max = sw.wide ? 128 : 64;
+    return mode == HQ_MODE_W8A8_MXFP8 && m >= 1 && m <= m_max && n % 64 == 0 && k % 128 == 0 && !has_bias &&
+           (epi_op == HQ_EPILOGUE_IDENTITY || epi_op == HQ_EPILOGUE_SIGMOID) && !sw.off;
+}
+
+int decode_width(int64_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
+
+DecPlan decode_plan(int64_t m, int64_t n, int64_t k_bytes, int sm_count) {
+    const DecodeSwitches sw = decode_switches();
+    return dec_plan(int(n), k_bytes, sm_count, !sw.nosplit, decode_width(m), sw.split);
+}
+
+template <int NACT>
+int launch_decode(const GemmArgs& g, char* err, size_t errlen) {
+    using C = DecCfg<NACT>;
+    static SmemOptIn opt_in;
+    int dev = 0;
+    HQ_CUDA_TRY(opt_in.ensure(gemm_decode_kernel<NACT>, C::kSmemBytes, &dev));
+    DecParams p;
+    p.plan = decode_plan(g.m, g.n, g.k_bytes, g.sm_count);
+    DecScratch scratch;
+    if (!p.plan.aligned && !dec_scratch(dev, g.stream, &scratch)) {
+        // no scratch buffer to be had: whole tiles per CTA need none
+        p.plan.ctas = p.plan.tiles < g.sm_count ? p.plan.tiles : g.sm_count;
+        p.plan.aligned = 1;
+        p.plan.fits32 = 0;
+    }
+    const int x_rows = int((g.m + 7) / 8 * 8);
+    CUtensorMap tm_w, tm_x, tm_o;
+    const bool maps_ok =
+        make_tmap_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes), uint64_t(g.n),
+                     uint64_t(g.k_bytes), kBKBytes, kDecRows, CU_TENSOR_MAP_SWIZZLE_128B) &&
+        make_tmap_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.a, uint64_t(g.k_bytes), uint64_t(g.m),
+                     uint64_t(g.k_bytes), kBKBytes, uint32_t(x_rows), CU_TENSOR_MAP_SWIZZLE_128B) &&
+        // the epilogue stores [16 rows x 32 columns] boxes; rows past M and columns past N are clipped
+        make_tmap_2d(&tm_o, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out, uint64_t(g.n), uint64_t(g.m),
+                     uint64_t(g.ldo) * 2, 32, 16, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (!maps_ok) {
+        return fail(err, errlen, HQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the GEMM operands");
+    }
+    p.sfw = g.sfb;
+    p.sfx = g.sfa;
+    p.scratch = scratch.partials;
+    p.counters = scratch.counters;
+    p.m = g.m;
+    p.n = g.n;
+    p.k_bytes = g.k_bytes;
+    p.kq_dim = g.kq_dim;
+    p.x_rows = x_rows;
+    p.epi_op = g.epi_op;
+    HQ_CUDA_TRY(launch(gemm_decode_kernel<NACT>, dim3(p.plan.ctas), dim3(kDecThreads), size_t(C::kSmemBytes),
+                       g.stream, g.pdl, 1, tm_w, tm_x, tm_o, p));
+    return HQ_OK;
+}
+
 const char* mode_name(int mode) {
     switch (mode) {
         case HQ_MODE_W8A8_MXFP8:
@@ -1958,6 +2045,16 @@ extern "C" int hq_describe_tile(int64_t m, int64_t n, int64_t k, int mode, int s
                         "No dense %s tile for M=%lld (grid M=%lld), N=%lld, K=%lld", hq::mode_name(mode),
                         (long long)(m < 128 ? m : hq_sf_rows(m)), (long long)(m < 128 ? m : hq_sf_rows(m)), (long long)n,
                         (long long)k);
+    }
+    if (hq::decode_eligible(m, n, k, mode, HQ_EPILOGUE_IDENTITY, false)) {
+        const hq::DecPlan plan = hq::decode_plan(m, n, k, sm > 0 ? sm : 148);
+        if (buf != nullptr && buflen > 0) {
+            snprintf(buf, buflen,
+                     "[gemm] mode=dense kind=%s m=%lld n=%lld k=%lld sm=%d -> swap 128x%d/256 pair=0 splitk=%d ctas=%d",
+                     hq::mode_name(mode), (long long)m, (long long)n, (long long)k, sm, hq::decode_width(m),
+                     plan.aligned ? 0 : 1, plan.ctas);
+        }
+        return HQ_OK;
     }
     if (buf != nullptr && buflen > 0) {
         // (the Identity epilogue is assumed for the split-K note)
@@ -2089,6 +2186,19 @@ int dense_gemm_impl(const void* a, const void* b, const void* sfa, const void* s
         g.direct_store = e != nullptr && strcmp(e, "direct") == 0;
     }
     g.stream = static_cast<cudaStream_t>(stream);
+
+    if (!is_situ && hq::decode_eligible(m, n, k, mode, epilogue, bias != nullptr)) {
+        switch (hq::decode_width(m)) {
+            case 16:
+                return hq::launch_decode<16>(g, err, errlen);
+            case 32:
+                return hq::launch_decode<32>(g, err, errlen);
+            case 64:
+                return hq::launch_decode<64>(g, err, errlen);
+            default:
+                return hq::launch_decode<128>(g, err, errlen);
+        }
+    }
 
 #define HQ_DISPATCH(KIND)                                                            \
     if (pick.pair) {                                                                 \
@@ -2563,6 +2673,26 @@ extern "C" int hq_selftest_bounded_wait(uint32_t limit_us, int device, void* str
     if (!guard.ok()) return hq::fail(err, errlen, HQ_ERR_CUDA, "cannot select CUDA device %d", device);
     HQ_CUDA_TRY(hq::launch(hq::wait_selftest_kernel, dim3(1), dim3(64), size_t(0), static_cast<cudaStream_t>(stream),
                            false, 1, uint64_t(limit_us) * 1000ull));
+    return HQ_OK;
+}
+
+extern "C" int hq_selftest_decode_plan(int64_t n, int64_t k, int sm_count, int force_split, char* err,
+                                       size_t errlen) {
+    if (n < 1 || k < 128 || k % 128 != 0 || sm_count < 1) {
+        return hq::fail(err, errlen, HQ_ERR_INVALID, "n >= 1, k a positive multiple of 128 and sm_count >= 1 expected");
+    }
+    hq::DecPlan p = hq::dec_plan(int(n), k, sm_count, true, 16, force_split != 0);
+    if (force_split == 2) {
+        // the general even deal: every CTA one contiguous run of units, whatever the tile boundaries
+        const int64_t units = int64_t(p.tiles) * p.ksteps;
+        p.ctas = int(units < sm_count ? units : sm_count);
+        p.aligned = 0;
+        p.fits32 = units * p.ctas < (int64_t(1) << 32) ? 1 : 0;
+    }
+    if (!hq::dec_plan_selfcheck(p)) {
+        return hq::fail(err, errlen, HQ_ERR_INVALID, "unit deal inconsistent: tiles=%d ksteps=%d ctas=%d aligned=%d",
+                        p.tiles, p.ksteps, p.ctas, p.aligned);
+    }
     return HQ_OK;
 }
 

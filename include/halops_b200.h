@@ -305,6 +305,19 @@ int hq_device_status(int device, void* stream, uint32_t* status, char* err,
 int hq_selftest_bounded_wait(uint32_t limit_us, int device, void* stream,
                              char* err, size_t errlen);
 
+/*
+ * Host-only check of how the small-M kernel deals its (128 weight rows) x (256
+ * bytes of K) units out to `sm_count` CTAs for an [n, k] MXFP8 weight: every
+ * unit worked exactly once, the runs contiguous, and the scratch slots of the
+ * CTAs that share a tile distinct.  `force_split` = 1 checks the split deal
+ * (every tile to a power-of-two number of CTAs) also where the dispatch would
+ * keep whole tiles per CTA, 2 the general even deal of one contiguous run of
+ * units per CTA.  Needs no GPU.  The
+ * reference has no counterpart (its small-M tiles are never split over K).
+ */
+int hq_selftest_decode_plan(int64_t n, int64_t k, int sm_count, int force_split,
+                            char* err, size_t errlen);
+
 /* Human-readable description of the tile the GEMM dispatch picks for a shape
  * (what the reference prints under IR_GEMM_TRACE,
  * csrc/kernel/gemm/gemm_dispatch.cuh:389-416).  Returns 0 and fills `buf`, or

@@ -316,6 +316,21 @@ def test_enum_and_interleave():
     assert r[32:48].tolist() == list(range(16, 32))
 
 
+def test_decode_unit_deal_is_consistent(native):
+    """The small-M kernel's deal of (128 weight rows x 256 bytes of K) units to the CTAs: every
+    unit once, contiguous runs, distinct scratch slots per tile -- checked by the library's
+    host-side self-check over many shapes and SM counts, with and without the even split."""
+    from halops_b200 import _native
+
+    for n in list(range(64, 2049, 64)) + [4736, 7168, 8192, 24576, 32768, 57344]:
+        for k in (128, 256, 384, 1024, 1152, 1536, 2048, 4096, 8192):
+            for sm in (1, 2, 7, 74, 132, 148, 160):
+                for force_split in (0, 1, 2):
+                    _native.call("hq_selftest_decode_plan", n, k, sm, force_split)
+    with pytest.raises(RuntimeError, match="multiple of 128"):
+        _native.call("hq_selftest_decode_plan", 128, 100, 148, 0)
+
+
 def test_describe_tile(native):
     import halops_b200 as hq
 
@@ -324,7 +339,13 @@ def test_describe_tile(native):
     assert "256x256/128 pair=1" in hq.describe_tile(8192, 4096, 4096, sm_count=148)
     # 144 single-CTA tiles fit one wave, 80 pair tiles need two
     assert "128x256/128 pair=0" in hq.describe_tile(1152, 4096, 4096, sm_count=148)
-    assert "128x64/128" in hq.describe_tile(8, 7168, 2048, sm_count=148)
+    # small M: the operand-swapped kernel; whole tiles per CTA, or every tile dealt to several
+    # CTAs when the weight has too few tiles to keep HBM busy
+    assert "swap 128x16/256 pair=0 splitk=0 ctas=56" in hq.describe_tile(8, 7168, 2048, sm_count=148)
+    assert "swap 128x64/256 pair=0 splitk=0 ctas=148" in hq.describe_tile(64, 24576, 1536, sm_count=148)
+    assert "swap 128x16/256 pair=0 splitk=0 ctas=64" in hq.describe_tile(8, 8192, 1024, sm_count=148)
+    assert "swap 128x64/256 pair=0 splitk=1 ctas=128" in hq.describe_tile(64, 4096, 8192, sm_count=148)
+    assert "swap" not in hq.describe_tile(65, 7168, 2048, sm_count=148)
     with pytest.raises(RuntimeError, match="No dense"):
         hq.describe_tile(128, 96, 128, sm_count=148)
 
