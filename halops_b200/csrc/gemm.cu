@@ -1927,6 +1927,92 @@ int launch_decode(const GemmArgs& g, char* err, size_t errlen) {
     return HQ_OK;
 }
 
+// ---------------------------------------------------------------------------- small M without any allocation
+//
+// hq_dense_gemm_small_m_noalloc is for callers that cannot let a library allocate device
+// memory behind their back: code that runs between the begin and end of a stream capture (a
+// cudaMalloc there fails the capture), serving loops that hand all of the GPU's memory to
+// their own pool at start-up and treat a later cudaMalloc as a bug, and real-time paths that
+// must not take the allocator's locks.  The small-M kernel needs scratch memory when it deals
+// one tile of the weight to several CTAs (float32 partial tiles and one counter per tile);
+// hq_dense_gemm gets it from cudaMalloc on first use.  This variant keeps it in the array
+// below, which is part of the library's image: every GPU that loads the library holds these
+// bytes until the process ends, whether the entry point is called or not.
+//
+// Limits that keep the array modest: at most kNoAllocMaxM activation rows (32-column
+// accumulators, 16 KB per partial tile), at most kNoAllocMaxCtas CTAs with two partial tiles
+// each, at most kNoAllocMaxTiles weight tiles of 128 rows.
+constexpr int kNoAllocMaxM = 32;
+constexpr int kNoAllocMaxCtas = 160;
+constexpr int kNoAllocMaxTiles = 4096;
+constexpr size_t kNoAllocPartialFloats = size_t(kNoAllocMaxCtas) * 2 * 32 * kDecRows;  // 5 MiB of float32
+constexpr size_t kNoAllocBytes = kNoAllocPartialFloats * sizeof(float) + size_t(kNoAllocMaxTiles) * sizeof(int);
+
+// In host code this name is only a handle for the runtime's symbol calls; the device address
+// comes from cudaGetSymbolAddress (see noalloc_scratch below).
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+// Device address of the array on the current device, looked up once per device.  The
+// look-up may initialise the module on that device, so the first call on a device should
+// come before any stream capture.
+cudaError_t noalloc_scratch(int dev, DecScratch* out) {
+    static std::mutex mu;
+    static unsigned char* addr[64];
+    std::lock_guard<std::mutex> lock(mu);
+    unsigned char* base = dev >= 0 && dev < 64 ? addr[dev] : nullptr;
+    if (base == nullptr) {
+        const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&base), g_noalloc_scratch);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) addr[dev] = base;
+    }
+    out->partials = reinterpret_cast<float*>(base);
+    out->counters = reinterpret_cast<int*>(base + kNoAllocPartialFloats * sizeof(float));
+    return cudaSuccess;
+}
+
+template <int NACT>
+int launch_decode_noalloc(const GemmArgs& g, const DecPlan& plan, char* err, size_t errlen) {
+    using C = DecCfg<NACT>;
+    static SmemOptIn opt_in;
+    int dev = 0;
+    HQ_CUDA_TRY(opt_in.ensure(gemm_decode_kernel<NACT>, C::kSmemBytes, &dev));
+    DecScratch scratch;
+    HQ_CUDA_TRY(noalloc_scratch(dev, &scratch));
+    DecParams p;
+    p.plan = plan;
+    if (!plan.aligned) {
+        // The array keeps what the last call left in it.  The partial tiles are written before
+        // they are read; the tile counters must start at zero, and a call that was cut short
+        // may have left some counted: clear the ones this launch uses, in stream order.
+        HQ_CUDA_TRY(cudaMemsetAsync(scratch.counters, 0, size_t(plan.tiles) * sizeof(int), g.stream));
+    }
+    const int x_rows = int((g.m + 7) / 8 * 8);
+    CUtensorMap tm_w, tm_x, tm_o;
+    const bool maps_ok =
+        make_tmap_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes), uint64_t(g.n),
+                     uint64_t(g.k_bytes), kBKBytes, kDecRows, CU_TENSOR_MAP_SWIZZLE_128B) &&
+        make_tmap_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.a, uint64_t(g.k_bytes), uint64_t(g.m),
+                     uint64_t(g.k_bytes), kBKBytes, uint32_t(x_rows), CU_TENSOR_MAP_SWIZZLE_128B) &&
+        make_tmap_2d(&tm_o, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out, uint64_t(g.n), uint64_t(g.m),
+                     uint64_t(g.ldo) * 2, 32, 16, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (!maps_ok) {
+        return fail(err, errlen, HQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the GEMM operands");
+    }
+    p.sfw = g.sfb;
+    p.sfx = g.sfa;
+    p.scratch = scratch.partials;
+    p.counters = scratch.counters;
+    p.m = g.m;
+    p.n = g.n;
+    p.k_bytes = g.k_bytes;
+    p.kq_dim = g.kq_dim;
+    p.x_rows = x_rows;
+    p.epi_op = g.epi_op;
+    HQ_CUDA_TRY(launch(gemm_decode_kernel<NACT>, dim3(plan.ctas), dim3(kDecThreads), size_t(C::kSmemBytes), g.stream,
+                       g.pdl, 1, tm_w, tm_x, tm_o, p));
+    return HQ_OK;
+}
+
 const char* mode_name(int mode) {
     switch (mode) {
         case HQ_MODE_W8A8_MXFP8:
@@ -2674,6 +2760,83 @@ extern "C" int hq_selftest_bounded_wait(uint32_t limit_us, int device, void* str
     HQ_CUDA_TRY(hq::launch(hq::wait_selftest_kernel, dim3(1), dim3(64), size_t(0), static_cast<cudaStream_t>(stream),
                            false, 1, uint64_t(limit_us) * 1000ull));
     return HQ_OK;
+}
+
+extern "C" int hq_dense_gemm_small_m_noalloc(const void* a, const void* b, const void* sfa, const void* sfb, void* out,
+                                             int64_t m, int64_t n, int64_t k, int64_t sfa_bytes, int64_t sfb_bytes,
+                                             int64_t ldo, int epilogue, int sm_count, int use_pdl, int device,
+                                             void* stream, char* err, size_t errlen) {
+    using hq::fail;
+    if (epilogue != HQ_EPILOGUE_IDENTITY && epilogue != HQ_EPILOGUE_SIGMOID) {
+        return fail(err, errlen, HQ_ERR_UNSUPPORTED, "Unsupported epilogue %d for w8a8-mxfp8", epilogue);
+    }
+    if (m < 0 || n < 0 || k < 0 || n > INT32_MAX || k > INT32_MAX) {
+        return fail(err, errlen, HQ_ERR_INVALID, "input must be a 2D tensor of shape [M, K]");
+    }
+    if (m > hq::kNoAllocMaxM) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "hq_dense_gemm_small_m_noalloc takes at most %d activation rows (its scratch memory is a fixed "
+                    "array), got M=%lld; use hq_dense_gemm", hq::kNoAllocMaxM, (long long)m);
+    }
+    if ((n + 127) / 128 > hq::kNoAllocMaxTiles) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "hq_dense_gemm_small_m_noalloc takes at most %d weight rows (one counter per 128 rows in a "
+                    "fixed array), got N=%lld; use hq_dense_gemm", hq::kNoAllocMaxTiles * 128, (long long)n);
+    }
+    if (m == 0 || n == 0) return HQ_OK;
+    if (k % 128 != 0 || n % 64 != 0 || k == 0) {
+        return fail(err, errlen, HQ_ERR_INVALID, "No dense w8a8-mxfp8 tile for M=%lld (grid M=%lld), N=%lld, K=%lld",
+                    (long long)m, (long long)m, (long long)n, (long long)k);
+    }
+    const int64_t sf_k = k / 32;
+    if (sfa_bytes < hq_sf_rows(m) * sf_k || sfb_bytes < hq_sf_rows(n) * sf_k) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "sfa / sfb must hold whole 128-row SfAtoms: expected at least %lld and %lld elements, got %lld "
+                    "and %lld", (long long)(hq_sf_rows(m) * sf_k), (long long)(hq_sf_rows(n) * sf_k),
+                    (long long)sfa_bytes, (long long)sfb_bytes);
+    }
+    const hq::DeviceGuard guard(device);
+    if (!guard.ok()) return fail(err, errlen, HQ_ERR_CUDA, "cannot select CUDA device %d", device);
+    const int sm_all = hq_sm_count(device);
+    const int sm = sm_count > 0 ? (sm_count < sm_all || sm_all == 0 ? sm_count : sm_all) : sm_all;
+    if (sm <= 0) return fail(err, errlen, HQ_ERR_CUDA, "cannot query the SM count of device %d", device);
+    if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || out == nullptr) {
+        return fail(err, errlen, HQ_ERR_INVALID, "null pointer argument");
+    }
+    if (!hq::aligned(a, 16) || !hq::aligned(b, 16) || !hq::aligned(sfa, 16) || !hq::aligned(sfb, 16) ||
+        !hq::aligned(out, 16) || ldo < n || ldo % 8 != 0) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "operands, scales and output must be 16-byte aligned and the output row stride a "
+                    "multiple of 8 elements");
+    }
+    // the same deal of the work as hq_dense_gemm makes for this shape, capped by the array's size
+    hq::DecPlan plan = hq::decode_plan(m, n, k, sm);
+    if (plan.ctas > hq::kNoAllocMaxCtas) {
+        return fail(err, errlen, HQ_ERR_INVALID,
+                    "hq_dense_gemm_small_m_noalloc runs on at most %d CTAs, this shape wants %d; pass a smaller sm_count",
+                    hq::kNoAllocMaxCtas, plan.ctas);
+    }
+    hq::GemmArgs g;
+    g.a = a;
+    g.b = b;
+    g.sfa = static_cast<const uint8_t*>(sfa);
+    g.sfb = static_cast<const uint8_t*>(sfb);
+    g.alpha = nullptr;
+    g.bias = nullptr;
+    g.epi_op = epilogue;
+    g.situ = hq::SituParams{};
+    g.out = static_cast<__nv_bfloat16*>(out);
+    g.ldo = ldo;
+    g.m = int(m);
+    g.n = int(n);
+    g.grp = hq::GroupParams{hq::kGroupDense, 1, 0, nullptr};
+    g.k_bytes = k;
+    g.kq_dim = int(sf_k / 4);
+    g.sm_count = sm;
+    g.pdl = use_pdl != 0;
+    g.direct_store = false;
+    g.stream = static_cast<cudaStream_t>(stream);
+    return m <= 16 ? hq::launch_decode_noalloc<16>(g, plan, err, errlen) : hq::launch_decode_noalloc<32>(g, plan, err, errlen);
 }
 
 extern "C" int hq_selftest_decode_plan(int64_t n, int64_t k, int sm_count, int force_split, char* err,

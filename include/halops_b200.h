@@ -306,6 +306,42 @@ int hq_selftest_bounded_wait(uint32_t limit_us, int device, void* stream,
                              char* err, size_t errlen);
 
 /*
+ * MXFP8 dense GEMM for at most 32 activation rows that allocates nothing: no
+ * cudaMalloc, no cudaFree, no allocating library call, on any call.  It has no
+ * counterpart in the reference.  It is for callers that cannot have a library
+ * allocate device memory under them: code between the begin and the end of a
+ * stream capture, servers that give all device memory to their own pool at
+ * start-up, paths that must not take the allocator's locks.  hq_dense_gemm
+ * gets the scratch memory of its small-M kernel (float32 partial tiles and one
+ * counter per 128 weight rows, used when one tile of the weight is dealt to
+ * several CTAs) from cudaMalloc on first use; this entry point keeps it in a
+ * fixed array of 5 MiB + 16 KiB inside the library, which every GPU that loads
+ * the library holds until the process ends.
+ *
+ *   out[m, n] = bf16(a[m, k] . b[n, k]^T), or its sigmoid (epilogue = Identity / Sigmoid);
+ *   operands, scales, strides and alignment as for hq_dense_gemm in "w8a8-mxfp8" mode,
+ *   no bias, no alpha.  Same kernel and same deal of the work as hq_dense_gemm makes for
+ *   the shape, hence the same bits.
+ *
+ * Rejected with HQ_ERR_INVALID and a message: m > 32, n > 524288 (4096 tiles
+ * of 128 rows), a launch of more than 160 CTAs (pass a smaller sm_count).
+ * The first call on a device looks the array's device address up
+ * (cudaGetSymbolAddress) and opts the kernel in to its shared memory; make it
+ * before any stream capture.  All calls on a device share the one array, and
+ * it keeps the last call's contents: the entry point clears the tile counters
+ * it is going to use with a cudaMemsetAsync on `stream` before the launch, and
+ * the partial tiles are written before they are read.  Two calls whose kernels
+ * may overlap on the GPU (different streams, or programmatic launches that run
+ * ahead) race on the array: serialise them.
+ */
+int hq_dense_gemm_small_m_noalloc(const void* a, const void* b, const void* sfa,
+                                  const void* sfb, void* out, int64_t m,
+                                  int64_t n, int64_t k, int64_t sfa_bytes,
+                                  int64_t sfb_bytes, int64_t ldo, int epilogue,
+                                  int sm_count, int use_pdl, int device,
+                                  void* stream, char* err, size_t errlen);
+
+/*
  * Host-only check of how the small-M kernel deals its (128 weight rows) x (256
  * bytes of K) units out to `sm_count` CTAs for an [n, k] MXFP8 weight: every
  * unit worked exactly once, the runs contiguous, and the scratch slots of the
