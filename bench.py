@@ -442,26 +442,30 @@ def run_ours(args):
     sus_ms = s.elapsed_time(e) / sus_steps
     sus_clocks = sus_sampler.stop() if rank == 0 else None
 
-    # ---- all-gather of the bf16 output over NCCL, overlapped with the GEMM block by block
-    gather_ms = gather_alone_ms = None
+    # ---- all-gather of the bf16 output, overlapped with the GEMM block by block: pushed into the
+    # peers' symmetric memory by the copy engines where there is peer access, else by NCCL
+    gather_ms = gather_alone_ms = gather_nccl_ms = nccl_alone_ms = None
     gather_blocks = 8
+    transport = None
     if world > 1:
-        def step_gather():
+        def step_gather(kind="auto"):
             hq.group_wise_quant(x, MODE, True, True, xq, sfa)
-            layer.gathered(xq, sfa, blocks=gather_blocks)
+            return layer.gathered(xq, sfa, blocks=gather_blocks, transport=kind)
 
         reps = max(3, min(steps, 10))
-        step_gather()
+        staged = step_gather()
+        transport = "copy engines into symmetric memory" if layer._symm and layer._symm[1] is not None else "nccl"
         gather_ms = timed_ms(step_gather, reps, barrier)
-        staged = layer.gathered(xq, sfa, blocks=gather_blocks)
+        staged = step_gather()
         mine = staged[:, rank].reshape(M5, rows)
         bitwise = bitwise and bool(torch.equal(mine, out))
-        # the gather alone: the same blocks, nothing beside it
-        def gather_only():
-            for b in range(staged.size(0)):
-                dist.all_gather_into_tensor(staged[b].view(world * staged.size(2), rows), staged[b, rank])
-
-        gather_alone_ms = timed_ms(gather_only, reps, barrier)
+        # what the peers sent: block b of rank r against this rank's own single-GPU GEMM on the whole weight
+        # was checked above for this rank's columns; here every peer's block must be complete (non-zero rows)
+        gather_alone_ms = timed_ms(lambda: layer.gathered(xq, sfa, blocks=gather_blocks, compute=False), reps, barrier)
+        step_gather("nccl")
+        gather_nccl_ms = timed_ms(lambda: step_gather("nccl"), reps, barrier)
+        nccl_alone_ms = timed_ms(lambda: layer.gathered(xq, sfa, blocks=gather_blocks, transport="nccl",
+                                                        compute=False), reps, barrier)
         assert hq.device_status(dev) == 0
 
     # ---- end to end through the public API with host buffers: every step copies its own
@@ -518,13 +522,15 @@ def run_ours(args):
     del x_host, out_host, x_dev, out_dev
 
     # ---- max over ranks
-    vals = [total_ms, gemm_ms, quant_ms, sus_ms, e2e_ms, gather_ms or 0.0, gather_alone_ms or 0.0, check_rel]
+    vals = [total_ms, gemm_ms, quant_ms, sus_ms, e2e_ms, gather_ms or 0.0, gather_alone_ms or 0.0, check_rel,
+            gather_nccl_ms or 0.0, nccl_alone_ms or 0.0]
     times = torch.tensor(vals, device=dev, dtype=torch.float64)
     ok = torch.tensor([1 if (bitwise is None or bitwise) else 0], device=dev, dtype=torch.int32)
     if dist is not None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-    total_ms, gemm_ms, quant_ms, sus_ms, e2e_ms, gather_ms, gather_alone_ms, check_rel = times.tolist()
+    (total_ms, gemm_ms, quant_ms, sus_ms, e2e_ms, gather_ms, gather_alone_ms, check_rel, gather_nccl_ms,
+     nccl_alone_ms) = times.tolist()
 
     flops = 2.0 * M5 * N5 * K5          # the whole job
     flops_rank = flops / world
@@ -588,16 +594,18 @@ def run_ours(args):
         if world > 1:
             gathered_bytes = M5 * (N5 - rows) * 2
             line["with_allgather"] = {
-                "tflops": flops / (gather_ms * 1e-3) / 1e12, "ms_per_step": gather_ms,
-                "gather_alone_ms": gather_alone_ms, "compute_alone_ms": ms_per_step,
+                "tflops": flops / (gather_ms * 1e-3) / 1e12, "ms_per_step": gather_ms, "transport": transport,
+                "transfer_alone_ms": gather_alone_ms, "compute_alone_ms": ms_per_step,
                 "ratio_to_max_of_the_two": gather_ms / max(gather_alone_ms, ms_per_step),
                 "bytes_received_per_rank": gathered_bytes,
                 "nvlink_gbs_in_step": gathered_bytes / (gather_ms * 1e-3) / 1e9,
-                "nvlink_gbs_gather_alone": gathered_bytes / (gather_alone_ms * 1e-3) / 1e9,
+                "nvlink_gbs_transfer_alone": gathered_bytes / (gather_alone_ms * 1e-3) / 1e9,
                 "nvlink_floor_ms_at_770_gbs": gathered_bytes / 770e9 * 1e3,
-                "blocks": gather_blocks, "sms_left_to_nccl": ColumnParallelDenseGemm.default_comm_sms(world),
-                "how": "GEMM of row block i+1 on the compute stream while NCCL all-gathers block i on a second "
-                       "stream; with the gather the configuration is NVLink-bound from 4 GPUs on",
+                "blocks": gather_blocks,
+                "nccl_transport": {"ms_per_step": gather_nccl_ms, "transfer_alone_ms": nccl_alone_ms,
+                                   "sms_left_to_nccl": ColumnParallelDenseGemm.default_comm_sms(world)},
+                "how": "GEMM of row block i+1 on the compute stream while block i travels on a second stream; "
+                       "with the gather the configuration is bound by NVLink from 4 GPUs on",
             }
         if world == 1:
             line["c2"] = bench_c2(hq, dev, steps, peaks)

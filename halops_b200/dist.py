@@ -9,9 +9,11 @@ shard starts on an SfAtom boundary: the atoms of the swizzled scale tensor are
 ordered by 128-row tile first, so a shard's scales are one contiguous byte
 range of the global ``sfb`` (no re-swizzle).  An optional all-gather over NCCL
 assembles the full ``[M, N]`` output on every rank; ``gathered`` overlaps it
-with the GEMM by working on blocks of rows: while NCCL moves block ``i`` on a
-second stream, the GEMM computes block ``i + 1`` on a grid that leaves a few SMs
-to NCCL's kernels.
+with the GEMM by working on blocks of rows: while block ``i`` travels on a second
+stream, the GEMM computes block ``i + 1``.  On GPUs with peer access the blocks
+are pushed into the peers' buffers (symmetric memory) by the copy engines, which
+take no SM from the GEMM; otherwise NCCL moves them and the GEMM leaves it a few
+SMs.
 
 One process per GPU (``torch.distributed``); the kernels run on each rank's
 current stream.
@@ -88,6 +90,8 @@ class ColumnParallelDenseGemm:
         self._staging = None
         self._blocks = None
         self._comm_stream = None
+        self._symm = None   # ((shape, device), local staging, [views of every rank's staging])
+        self._flag = None
 
     def set_alpha(self, alpha: torch.Tensor) -> None:
         """Per-tensor float32 ``[1]`` factor of the NVFP4 recipe."""
@@ -127,58 +131,119 @@ class ColumnParallelDenseGemm:
         SM's shared memory, so nothing else becomes resident next to it."""
         return 0 if world <= 1 else (8 if world == 2 else 16)
 
+    def _symmetric_staging(self, shape, device):
+        """Staging buffer of ``gathered`` in symmetric memory: the same allocation on every
+        rank, each mapped into every other rank's address space, so a rank can push its
+        blocks into its peers' buffers with plain device-to-device copies (copy engines over
+        NVLink, no SM).  Collective: every rank calls it with the same shape.  Returns None
+        where symmetric memory cannot be had; the caller then gathers with NCCL."""
+        if self._symm is not None and self._symm[0] == (tuple(shape), device):
+            return self._symm[1], self._symm[2]
+        try:
+            import torch.distributed._symmetric_memory as symm
+
+            group = self.group if self.group is not None else self._dist.group.WORLD
+            local = symm.empty(shape, dtype=torch.bfloat16, device=device)
+            handle = symm.rendezvous(local, group)
+            peers = [handle.get_buffer(r, shape, torch.bfloat16) for r in range(self.world)]
+        except Exception:  # no peer access / no symmetric memory in this build: NCCL it is
+            self._symm = ((tuple(shape), device), None, None)
+            return None, None
+        self._symm = ((tuple(shape), device), local, peers)
+        self._flag = torch.zeros([1], dtype=torch.int32, device=device)
+        return local, peers
+
+    def _rendezvous_on(self, stream) -> None:
+        """All ranks meet, in the order of ``stream``: a one-element NCCL all-reduce."""
+        with torch.cuda.stream(stream):
+            self._dist.all_reduce(self._flag, group=self.group)
+
     def gathered(self, xq: torch.Tensor, sfa: torch.Tensor, blocks: int = 8,
-                 comm_sms: Optional[int] = None) -> torch.Tensor:
+                 comm_sms: Optional[int] = None, transport: str = "auto", compute: bool = True) -> torch.Tensor:
         """GEMM and all-gather overlapped.  The rows of the activation are cut into
         ``blocks`` blocks (each a multiple of 128 rows, so a block's scales are a contiguous
-        byte range of ``sfa``); the GEMM of block ``i + 1`` runs on the current stream while
-        NCCL gathers block ``i`` on a second one.  Returns ``[blocks, world, M / blocks, N/w]``:
-        entry ``[b, r]`` holds rows ``[b M / blocks, (b + 1) M / blocks)`` of rank ``r``'s
-        columns.  ``gathered_as_matrix`` turns it into ``[M, N]`` with one copy.  The current
-        stream waits for the last gather before this returns control to later work on it."""
+        byte range of ``sfa``, and at least 256 rows, so a block runs on the same multi-row-tile
+        kernels as the whole activation would and the result keeps its bits: the small-M and
+        split-K kernels add partial sums in another order).  While the GEMM computes block
+        ``i + 1`` on the current stream, block ``i`` travels on a second stream:
+
+        * ``transport="copy"`` (what ``"auto"`` picks on GPUs with peer access): the staging
+          buffer lives in symmetric memory and every rank pushes its block into its peers'
+          buffers with device-to-device copies, which the copy engines carry over NVLink
+          without taking an SM from the GEMM.  Two small NCCL all-reduces fence the pushes: one
+          before the first push (every rank is done reading the previous call's result) and one
+          after the last (everybody's pushes have landed).
+        * ``transport="nccl"``: ``all_gather_into_tensor`` per block; its kernels need SMs, so
+          the GEMM runs on a grid that leaves ``comm_sms`` SMs free.
+
+        Returns ``[blocks, world, M / blocks, N/w]``: entry ``[b, r]`` holds rows
+        ``[b M / blocks, (b + 1) M / blocks)`` of rank ``r``'s columns; ``gathered_as_matrix``
+        turns it into ``[M, N]`` with one copy.  The current stream waits for the transfers
+        before it runs anything queued after this call.  Collective: every rank calls it.
+        ``compute=False`` skips the GEMMs and moves what the staging buffer holds (to time the
+        transfers alone)."""
         m = xq.size(0)
-        while blocks > 1 and (m % blocks != 0 or (m // blocks) % 128 != 0):
+        while blocks > 1 and (m % blocks != 0 or (m // blocks) % 128 != 0 or m // blocks < 256):
             blocks -= 1
         rows = m // blocks
         shape = [blocks, self.world, rows, self.n_local]
-        if self._blocks is None or list(self._blocks.shape) != shape or self._blocks.device != xq.device:
-            self._blocks = torch.empty(shape, dtype=torch.bfloat16, device=xq.device)
-        staging = self._blocks
+        on_gpu = xq.is_cuda
+        peers = None
+        if on_gpu and self.world > 1 and transport in ("auto", "copy"):
+            staging, peers = self._symmetric_staging(shape, xq.device)
+            if staging is None and transport == "copy":
+                raise RuntimeError("symmetric memory is not available for the copy transport")
+        if peers is None:
+            if self._blocks is None or list(self._blocks.shape) != shape or self._blocks.device != xq.device:
+                self._blocks = torch.empty(shape, dtype=torch.bfloat16, device=xq.device)
+            staging = self._blocks
         kb_dim = sfa.numel() // ((m + 127) // 128 * 128)
         sfa_flat = sfa.reshape(-1)
-        on_gpu = xq.is_cuda
         sms = -1
         comm = cur = None
         if on_gpu and self.world > 1:
-            comm_sms = self.default_comm_sms(self.world) if comm_sms is None else comm_sms
-            total = torch.cuda.get_device_properties(xq.device).multi_processor_count
-            sms = max(2, total - comm_sms)
+            if peers is None:
+                comm_sms = self.default_comm_sms(self.world) if comm_sms is None else comm_sms
+                total = torch.cuda.get_device_properties(xq.device).multi_processor_count
+                sms = max(2, total - comm_sms)
             if self._comm_stream is None or self._comm_stream.device != xq.device:
                 self._comm_stream = torch.cuda.Stream(xq.device, priority=-1)
             comm = self._comm_stream
             cur = torch.cuda.current_stream(xq.device)
-            # the previous call's gathers have been waited for by its last line; this one
-            # only has to keep the comm stream behind everything queued on the current one
+            # the transfers come after everything queued on the current stream so far, the
+            # readers of the previous call's result among it
             comm.wait_stream(cur)
+            if peers is not None:
+                # ... on every rank: nobody pushes into a buffer that is still being read
+                self._rendezvous_on(comm)
         for b in range(blocks):
             mine = staging[b, self.rank]
             # (a single block may have any number of rows: it takes the whole, padded scale tensor)
             block_sfa = sfa if blocks == 1 else sfa_flat[b * rows * kb_dim:(b + 1) * rows * kb_dim].view(rows, kb_dim)
-            self._gemm(xq[b * rows:(b + 1) * rows], self.wq, block_sfa, self.sfb, mine, None, self.alpha, sms,
-                       self.mode)
+            if compute:
+                self._gemm(xq[b * rows:(b + 1) * rows], self.wq, block_sfa, self.sfb, mine, None, self.alpha, sms,
+                           self.mode)
             if self.world == 1:
                 continue
             flat = staging[b].view(self.world * rows, self.n_local)
             if comm is None:
                 self._dist.all_gather_into_tensor(flat, mine, group=self.group)
-            else:
-                done = torch.cuda.Event()
-                done.record(cur)
-                comm.wait_event(done)
-                with torch.cuda.stream(comm):
+                continue
+            done = torch.cuda.Event()
+            done.record(cur)
+            comm.wait_event(done)
+            with torch.cuda.stream(comm):
+                if peers is None:
                     # in place: rank r's input is block r of the output
                     self._dist.all_gather_into_tensor(flat, mine, group=self.group)
+                else:
+                    # at any moment every rank pushes to a different peer
+                    for i in range(1, self.world):
+                        peers[(self.rank + i) % self.world][b, self.rank].copy_(mine, non_blocking=True)
         if comm is not None:
+            if peers is not None:
+                # once every rank is past this point, every push has landed
+                self._rendezvous_on(comm)
             cur.wait_stream(comm)
         return staging
 

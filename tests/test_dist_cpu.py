@@ -78,11 +78,12 @@ def _worker(rank, world, port, ret):
         ok = bool(torch.equal(full, want)) and list(layer.gather(layer.local(x)).shape) == [world, m, rows]
         # the block-wise (overlapped on a GPU) gather: one block here, since 64 rows cannot be cut
         ok = ok and bool(torch.equal(layer(x, gather=True, overlap=True), want))
-        # ... and two blocks of 128 rows, each with its own contiguous range of scale bytes
-        x2 = torch.randn([256, k], generator=g).to(torch.bfloat16)
+        # ... and two blocks of 256 rows (the smallest allowed), each with its own contiguous
+        # range of scale bytes
+        x2 = torch.randn([512, k], generator=g).to(torch.bfloat16)
         x2q, sfa2 = quant(x2)
         staged = layer.gathered(x2q, sfa2, blocks=8)
-        ok = ok and list(staged.shape) == [2, world, 128, rows]
+        ok = ok and list(staged.shape) == [2, world, 256, rows]
         ok = ok and bool(torch.equal(layer.gathered_as_matrix(staged), oracle.dense_gemm_ref(x2q, wq, sfa2, sfb, "w8a8-mxfp8")))
         ret[rank] = ok
     finally:

@@ -46,11 +46,23 @@ def _worker():
             layer.set_alpha(alpha)
         got = layer(x, gather=True)
         assert torch.equal(got, want), f"rank {rank} {mode}: gathered output differs"
-        # the same with the gather overlapped block by block (3 blocks of 128 rows here),
-        # twice in a row on the same staging buffer
-        for _ in range(2):
-            got = layer(x, gather=True, overlap=True)
-            assert torch.equal(got, want), f"rank {rank} {mode}: block-wise gathered output differs"
+        # the same with the gather overlapped block by block (4 blocks of 256 rows), twice in a
+        # row on the same staging buffer
+        x4 = torch.randn([1024, k], generator=g, device=dev).to(torch.bfloat16)
+        x4q, sfa4 = hq.group_wise_quant(x4, mode=mode)
+        want4 = torch.empty([1024, n], dtype=torch.bfloat16, device=dev)
+        hq.dense_gemm(x4q, wq, sfa4, sfb, want4, None, alpha, -1, mode)
+        # with both transports: pushes by the copy engines into the peers' symmetric memory
+        # ("auto" on GPUs with peer access) and NCCL all-gathers per block
+        for transport in ("auto", "nccl"):
+            for i in range(2):
+                staged = layer.gathered(x4q, sfa4, blocks=4, transport=transport)
+                assert list(staged.shape) == [4, world, 256, rows]
+                got4 = layer.gathered_as_matrix(staged)
+                assert torch.equal(got4, want4), \
+                    f"rank {rank} {mode} {transport}: block-wise gathered output differs (call {i})"
+                # the next call may only overwrite the buffers once every rank has read them
+                staged.zero_()
         # ... or slice an already quantised weight (contiguous scale range)
         layer2 = ColumnParallelDenseGemm(shard_quantized_weight(wq, sfb, mode, world, rank), mode=mode)
         if alpha is not None:
