@@ -15,6 +15,9 @@
 //            map extent, so neither A nor the output is ever padded)
 //   warps 6-9 scales: shared memory -> registers -> tensor memory (tcgen05.st),
 //            one warp per lane quarter, a few k-tiles ahead of the MMAs
+//   warp 10  64-wide dense tiles only: a second MMA issuer that takes every other
+//            k-tile into an accumulator of its own (the epilogue adds the two); one
+//            thread needs about 600 cycles to issue and commit a k-tile of 8 KB
 // Every mbarrier wait is bounded: a role that waits longer than kTimeoutNs
 // records a code in the device status word, raises the CTA's abort flag and
 // all roles leave through the common teardown that frees tensor memory.
@@ -31,7 +34,7 @@ namespace {
 
 constexpr int kBM = 128;           // rows of A per CTA tile
 constexpr int kBKBytes = 128;      // bytes of K per stage row: 128 e4m3 or 256 e2m1
-constexpr int kThreads = 320;      // single-CTA kernel: 10 warps (pair kernel: see Cfg2)
+constexpr int kThreads = 352;      // single-CTA kernel: 11 warps (pair kernel: see Cfg2)
 constexpr int kEpiWarps = 4;
 constexpr int kSfWarps = 4;        // single-CTA kernel: warps 6-9 move the scales into tensor memory
 constexpr int kEpiChunk = 32;      // accumulator columns per tcgen05.ld / TMA store
@@ -81,7 +84,9 @@ struct Cfg {
     static constexpr int kAccStride = BN - kOverlap;
     static constexpr int kSfaCol = kAccStride + BN;  // set 0
     static constexpr int kSfbCol = kSfaCol + kSfKAtoms * 4;
-    static constexpr int kColsUsed = kSfaCol + kSfRegion;
+    // 64-wide tiles: two more accumulator stages, for the second MMA issuer (behind the scales)
+    static constexpr int kDualCol = kSfaCol + kSfRegion;
+    static constexpr int kColsUsed = kDualCol + (BN == 64 ? 2 * BN : 0);
     static constexpr int kTmemCols = kColsUsed <= 32 ? 32 : kColsUsed <= 64 ? 64 : kColsUsed <= 128 ? 128
                                      : kColsUsed <= 256 ? 256 : 512;
     static_assert(kColsUsed <= 512, "tensor memory budget");
@@ -427,8 +432,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const uint8_t* __restrict__ sfb, const float* __restrict__ alpha,
             const __nv_bfloat16* __restrict__ bias, int epi_op, __nv_bfloat16* __restrict__ out, int64_t ldo,
             int M, int N, int k_tiles, int kq_dim, int tiles_m, int tiles_n, int a_rows, int direct_store,
-            const GroupParams grp, const SituParams situ) {
+            int dual_issue, const GroupParams grp, const SituParams situ) {
     using C = Cfg<BN, KIND>;
+    // Two MMA issuers with an accumulator each (64-wide dense tiles, plain epilogues): the k-tiles
+    // of a tile are summed as (even ones) + (odd ones), deterministically, but not in the k order
+    // of the other tiles.
+    const bool dual = BN == 64 && !kSplitK && dual_issue != 0;
     static_assert(!kSplitK || (BN == 64 && 2 * C::kABytes == kBM * BN * 4 && C::kStages >= 6), "split-K buffer");
     // stages of the ring; with split-K the last two A stages hold the partial sums received
     constexpr uint32_t kRing = kSplitK ? C::kStages - 2 : C::kStages;
@@ -462,7 +471,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);
         }
         for (int s = 0; s < 2; ++s) {
-            ptx::mbar_init(ptx::smem_u32(&bars->acc_full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bars->acc_full[s]), dual ? 2 : 1);  // one commit per MMA issuer
             ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[s]), kEpiWarps);
             ptx::mbar_init(ptx::smem_u32(&bars->overlap_free[s]), kEpiWarps);
         }
@@ -530,9 +539,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             // let a dependent kernel start its prologue
             ptx::pdl_launch_dependents();
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+    } else if (warp == 1 || warp == 10) {
+        // ------------------------------------------------------------ MMA issuer(s)
+        const int me = warp == 1 ? 0 : 1;
+        if (lane == 0 && (me == 0 || dual)) {
             uint32_t it = 0;
             uint32_t t = 0;
             bool ok = true;
@@ -541,6 +551,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             for (; ok && work.next(wk); ++t) {
                 const uint32_t as = t & 1u;
                 const uint32_t aph = (t >> 1) & 1u;
+                // (with two issuers both wait here, also the one that has no k-tile in a tile of
+                // one: its arrival below must not run ahead of the stage's previous use)
                 ok = wait_bar(ptx::smem_u32(&bars->acc_empty[as]), aph ^ 1u, abort, kStatusMma);
                 if (!ok) break;
                 if (C::kOverlap != 0 && t > 0) {
@@ -550,10 +562,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     if (!ok) break;
                 }
                 ptx::tc_fence_after();
-                const uint32_t acc = tmem + as * C::kAccStride;
+                const uint32_t acc = tmem + (me == 0 ? as * C::kAccStride : C::kDualCol + as * BN);
                 // a 64-wide tile uses half of a 128-row scale atom
                 const uint32_t sfb_shift = BN == 64 ? uint32_t(wk.sfb_shift) : 0u;
+                bool issued = false;
                 for (int kt = k_begin; kt < k_end; ++kt, ++it) {
+                    if (dual && ((kt - k_begin) & 1) != me) continue;
                     const uint32_t s = it % kRing;
                     const uint32_t ph = (it / kRing) & 1u;
                     // the scales of this k-tile are in their set (the scale warps waited for the
@@ -584,16 +598,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             acc, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2),
                             instr_desc<BN, KIND>(sf_id), set + C::kSfaCol + atom * 4,
                             set + C::kSfbCol + atom * C::kNAtoms * 4 + sfb_shift,
-                            (kt > k_begin || k > 0) ? 1u : 0u);
+                            (issued || k > 0) ? 1u : 0u);
                     }
+                    issued = true;
                     // stage s may be refilled once these MMAs have read it
                     ptx::tc_commit(ptx::smem_u32(&bars->empty[s]));
                 }
-                if (ok) ptx::tc_commit(ptx::smem_u32(&bars->acc_full[as]));
+                if (!ok) break;
+                // a commit tracks the executing thread's operations: every issuer reports its own
+                if (issued) {
+                    ptx::tc_commit(ptx::smem_u32(&bars->acc_full[as]));
+                } else {
+                    ptx::mbar_arrive(ptx::smem_u32(&bars->acc_full[as]));
+                }
             }
         }
     } else if (warp >= 2 + kEpiWarps) {
-        // ------------------------------------------------------------ scales -> tensor memory
+        // ------------------------------------------------------------ scales -> tensor memory (warps 6-9)
         // One SfAtom is 32 rows of 16 bytes; lane l of every lane quarter of tensor memory
         // holds row l in 4 columns (what tcgen05.cp.32x128b.warpx4 would write).  Each of
         // the four warps fills its own quarter from the same shared-memory image.
@@ -737,6 +758,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 } else {
                     ptx::tc_load_32x32(acc + c * kEpiChunk, r);
                     ptx::tc_wait_ld();
+                }
+                if constexpr (BN == 64 && !kSplitK) {
+                    // the second issuer's accumulator (it has k-tiles whenever the tile has two or more)
+                    if (dual && k_end - k_begin > 1) {
+                        uint32_t r2[32];
+                        ptx::tc_load_32x32(tmem + C::kDualCol + as * BN + (lane_base << 16) + c * kEpiChunk, r2);
+                        ptx::tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
+                    }
                 }
                 if constexpr (kSplitK) {
                     // row `ar`, columns [32 c, 32 c + 32) of the 128 x 64 fp32 buffer
@@ -1778,13 +1809,21 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
             HQ_CUDA_TRY(launch(gemm_kernel<BN, KIND, true>, dim3(2 * tiles_n), dim3(kThreads), size_t(C::kSmemBytes),
                                g.stream, g.pdl, 2, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.bias, g.epi_op, g.out,
                                g.ldo, g.m, g.n, k_tiles, g.kq_dim, tiles_m, tiles_n, a_rows,
-                               g.direct_store ? 1 : 0, g.grp, g.situ));
+                               g.direct_store ? 1 : 0, 0, g.grp, g.situ));
             return HQ_OK;
         }
     }
+    // One row of 64-wide dense tiles with a plain epilogue (65 to 128 activation rows, or fewer
+    // when the small-M kernel is not taken): two MMA issuers (see the kernel).  Problems with
+    // several rows of tiles keep one issuer, so that every tile shape sums the k-tiles of an
+    // output element in the same order and gives the same bits.
+    const int dual = BN == 64 && g.grp.kind == kGroupDense && tiles_m == 1 && k_tiles >= 2 &&
+                             (g.epi_op == HQ_EPILOGUE_IDENTITY || g.epi_op == HQ_EPILOGUE_SIGMOID)
+                         ? 1
+                         : 0;
     HQ_CUDA_TRY(launch(gemm_kernel<BN, KIND>, dim3(grid), dim3(kThreads), size_t(C::kSmemBytes), g.stream,
                        g.pdl, 1, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.bias, g.epi_op, g.out, g.ldo, g.m, g.n, k_tiles,
-                       g.kq_dim, tiles_m, tiles_n, a_rows, g.direct_store ? 1 : 0, g.grp, g.situ));
+                       g.kq_dim, tiles_m, tiles_n, a_rows, g.direct_store ? 1 : 0, dual, g.grp, g.situ));
     return HQ_OK;
 }
 

@@ -186,3 +186,24 @@ def test_fewer_sms_and_the_older_tile_agree(hq, monkeypatch):
     _check(old, aq, bq, sfa, sfb)
     diff = (new.float() - old.float()).abs()
     assert (diff <= old.float().abs() * 2 ** -7 + 1e-3 * old.float().abs().max()).all()
+
+
+@pytest.mark.parametrize("m,n,k,env", [(128, 7168, 2048, ""), (100, 24576, 1536, ""), (65, 8192, 4096, ""),
+                                       (128, 192, 256, ""), (128, 320, 128, ""), (8, 7168, 2048, "off"),
+                                       (64, 4736, 1152, "off")], ids=lambda v: str(v))
+def test_one_row_of_64_wide_tiles_with_two_issuers(hq, monkeypatch, m, n, k, env):
+    """65 to 128 activation rows (and fewer with the small-M kernel switched off) run on the
+    128 x 64 tile with the activations as the M of the MMA, where two threads issue the MMAs of
+    alternate k-tiles into accumulators of their own: against the oracle, 20 runs bit-identical,
+    with and without programmatic launch, plain and sigmoid epilogue, a single k-tile too."""
+    if env:
+        monkeypatch.setenv("HALOPS_B200_DECODE", env)
+    assert "128x64/128" in hq.describe_tile(m, n, k)
+    aq, bq, sfa, sfb = _quant(hq, _rand(m, k, 40 + m, "student_t"), _rand(n, k, 41 + m, "weight"))
+    base = _run(hq, aq, bq, sfa, sfb)
+    _check(base, aq, bq, sfa, sfb)
+    for i in range(20):
+        assert torch.equal(base, _run(hq, aq, bq, sfa, sfb, use_pdl=bool(i & 1))), f"run {i} differs"
+    sig = _run(hq, aq, bq, sfa, sfb, epilogue=hq.EpilogueOp.Sigmoid)
+    ref = torch.sigmoid(oracle.dequantize(aq, sfa, "w8a8-mxfp8") @ oracle.dequantize(bq, sfb, "w8a8-mxfp8").T)
+    torch.testing.assert_close(sig.float().cpu(), ref, rtol=2e-2, atol=1e-2)

@@ -436,23 +436,33 @@ def test_situ_quant_epilogue(hq, m, n, k, with_bias, beta, linear_beta):
     ids=lambda v: str(v))
 def test_split_k_shapes(hq, monkeypatch, mode, m, n, k):
     """One row of at most 74 64-wide tiles and at least 8 k-tiles: two CTAs share a tile, half
-    of K each, partial sums through distributed shared memory.  The result is deterministic
-    and within a bfloat16 rounding of the unsplit kernel's (the two halves of K are summed in
-    float32 in another order)."""
+    of K each, partial sums through distributed shared memory.  Without the split the same tile
+    runs with two MMA issuers that take alternate k-tiles into accumulators of their own.  Both
+    are deterministic and within a bfloat16 rounding of each other and of the 128-wide tile
+    (which sums the k-tiles in order)."""
     a, b = _rand(m, k, 21), _rand(n, k, 22, "weight")
     aq, bq, sfa, sfb = _quantize(hq, a, b, mode)
     monkeypatch.setenv("HALOPS_B200_TILE", "64")
     monkeypatch.setenv("HALOPS_B200_SPLITK", "0")
     assert "128x64" in hq.describe_tile(m, n, k, mode) and "splitk=0" in hq.describe_tile(m, n, k, mode)
     unsplit = _gemm(hq, aq, bq, sfa, sfb, mode)
+    _check(unsplit, aq, bq, sfa, sfb, mode)
+    assert torch.equal(unsplit, _gemm(hq, aq, bq, sfa, sfb, mode, use_pdl=True))
     monkeypatch.delenv("HALOPS_B200_SPLITK")
     assert "splitk=1" in hq.describe_tile(m, n, k, mode)
     out = _gemm(hq, aq, bq, sfa, sfb, mode)
     _check(out, aq, bq, sfa, sfb, mode)
     assert torch.equal(out, _gemm(hq, aq, bq, sfa, sfb, mode, use_pdl=True))
-    # one bfloat16 step (2^-8 relative) plus the float32 reordering noise near zero
-    diff = (out.float() - unsplit.float()).abs()
-    assert (diff <= unsplit.float().abs() * 2 ** -7 + 1e-3 * unsplit.float().abs().max()).all()
+
+    def close(x, y):  # one bfloat16 step (2^-8 relative) plus the float32 reordering noise near zero
+        diff = (x.float() - y.float()).abs()
+        return bool((diff <= y.float().abs() * 2 ** -7 + 1e-3 * y.float().abs().max()).all())
+
+    assert close(out, unsplit)
+    if n % 128 == 0:
+        monkeypatch.setenv("HALOPS_B200_TILE", "128")
+        in_order = _gemm(hq, aq, bq, sfa, sfb, mode)
+        assert close(out, in_order) and close(unsplit, in_order)
 
 
 @pytest.mark.parametrize("mode, m, n, k", [("w8a8-mxfp8", 256, 512, 1024), ("w8a8-mxfp8", 100, 256, 512),
