@@ -92,6 +92,7 @@ class ColumnParallelDenseGemm:
         self._comm_stream = None
         self._symm = None   # ((shape, device), local staging, [views of every rank's staging])
         self._flag = None
+        self._push_streams = None
 
     def set_alpha(self, alpha: torch.Tensor) -> None:
         """Per-tensor float32 ``[1]`` factor of the NVFP4 recipe."""
@@ -216,6 +217,9 @@ class ColumnParallelDenseGemm:
             if peers is not None:
                 # ... on every rank: nobody pushes into a buffer that is still being read
                 self._rendezvous_on(comm)
+                if self._push_streams is None or self._push_streams[0].device != xq.device:
+                    self._push_streams = [torch.cuda.Stream(xq.device, priority=-1)
+                                          for _ in range(min(4, self.world - 1))]
         for b in range(blocks):
             mine = staging[b, self.rank]
             # (a single block may have any number of rows: it takes the whole, padded scale tensor)
@@ -231,17 +235,26 @@ class ColumnParallelDenseGemm:
                 continue
             done = torch.cuda.Event()
             done.record(cur)
-            comm.wait_event(done)
-            with torch.cuda.stream(comm):
-                if peers is None:
+            if peers is None:
+                comm.wait_event(done)
+                with torch.cuda.stream(comm):
                     # in place: rank r's input is block r of the output
                     self._dist.all_gather_into_tensor(flat, mine, group=self.group)
-                else:
-                    # at any moment every rank pushes to a different peer
-                    for i in range(1, self.world):
+            if peers is not None:
+                # Pushes to different peers go out on several streams, so that several copy engines
+                # work at once (one stream of 29 MB copies reached 465 GB/s on 8 GPUs); at any
+                # moment every rank pushes to different peers than the others.
+                for i in range(1, self.world):
+                    side = self._push_streams[(i - 1) % len(self._push_streams)]
+                    side.wait_event(done)
+                    if b == 0:
+                        side.wait_stream(comm)  # behind the rendezvous that opens the peers' buffers
+                    with torch.cuda.stream(side):
                         peers[(self.rank + i) % self.world][b, self.rank].copy_(mine, non_blocking=True)
         if comm is not None:
             if peers is not None:
+                for side in self._push_streams:
+                    comm.wait_stream(side)
                 # once every rank is past this point, every push has landed
                 self._rendezvous_on(comm)
             cur.wait_stream(comm)
