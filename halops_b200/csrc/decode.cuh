@@ -74,6 +74,8 @@ struct DecPlan {
     int ctas;
     int aligned;
     int fits32;   // units * ctas < 2^32: the device may deal in 32-bit arithmetic
+    int cluster;  // > 1: the CTAs of one tile form a thread-block cluster of this size and exchange
+                  // their partial tiles through shared memory instead of the scratch buffer
 };
 
 __host__ __device__ inline int64_t dec_begin(const DecPlan& p, int c) {
@@ -158,6 +160,25 @@ __device__ __forceinline__ bool epi_rendezvous(Barriers* bars, uint32_t& phase, 
     return ok;
 }
 
+// Bounded wait on a barrier that CTAs of the cluster arrive on with release semantics: acquires
+// what they wrote into this CTA's shared memory before arriving.
+__device__ __forceinline__ bool wait_bar_cluster(uint32_t bar, uint32_t parity, volatile uint32_t* abort, uint32_t code) {
+    if (ptx::mbar_try_wait_cluster(bar, parity)) return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    while (!ptx::mbar_try_wait_cluster(bar, parity)) {
+        if ((++spins & 31u) == 0u) {
+            if (*abort != 0u) return false;
+            if (ptx::globaltimer_ns() - t0 > kTimeoutNs) {
+                *abort = 1u;
+                atomicOr(&g_status[0], code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
 // bf16(y) or bf16(sigmoid(y)) in the reference's formulation (see epilogue_chunk), as 16 bits
 __device__ __forceinline__ uint16_t dec_finish(float y, int epi_op) {
     if (epi_op == HQ_EPILOGUE_SIGMOID) y = fmaf(0.5f, tanh_fast(0.5f * y), 0.5f);
@@ -223,6 +244,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
         for (int s = 0; s < C::kSfSets; ++s) ptx::mbar_init(ptx::smem_u32(&bars->sf_ready[s]), 1);
         ptx::mbar_init(ptx::smem_u32(&bars->epi_sync), kEpiWarps);
+        if (p.plan.cluster > 1) {
+            ptx::mbar_init(ptx::smem_u32(&bars->turn[0]), 1);  // "the first CTA's ring is free"
+            ptx::mbar_init(ptx::smem_u32(&bars->recv_full), uint32_t(p.plan.cluster - 1) * kEpiWarps);
+        }
         bars->abort = 0;
         ptx::fence_mbar_init();
     }
@@ -232,6 +257,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     }
     ptx::tc_fence_before();
     __syncthreads();
+    // the other CTAs' barriers exist before anyone signals across the cluster
+    if (p.plan.cluster > 1) ptx::cluster_sync();
     ptx::tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
 
@@ -378,6 +405,72 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             const uint32_t acc = tmem + as * kDecIssuers * NACT + (lane_base << 16);
             const bool two = sg.k1 - sg.k0 > 1;  // the second issuer had steps of this piece
             const int col0 = sg.tile * kDecRows + int(lane_base);  // first output column of this warp
+            if (sg.partial && p.plan.cluster > 1) {
+                // ---- the tile's CTAs are one cluster: partial tiles go into the first CTA's shared
+                // memory (its operand ring, idle once its MMAs have completed), which adds them in
+                // rank order, i.e. in K order, and stores the result
+                const uint32_t crank = ptx::cluster_ctarank();
+                const uint32_t ring_ok = ptx::smem_u32(&bars->turn[0]);
+                const uint32_t recv_full = ptx::smem_u32(&bars->recv_full);
+                constexpr uint32_t kPartBytes = NACT * kDecRows * 4;
+                if (crank != 0) {
+                    ok = wait_bar_cluster(ring_ok, 0, abort, kStatusEpilogue);
+                    if (!ok) break;
+                    const uint32_t dst = ptx::mapa_cluster(w_base, 0) + (crank - 1) * kPartBytes + uint32_t(row) * 4;
+#pragma unroll 1
+                    for (int ci = 0; ci < m_chunks; ++ci) {
+                        uint32_t r0[16], r1[16];
+                        tc_load_32x16(acc + ci * 16, r0);
+                        if (two) tc_load_32x16(acc + NACT + ci * 16, r1);
+                        ptx::tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float v = two ? __uint_as_float(r0[j]) + __uint_as_float(r1[j]) : __uint_as_float(r0[j]);
+                            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst + (ci * 16 + j) * (kDecRows * 4)), "f"(v)
+                                         : "memory");
+                        }
+                    }
+                    ptx::tc_fence_before();
+                    // every lane's stores are ordered before the warp's one remote arrival
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[as]));
+                        ptx::mbar_arrive_cluster_addr(ptx::mapa_cluster(recv_full, 0));
+                    }
+                } else {
+                    // acc_full has completed: this CTA's MMAs no longer read the ring
+                    if (tid == 0) {
+                        for (int r = 1; r < p.plan.cluster; ++r) ptx::mbar_arrive_cluster_addr(ptx::mapa_cluster(ring_ok, uint32_t(r)));
+                    }
+                    ok = wait_bar_cluster(recv_full, 0, abort, kStatusEpilogue);
+                    if (!ok) break;
+#pragma unroll 1
+                    for (int ci = 0; ci < m_chunks; ++ci) {
+                        uint32_t r0[16], r1[16];
+                        tc_load_32x16(acc + ci * 16, r0);
+                        if (two) tc_load_32x16(acc + NACT + ci * 16, r1);
+                        ptx::tc_wait_ld();
+                        float v[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = two ? __uint_as_float(r0[j]) + __uint_as_float(r1[j]) : __uint_as_float(r0[j]);
+                        for (int r = 1; r < p.plan.cluster; ++r) {
+                            const uint32_t src = w_base + uint32_t(r - 1) * kPartBytes + uint32_t(row) * 4 + ci * 16 * (kDecRows * 4);
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                float x;
+                                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x) : "r"(src + j * (kDecRows * 4)));
+                                v[j] += x;
+                            }
+                        }
+                        dec_store_box(&tm_o, my_bufs + (stores & 1u) * kDecEpiBufBytes, lane, v, p.epi_op, col0, ci * 16);
+                        ++stores;
+                    }
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[as]));
+                }
+                continue;
+            }
             float* const mine = !sg.partial ? nullptr
                                 : p.scratch + int64_t(dec_slot(p.plan, cta, sg.tile)) * (NACT * kDecRows) + row;
 #pragma unroll 1
@@ -458,6 +551,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     }
     ptx::tc_fence_before();
     __syncthreads();
+    // no CTA of a cluster leaves while another may still write into its shared memory or
+    // arrive on its barriers (every wait above is bounded, so all of them get here)
+    if (p.plan.cluster > 1) ptx::cluster_sync();
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc<1>(tmem, C::kTmemCols);
@@ -518,26 +614,40 @@ inline bool dec_scratch(int dev, cudaStream_t stream, DecScratch* out) {
 // memory round trip (measured: one 32 KB step per 0.42 us), while the float32 exchange of
 // partial tiles at the end of a split run costs about 3.3 us plus 1 us per 64 activation
 // columns.  A split deals every tile to `s` CTAs (s a power of two with tiles * s <= SMs).
-inline DecPlan dec_plan(int n, int64_t k_bytes, int sm_count, bool allow_split, int nact, bool force_split) {
+inline DecPlan dec_plan(int n, int64_t k_bytes, int sm_count, bool allow_split, int nact, bool force_split,
+                        int64_t ring_bytes, bool allow_cluster) {
     DecPlan p;
     p.tiles = (n + kDecRows - 1) / kDecRows;
     p.ksteps = int((k_bytes + kDecStepBytes - 1) / kDecStepBytes);
     p.fits32 = 0;
+    p.cluster = 0;
     const int whole_ctas = p.tiles < sm_count ? p.tiles : sm_count;
     p.ctas = whole_ctas;
     p.aligned = 1;
     int s = 1;
     while (p.tiles * s * 2 <= sm_count && s * 2 <= p.ksteps) s *= 2;
     if (!allow_split || s == 1 || p.tiles > kDecCounterSlots || p.tiles * s > 160) return p;
+    // A cluster (at most 8 CTAs, the portable maximum) exchanges the partial tiles through the
+    // first CTA's shared memory, if they fit into its operand ring: about 1 us instead of 3.3.
+    int sc = s > 8 ? 8 : s;
+    while (sc > 1 && int64_t(sc - 1) * nact * kDecRows * 4 > ring_bytes) sc /= 2;
     const double step_us = 0.42, hbm_bytes_per_us = 6.0e6;
     const double bytes = double(p.tiles) * kDecRows * double(k_bytes);
+    const double hbm_us = bytes / hbm_bytes_per_us;
     const double whole_us = double((p.tiles + whole_ctas - 1) / whole_ctas) * p.ksteps * step_us;
-    const double split_steps = double((p.ksteps + s - 1) / s);
-    const double stream_us = bytes / hbm_bytes_per_us > split_steps * step_us ? bytes / hbm_bytes_per_us : split_steps * step_us;
-    const double split_us = stream_us + 3.3 + double(nact) / 64.0;
-    if (force_split || split_us < (bytes / hbm_bytes_per_us > whole_us ? bytes / hbm_bytes_per_us : whole_us)) {
-        p.ctas = p.tiles * s;
+    const auto split_us = [&](int parts, double exchange_us) {
+        const double steps_us = double((p.ksteps + parts - 1) / parts) * step_us;
+        return (hbm_us > steps_us ? hbm_us : steps_us) + exchange_us;
+    };
+    const double global_us = split_us(s, 3.3 + double(nact) / 64.0);
+    const double cluster_us = allow_cluster && sc > 1 ? split_us(sc, 1.0 + double(nact) / 256.0) : 1e30;
+    const double base_us = hbm_us > whole_us ? hbm_us : whole_us;
+    const bool cluster = cluster_us <= global_us;
+    if (force_split || (cluster ? cluster_us : global_us) < base_us) {
+        const int parts = cluster ? sc : s;
+        p.ctas = p.tiles * parts;
         p.aligned = 0;
+        p.cluster = cluster ? parts : 0;
         p.fits32 = int64_t(p.tiles) * p.ksteps * p.ctas < (int64_t(1) << 32) ? 1 : 0;
     }
     return p;

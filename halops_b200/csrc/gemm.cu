@@ -1886,9 +1886,10 @@ int launch_pair(const GemmArgs& g, char* err, size_t errlen) {
 // Switches of the small-M kernel, for experiments and tests (HALOPS_B200_DECODE, a comma-separated
 // list read on every call): "off" sends small M to the 128 x 64 tile instead, "nosplit" keeps
 // every CTA on whole tiles, "split" deals every tile to several CTAs whatever the estimate says,
-// "wide" also takes 65 to 128 activation rows.
+// "wide" also takes 65 to 128 activation rows, "nocluster" exchanges partial tiles through the
+// global scratch buffer also where a cluster could do it through shared memory.
 struct DecodeSwitches {
-    bool off = false, nosplit = false, split = false, wide = false;
+    bool off = false, nosplit = false, split = false, wide = false, nocluster = false;
 };
 DecodeSwitches decode_switches() {
     DecodeSwitches d;
@@ -1898,6 +1899,7 @@ DecodeSwitches decode_switches() {
     d.nosplit = strstr(e, "nosplit") != nullptr;
     d.split = !d.nosplit && strstr(e, "split") != nullptr;
     d.wide = strstr(e, "wide") != nullptr;
+    d.nocluster = strstr(e, "nocluster") != nullptr;
     return d;
 }
 
@@ -1918,9 +1920,24 @@ bool decode_eligible(int64_t m, int64_t n, int64_t k, int mode, int epi_op, bool
 
 int decode_width(int64_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
 
+// bytes of the operand ring of gemm_decode_kernel<NACT>: where a cluster's partial tiles land
+int64_t decode_ring_bytes(int nact) {
+    switch (nact) {
+        case 16:
+            return int64_t(DecCfg<16>::kStages) * DecCfg<16>::kWBytes;
+        case 32:
+            return int64_t(DecCfg<32>::kStages) * DecCfg<32>::kWBytes;
+        case 64:
+            return int64_t(DecCfg<64>::kStages) * DecCfg<64>::kWBytes;
+        default:
+            return int64_t(DecCfg<128>::kStages) * DecCfg<128>::kWBytes;
+    }
+}
+
 DecPlan decode_plan(int64_t m, int64_t n, int64_t k_bytes, int sm_count) {
     const DecodeSwitches sw = decode_switches();
-    return dec_plan(int(n), k_bytes, sm_count, !sw.nosplit, decode_width(m), sw.split);
+    const int nact = decode_width(m);
+    return dec_plan(int(n), k_bytes, sm_count, !sw.nosplit, nact, sw.split, decode_ring_bytes(nact), !sw.nocluster);
 }
 
 template <int NACT>
@@ -1932,7 +1949,38 @@ int launch_decode(const GemmArgs& g, char* err, size_t errlen) {
     DecParams p;
     p.plan = decode_plan(g.m, g.n, g.k_bytes, g.sm_count);
     DecScratch scratch;
-    if (!p.plan.aligned && !dec_scratch(dev, g.stream, &scratch)) {
+    if (p.plan.cluster > 1) {
+        // a cluster of this size must fit on the device at all (8 CTAs with all of their SM's shared
+        // memory need 8 free SMs of one GPC); asked once per device and size
+        static std::mutex mu;
+        static int8_t fits[64][9];  // 0 unknown, 1 yes, -1 no
+        std::lock_guard<std::mutex> lock(mu);
+        int8_t& f = fits[dev >= 0 && dev < 64 ? dev : 63][p.plan.cluster];
+        if (f == 0 || dev < 0 || dev >= 64) {
+            cudaLaunchConfig_t occ = {};
+            occ.gridDim = dim3(unsigned(p.plan.cluster));
+            occ.blockDim = dim3(kDecThreads);
+            occ.dynamicSmemBytes = size_t(C::kSmemBytes);
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = unsigned(p.plan.cluster);
+            at[0].val.clusterDim.y = 1;
+            at[0].val.clusterDim.z = 1;
+            occ.attrs = at;
+            occ.numAttrs = 1;
+            int n = 0;
+            const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_decode_kernel<NACT>, &occ);
+            if (e != cudaSuccess) cudaGetLastError();
+            f = e == cudaSuccess && n > 0 ? 1 : -1;
+        }
+        if (f < 0) {
+            p.plan.ctas = p.plan.tiles < g.sm_count ? p.plan.tiles : g.sm_count;
+            p.plan.aligned = 1;
+            p.plan.fits32 = 0;
+            p.plan.cluster = 0;
+        }
+    }
+    if (!p.plan.aligned && p.plan.cluster <= 1 && !dec_scratch(dev, g.stream, &scratch)) {
         // no scratch buffer to be had: whole tiles per CTA need none
         p.plan.ctas = p.plan.tiles < g.sm_count ? p.plan.tiles : g.sm_count;
         p.plan.aligned = 1;
@@ -1962,7 +2010,7 @@ int launch_decode(const GemmArgs& g, char* err, size_t errlen) {
     p.x_rows = x_rows;
     p.epi_op = g.epi_op;
     HQ_CUDA_TRY(launch(gemm_decode_kernel<NACT>, dim3(p.plan.ctas), dim3(kDecThreads), size_t(C::kSmemBytes),
-                       g.stream, g.pdl, 1, tm_w, tm_x, tm_o, p));
+                       g.stream, g.pdl, unsigned(p.plan.cluster > 1 ? p.plan.cluster : 1), tm_w, tm_x, tm_o, p));
     return HQ_OK;
 }
 
@@ -2048,7 +2096,7 @@ int launch_decode_noalloc(const GemmArgs& g, const DecPlan& plan, char* err, siz
     p.x_rows = x_rows;
     p.epi_op = g.epi_op;
     HQ_CUDA_TRY(launch(gemm_decode_kernel<NACT>, dim3(plan.ctas), dim3(kDecThreads), size_t(C::kSmemBytes), g.stream,
-                       g.pdl, 1, tm_w, tm_x, tm_o, p));
+                       g.pdl, unsigned(plan.cluster > 1 ? plan.cluster : 1), tm_w, tm_x, tm_o, p));
     return HQ_OK;
 }
 
@@ -2175,9 +2223,9 @@ extern "C" int hq_describe_tile(int64_t m, int64_t n, int64_t k, int mode, int s
         const hq::DecPlan plan = hq::decode_plan(m, n, k, sm > 0 ? sm : 148);
         if (buf != nullptr && buflen > 0) {
             snprintf(buf, buflen,
-                     "[gemm] mode=dense kind=%s m=%lld n=%lld k=%lld sm=%d -> swap 128x%d/256 pair=0 splitk=%d ctas=%d",
+                     "[gemm] mode=dense kind=%s m=%lld n=%lld k=%lld sm=%d -> swap 128x%d/256 pair=0 splitk=%d ctas=%d cluster=%d",
                      hq::mode_name(mode), (long long)m, (long long)n, (long long)k, sm, hq::decode_width(m),
-                     plan.aligned ? 0 : 1, plan.ctas);
+                     plan.aligned ? 0 : 1, plan.ctas, plan.cluster > 1 ? plan.cluster : 1);
         }
         return HQ_OK;
     }
@@ -2883,12 +2931,13 @@ extern "C" int hq_selftest_decode_plan(int64_t n, int64_t k, int sm_count, int f
     if (n < 1 || k < 128 || k % 128 != 0 || sm_count < 1) {
         return hq::fail(err, errlen, HQ_ERR_INVALID, "n >= 1, k a positive multiple of 128 and sm_count >= 1 expected");
     }
-    hq::DecPlan p = hq::dec_plan(int(n), k, sm_count, true, 16, force_split != 0);
+    hq::DecPlan p = hq::dec_plan(int(n), k, sm_count, true, 16, force_split != 0, hq::decode_ring_bytes(16), true);
     if (force_split == 2) {
         // the general even deal: every CTA one contiguous run of units, whatever the tile boundaries
         const int64_t units = int64_t(p.tiles) * p.ksteps;
         p.ctas = int(units < sm_count ? units : sm_count);
         p.aligned = 0;
+        p.cluster = 0;
         p.fits32 = units * p.ctas < (int64_t(1) << 32) ? 1 : 0;
     }
     if (!hq::dec_plan_selfcheck(p)) {

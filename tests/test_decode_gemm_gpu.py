@@ -88,12 +88,12 @@ def test_charted_shapes(hq, monkeypatch, m, n, k, wide):
 @pytest.mark.parametrize("m,n,k", [(1, 64, 128), (5, 192, 384), (17, 4736, 1152), (33, 128, 128), (100, 1024, 1024),
                                    (127, 320, 640), (16, 64, 4096), (9, 2112, 256), (128, 128, 8192)],
                          ids=lambda v: str(v))
-@pytest.mark.parametrize("deal", ["wide", "wide,split", "wide,nosplit"])
+@pytest.mark.parametrize("deal", ["wide", "wide,split", "wide,split,nocluster", "wide,nosplit"])
 def test_ragged_sizes_and_both_deals(hq, monkeypatch, m, n, k, deal):
     """M off the activation widths, N with a last tile of 64 rows, K with a last step of 128
     bytes, one tile, one step; with every tile dealt to several CTAs where there are SMs for
-    that (partial tiles through the scratch buffer), with whole tiles per CTA, and as the
-    dispatch decides.  Rows past M and columns past N
+    that (partial tiles through the first CTA's shared memory in a cluster, or through the
+    scratch buffer), with whole tiles per CTA, and as the dispatch decides.  Rows past M and columns past N
     are never written (the output is a window of a sentinel-filled buffer)."""
     monkeypatch.setenv("HALOPS_B200_DECODE", deal)
     assert "swap" in hq.describe_tile(m, n, k)
@@ -109,12 +109,16 @@ def test_ragged_sizes_and_both_deals(hq, monkeypatch, m, n, k, deal):
 
 @pytest.mark.parametrize("m,n,k", [(8, 7168, 2048), (128, 4096, 2048), (64, 4096, 8192), (16, 640, 1152)],
                          ids=lambda v: str(v))
-def test_deterministic_and_pdl(hq, monkeypatch, m, n, k):
+@pytest.mark.parametrize("exchange", ["cluster", "scratch"])
+def test_deterministic_and_pdl(hq, monkeypatch, m, n, k, exchange):
     """Partial tiles are summed in K order, not in arrival order: 30 runs give the same bits,
-    with and without programmatic launch; the two deals differ only by float32 reassociation."""
+    with and without programmatic launch, whether they are exchanged through shared memory
+    in a cluster or through the scratch buffer; a split and an unsplit run differ only by
+    float32 reassociation."""
     aq, bq, sfa, sfb = _quant(hq, _rand(m, k, 700 + m, "student_t"), _rand(n, k, 800 + m, "weight"))
-    monkeypatch.setenv("HALOPS_B200_DECODE", "wide,split")
-    assert "splitk=1" in hq.describe_tile(m, n, k)
+    monkeypatch.setenv("HALOPS_B200_DECODE", "wide,split" + (",nocluster" if exchange == "scratch" else ""))
+    tile = hq.describe_tile(m, n, k)
+    assert "splitk=1" in tile and ("cluster=1" in tile) == (exchange == "scratch")
     base = _run(hq, aq, bq, sfa, sfb)
     _check(base, aq, bq, sfa, sfb)
     for i in range(30):
@@ -130,7 +134,7 @@ def test_deterministic_and_pdl(hq, monkeypatch, m, n, k):
 def test_back_to_back_launches_share_the_scratch_buffer(hq, monkeypatch):
     """Two different split problems queued on one stream without a synchronisation in between
     use the same scratch buffer and tile counters one after the other."""
-    monkeypatch.setenv("HALOPS_B200_DECODE", "wide,split")
+    monkeypatch.setenv("HALOPS_B200_DECODE", "wide,split,nocluster")
     p1 = _quant(hq, _rand(8, 2048, 1), _rand(7168, 2048, 2, "weight"))
     p2 = _quant(hq, _rand(100, 1536, 3), _rand(4736, 1536, 4, "weight"))
     o1 = torch.empty([8, 7168], dtype=torch.bfloat16, device="cuda")
@@ -145,7 +149,7 @@ def test_back_to_back_launches_share_the_scratch_buffer(hq, monkeypatch):
 
 
 def test_second_stream_gets_its_own_scratch(hq, monkeypatch):
-    monkeypatch.setenv("HALOPS_B200_DECODE", "split")
+    monkeypatch.setenv("HALOPS_B200_DECODE", "split,nocluster")
     p1 = _quant(hq, _rand(16, 2048, 5), _rand(7168, 2048, 6, "weight"))
     want = _run(hq, *p1)
     side = torch.cuda.Stream()

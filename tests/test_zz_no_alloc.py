@@ -46,10 +46,22 @@ def _noalloc(aq, bq, sfa, sfb, out, epilogue=0, sm_count=-1):
                  out.device.index, torch.cuda.current_stream().cuda_stream)
 
 
-@pytest.mark.parametrize("m,n,k,split", [(8, 2048, 4096, True), (32, 4096, 8192, True), (16, 7168, 2048, False),
-                                         (1, 640, 1152, False), (4, 1024, 8320, True), (20, 24576, 1536, False)], ids=lambda v: str(v))
-def test_matches_the_allocating_entry_point_twice_in_a_row(hq, m, n, k, split):
-    assert ("splitk=1" if split else "splitk=0") in hq.describe_tile(m, n, k)
+@pytest.mark.parametrize("m,n,k,deal", [(8, 2048, 4096, "scratch"), (32, 4096, 8192, "scratch"),
+                                        (4, 1024, 8320, "scratch"), (8, 512, 32768, "scratch as dispatched"),
+                                        (8, 2048, 4096, "cluster"), (16, 7168, 2048, "whole tiles"),
+                                        (20, 24576, 1536, "whole tiles")], ids=lambda v: str(v))
+def test_matches_the_allocating_entry_point_twice_in_a_row(hq, monkeypatch, m, n, k, deal):
+    # the cases that deal a tile to several CTAs through the scratch memory are the point of the
+    # entry; the others check that it is the same kernel in every other respect
+    if deal == "scratch":
+        monkeypatch.setenv("HALOPS_B200_DECODE", "nocluster")
+    tile = hq.describe_tile(m, n, k)
+    if deal.startswith("scratch"):
+        assert "splitk=1" in tile and "cluster=1" in tile, tile
+    elif deal == "cluster":
+        assert "splitk=1" in tile and "cluster=1" not in tile, tile
+    else:
+        assert "splitk=0" in tile, tile
     aq, bq, sfa, sfb = _operands(hq, m, n, k, seed=1000 + m)
     want = torch.empty([m, n], dtype=torch.bfloat16, device="cuda")
     hq.dense_gemm(aq, bq, sfa, sfb, want, None, None, -1, "w8a8-mxfp8", False)
