@@ -448,6 +448,7 @@ def run_ours(args):
     gather_ms = gather_alone_ms = gather_nccl_ms = nccl_alone_ms = None
     gather_blocks = 8
     transport = gather_error = None
+    other = {}
     if world > 1:
         def step_gather(kind="auto"):
             hq.group_wise_quant(x, MODE, True, True, xq, sfa)
@@ -455,22 +456,25 @@ def run_ours(args):
 
         reps = max(3, min(steps, 10))
         try:
-            staged = step_gather()
-            transport = ("copy engines into symmetric memory" if layer._symm and layer._symm[1] is not None
-                         else "nccl")
-            gather_ms = timed_ms(step_gather, reps, barrier)
-            staged = step_gather()
+            # both transports are timed; the line's figure is the one `gathered` picks by itself
+            staged = step_gather("copy")
+            have_copy = bool(layer._symm and layer._symm[1] is not None)
+            copy_ms = timed_ms(lambda: step_gather("copy"), reps, barrier)
+            staged = step_gather("copy")
             mine = staged[:, rank].reshape(M5, rows)
             bitwise = bitwise and bool(torch.equal(mine, out))
-            # every peer's block arrived: block b of rank r, sampled rows, against this rank's own
-            # single-GPU GEMM on the whole weight is what `bitwise` checked for this rank's columns;
-            # the transfers alone:
-            gather_alone_ms = timed_ms(lambda: layer.gathered(xq, sfa, blocks=gather_blocks, compute=False), reps,
-                                       barrier)
-            step_gather("nccl")
+            copy_alone_ms = timed_ms(lambda: layer.gathered(xq, sfa, blocks=gather_blocks, transport="copy",
+                                                            compute=False), reps, barrier)
+            staged = step_gather("nccl")
+            bitwise = bitwise and bool(torch.equal(staged[:, rank].reshape(M5, rows), out))
             gather_nccl_ms = timed_ms(lambda: step_gather("nccl"), reps, barrier)
             nccl_alone_ms = timed_ms(lambda: layer.gathered(xq, sfa, blocks=gather_blocks, transport="nccl",
                                                             compute=False), reps, barrier)
+            if have_copy and world <= 4:
+                transport, gather_ms, gather_alone_ms = "copy engines into symmetric memory", copy_ms, copy_alone_ms
+            else:
+                transport, gather_ms, gather_alone_ms = "nccl all-gather per block", gather_nccl_ms, nccl_alone_ms
+            other = {"copy_engines": {"ms_per_step": copy_ms, "transfer_alone_ms": copy_alone_ms}} if have_copy else {}
             assert hq.device_status(dev) == 0
         except Exception as ex:  # the line below still reports the step without the gather
             gather_error = repr(ex)[:300]
@@ -530,15 +534,17 @@ def run_ours(args):
     del x_host, out_host, x_dev, out_dev
 
     # ---- max over ranks
+    copy_pair = other.get("copy_engines", {})
     vals = [total_ms, gemm_ms, quant_ms, sus_ms, e2e_ms, gather_ms or 0.0, gather_alone_ms or 0.0, check_rel,
-            gather_nccl_ms or 0.0, nccl_alone_ms or 0.0]
+            gather_nccl_ms or 0.0, nccl_alone_ms or 0.0, copy_pair.get("ms_per_step", 0.0),
+            copy_pair.get("transfer_alone_ms", 0.0)]
     times = torch.tensor(vals, device=dev, dtype=torch.float64)
     ok = torch.tensor([1 if (bitwise is None or bitwise) else 0], device=dev, dtype=torch.int32)
     if dist is not None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     (total_ms, gemm_ms, quant_ms, sus_ms, e2e_ms, gather_ms, gather_alone_ms, check_rel, gather_nccl_ms,
-     nccl_alone_ms) = times.tolist()
+     nccl_alone_ms, copy_ms_max, copy_alone_max) = times.tolist()
 
     flops = 2.0 * M5 * N5 * K5          # the whole job
     flops_rank = flops / world
@@ -612,6 +618,8 @@ def run_ours(args):
                 "blocks": gather_blocks,
                 "nccl_transport": {"ms_per_step": gather_nccl_ms, "transfer_alone_ms": nccl_alone_ms,
                                    "sms_left_to_nccl": ColumnParallelDenseGemm.default_comm_sms(world)},
+                "copy_engine_transport": ({"ms_per_step": copy_ms_max, "transfer_alone_ms": copy_alone_max}
+                                          if copy_ms_max else None),
                 "how": "GEMM of row block i+1 on the compute stream while block i travels on a second stream; "
                        "with the gather the configuration is bound by NVLink from 4 GPUs on",
             }

@@ -92,7 +92,6 @@ class ColumnParallelDenseGemm:
         self._comm_stream = None
         self._symm = None   # ((shape, device), local staging, [views of every rank's staging])
         self._flag = None
-        self._push_streams = None
 
     def set_alpha(self, alpha: torch.Tensor) -> None:
         """Per-tensor float32 ``[1]`` factor of the NVFP4 recipe."""
@@ -168,14 +167,14 @@ class ColumnParallelDenseGemm:
         split-K kernels add partial sums in another order).  While the GEMM computes block
         ``i + 1`` on the current stream, block ``i`` travels on a second stream:
 
-        * ``transport="copy"`` (what ``"auto"`` picks on GPUs with peer access): the staging
+        * ``transport="copy"`` (what ``"auto"`` picks for up to 4 ranks with peer access): the staging
           buffer lives in symmetric memory and every rank pushes its block into its peers'
           buffers with device-to-device copies, which the copy engines carry over NVLink
           without taking an SM from the GEMM.  Two small NCCL all-reduces fence the pushes: one
           before the first push (every rank is done reading the previous call's result) and one
           after the last (everybody's pushes have landed).
-        * ``transport="nccl"``: ``all_gather_into_tensor`` per block; its kernels need SMs, so
-          the GEMM runs on a grid that leaves ``comm_sms`` SMs free.
+        * ``transport="nccl"`` (``"auto"`` from 8 ranks on): ``all_gather_into_tensor`` per block; its
+          kernels need SMs, so the GEMM runs on a grid that leaves ``comm_sms`` SMs free.
 
         Returns ``[blocks, world, M / blocks, N/w]``: entry ``[b, r]`` holds rows
         ``[b M / blocks, (b + 1) M / blocks)`` of rank ``r``'s columns; ``gathered_as_matrix``
@@ -190,10 +189,14 @@ class ColumnParallelDenseGemm:
         shape = [blocks, self.world, rows, self.n_local]
         on_gpu = xq.is_cuda
         peers = None
-        if on_gpu and self.world > 1 and transport in ("auto", "copy"):
+        # "auto": the copy engines up to 4 ranks; from 8 ranks on NCCL's all-gathers move more bytes
+        # per second than pushes of a block to seven peers in turn (581 against 465 GB/s into a
+        # rank on 8 B200; pushes on several streams at once were slower still)
+        if transport == "auto":
+            transport = "copy" if self.world <= 4 else "nccl"
+        if on_gpu and self.world > 1 and transport == "copy":
             staging, peers = self._symmetric_staging(shape, xq.device)
-            if staging is None and transport == "copy":
-                raise RuntimeError("symmetric memory is not available for the copy transport")
+            # (without peer access or symmetric memory in this build: NCCL it is)
         if peers is None:
             if self._blocks is None or list(self._blocks.shape) != shape or self._blocks.device != xq.device:
                 self._blocks = torch.empty(shape, dtype=torch.bfloat16, device=xq.device)
@@ -217,9 +220,6 @@ class ColumnParallelDenseGemm:
             if peers is not None:
                 # ... on every rank: nobody pushes into a buffer that is still being read
                 self._rendezvous_on(comm)
-                if self._push_streams is None or self._push_streams[0].device != xq.device:
-                    self._push_streams = [torch.cuda.Stream(xq.device, priority=-1)
-                                          for _ in range(min(4, self.world - 1))]
         for b in range(blocks):
             mine = staging[b, self.rank]
             # (a single block may have any number of rows: it takes the whole, padded scale tensor)
@@ -235,26 +235,17 @@ class ColumnParallelDenseGemm:
                 continue
             done = torch.cuda.Event()
             done.record(cur)
-            if peers is None:
-                comm.wait_event(done)
-                with torch.cuda.stream(comm):
+            comm.wait_event(done)
+            with torch.cuda.stream(comm):
+                if peers is None:
                     # in place: rank r's input is block r of the output
                     self._dist.all_gather_into_tensor(flat, mine, group=self.group)
-            if peers is not None:
-                # Pushes to different peers go out on several streams, so that several copy engines
-                # work at once (one stream of 29 MB copies reached 465 GB/s on 8 GPUs); at any
-                # moment every rank pushes to different peers than the others.
-                for i in range(1, self.world):
-                    side = self._push_streams[(i - 1) % len(self._push_streams)]
-                    side.wait_event(done)
-                    if b == 0:
-                        side.wait_stream(comm)  # behind the rendezvous that opens the peers' buffers
-                    with torch.cuda.stream(side):
+                else:
+                    # at any moment every rank pushes to a different peer
+                    for i in range(1, self.world):
                         peers[(self.rank + i) % self.world][b, self.rank].copy_(mine, non_blocking=True)
         if comm is not None:
             if peers is not None:
-                for side in self._push_streams:
-                    comm.wait_stream(side)
                 # once every rank is past this point, every push has landed
                 self._rendezvous_on(comm)
             cur.wait_stream(comm)

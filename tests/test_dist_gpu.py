@@ -52,9 +52,9 @@ def _worker():
         x4q, sfa4 = hq.group_wise_quant(x4, mode=mode)
         want4 = torch.empty([1024, n], dtype=torch.bfloat16, device=dev)
         hq.dense_gemm(x4q, wq, sfa4, sfb, want4, None, alpha, -1, mode)
-        # with both transports: pushes by the copy engines into the peers' symmetric memory
-        # ("auto" on GPUs with peer access) and NCCL all-gathers per block
-        for transport in ("auto", "nccl"):
+        # with both transports: pushes by the copy engines into the peers' symmetric memory and NCCL
+        # all-gathers per block ("auto" picks the first up to 4 ranks, the second from 8 on)
+        for transport in ("copy", "nccl", "auto"):
             for i in range(2):
                 staged = layer.gathered(x4q, sfa4, blocks=4, transport=transport)
                 assert list(staged.shape) == [4, world, 256, rows]
