@@ -610,12 +610,15 @@ inline bool dec_scratch(int dev, cudaStream_t stream, DecScratch* out) {
 }
 
 // Deal of the units.  Whole tiles per CTA unless the weight has so few tiles that the CTAs at
-// work cannot keep HBM busy: a CTA streams at most what its shared memory holds in flight per
-// memory round trip (measured: one 32 KB step per 0.42 us), while the float32 exchange of
-// partial tiles at the end of a split run costs about 3.3 us plus 1 us per 64 activation
-// columns.  A split deals every tile to `s` CTAs (s a power of two with tiles * s <= SMs).
+// work cannot keep HBM busy and the float32 exchange of partial tiles at the end of a split
+// run costs less than it saves.  A split deals every tile to `s` CTAs (s a power of two with
+// tiles * s <= SMs).
+struct DecClusterLimits {
+    int max_active[9];  // clusters of 2, 4, 8 CTAs of this kernel that can be resident at once
+};
+
 inline DecPlan dec_plan(int n, int64_t k_bytes, int sm_count, bool allow_split, int nact, bool force_split,
-                        int64_t ring_bytes, bool allow_cluster) {
+                        int64_t ring_bytes, const DecClusterLimits* clusters) {
     DecPlan p;
     p.tiles = (n + kDecRows - 1) / kDecRows;
     p.ksteps = int((k_bytes + kDecStepBytes - 1) / kDecStepBytes);
@@ -628,9 +631,17 @@ inline DecPlan dec_plan(int n, int64_t k_bytes, int sm_count, bool allow_split, 
     while (p.tiles * s * 2 <= sm_count && s * 2 <= p.ksteps) s *= 2;
     if (!allow_split || s == 1 || p.tiles > kDecCounterSlots || p.tiles * s > 160) return p;
     // A cluster (at most 8 CTAs, the portable maximum) exchanges the partial tiles through the
-    // first CTA's shared memory, if they fit into its operand ring: about 1 us instead of 3.3.
-    int sc = s > 8 ? 8 : s;
-    while (sc > 1 && int64_t(sc - 1) * nact * kDecRows * 4 > ring_bytes) sc /= 2;
+    // first CTA's shared memory, if they fit into its operand ring and all of the tiles' clusters
+    // can be resident at once (a second wave of clusters would wait for the whole first one).
+    int sc = 0;
+    if (clusters != nullptr) {
+        sc = s > 8 ? 8 : s;
+        while (sc > 1 && (int64_t(sc - 1) * nact * kDecRows * 4 > ring_bytes || p.tiles > clusters->max_active[sc])) sc /= 2;
+    }
+    // Measured on B200: a CTA streams one 32 KB step per 0.42 us at most (what its shared memory
+    // holds in flight per memory round trip); the exchange through a cluster costs 2 us plus
+    // 0.3 us per CTA of the cluster, through the scratch buffer 5.5 us (fences, an atomic and
+    // the loads of the last CTA to arrive), both plus the partial tiles' own bytes.
     const double step_us = 0.42, hbm_bytes_per_us = 6.0e6;
     const double bytes = double(p.tiles) * kDecRows * double(k_bytes);
     const double hbm_us = bytes / hbm_bytes_per_us;
@@ -639,11 +650,11 @@ inline DecPlan dec_plan(int n, int64_t k_bytes, int sm_count, bool allow_split, 
         const double steps_us = double((p.ksteps + parts - 1) / parts) * step_us;
         return (hbm_us > steps_us ? hbm_us : steps_us) + exchange_us;
     };
-    const double global_us = split_us(s, 3.3 + double(nact) / 64.0);
-    const double cluster_us = allow_cluster && sc > 1 ? split_us(sc, 1.0 + double(nact) / 256.0) : 1e30;
+    const double global_us = split_us(s, 5.5 + double(nact) / 64.0);
+    const double cluster_us = sc > 1 ? split_us(sc, 2.0 + 0.3 * sc + double(nact) / 100.0) : 1e30;
     const double base_us = hbm_us > whole_us ? hbm_us : whole_us;
     const bool cluster = cluster_us <= global_us;
-    if (force_split || (cluster ? cluster_us : global_us) < base_us) {
+    if (force_split || (cluster ? cluster_us : global_us) < 0.85 * base_us) {
         const int parts = cluster ? sc : s;
         p.ctas = p.tiles * parts;
         p.aligned = 0;

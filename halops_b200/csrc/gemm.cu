@@ -1934,10 +1934,70 @@ int64_t decode_ring_bytes(int nact) {
     }
 }
 
+// How many clusters of 2, 4 and 8 CTAs of gemm_decode_kernel<NACT> the current device can hold at
+// once; asked once per device and width.  Without a device (shape queries on a machine without
+// a GPU) the figures of a B200 stand in: 74, 36 and 14.
+template <int NACT>
+void decode_cluster_query(DecClusterLimits* out) {
+    for (int sc = 2; sc <= 8; sc *= 2) {
+        cudaLaunchConfig_t occ = {};
+        occ.gridDim = dim3(unsigned(sc));
+        occ.blockDim = dim3(kDecThreads);
+        occ.dynamicSmemBytes = size_t(DecCfg<NACT>::kSmemBytes);
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = unsigned(sc);
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        occ.attrs = at;
+        occ.numAttrs = 1;
+        int n = 0;
+        if (cudaFuncSetAttribute(gemm_decode_kernel<NACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 DecCfg<NACT>::kSmemBytes) != cudaSuccess ||
+            cudaOccupancyMaxActiveClusters(&n, gemm_decode_kernel<NACT>, &occ) != cudaSuccess) {
+            cudaGetLastError();
+            n = sc == 2 ? 74 : sc == 4 ? 36 : 14;
+        }
+        out->max_active[sc] = n;
+    }
+}
+
+const DecClusterLimits* decode_cluster_limits(int nact) {
+    static std::mutex mu;
+    static DecClusterLimits limits[64][4];
+    static bool known[64][4];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        dev = 63;
+    }
+    const int slot = dev >= 0 && dev < 64 ? dev : 63;
+    const int w = nact == 16 ? 0 : nact == 32 ? 1 : nact == 64 ? 2 : 3;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!known[slot][w]) {
+        switch (nact) {
+            case 16:
+                decode_cluster_query<16>(&limits[slot][w]);
+                break;
+            case 32:
+                decode_cluster_query<32>(&limits[slot][w]);
+                break;
+            case 64:
+                decode_cluster_query<64>(&limits[slot][w]);
+                break;
+            default:
+                decode_cluster_query<128>(&limits[slot][w]);
+        }
+        known[slot][w] = true;
+    }
+    return &limits[slot][w];
+}
+
 DecPlan decode_plan(int64_t m, int64_t n, int64_t k_bytes, int sm_count) {
     const DecodeSwitches sw = decode_switches();
     const int nact = decode_width(m);
-    return dec_plan(int(n), k_bytes, sm_count, !sw.nosplit, nact, sw.split, decode_ring_bytes(nact), !sw.nocluster);
+    return dec_plan(int(n), k_bytes, sm_count, !sw.nosplit, nact, sw.split, decode_ring_bytes(nact),
+                    sw.nocluster ? nullptr : decode_cluster_limits(nact));
 }
 
 template <int NACT>
@@ -1949,37 +2009,6 @@ int launch_decode(const GemmArgs& g, char* err, size_t errlen) {
     DecParams p;
     p.plan = decode_plan(g.m, g.n, g.k_bytes, g.sm_count);
     DecScratch scratch;
-    if (p.plan.cluster > 1) {
-        // a cluster of this size must fit on the device at all (8 CTAs with all of their SM's shared
-        // memory need 8 free SMs of one GPC); asked once per device and size
-        static std::mutex mu;
-        static int8_t fits[64][9];  // 0 unknown, 1 yes, -1 no
-        std::lock_guard<std::mutex> lock(mu);
-        int8_t& f = fits[dev >= 0 && dev < 64 ? dev : 63][p.plan.cluster];
-        if (f == 0 || dev < 0 || dev >= 64) {
-            cudaLaunchConfig_t occ = {};
-            occ.gridDim = dim3(unsigned(p.plan.cluster));
-            occ.blockDim = dim3(kDecThreads);
-            occ.dynamicSmemBytes = size_t(C::kSmemBytes);
-            cudaLaunchAttribute at[1];
-            at[0].id = cudaLaunchAttributeClusterDimension;
-            at[0].val.clusterDim.x = unsigned(p.plan.cluster);
-            at[0].val.clusterDim.y = 1;
-            at[0].val.clusterDim.z = 1;
-            occ.attrs = at;
-            occ.numAttrs = 1;
-            int n = 0;
-            const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_decode_kernel<NACT>, &occ);
-            if (e != cudaSuccess) cudaGetLastError();
-            f = e == cudaSuccess && n > 0 ? 1 : -1;
-        }
-        if (f < 0) {
-            p.plan.ctas = p.plan.tiles < g.sm_count ? p.plan.tiles : g.sm_count;
-            p.plan.aligned = 1;
-            p.plan.fits32 = 0;
-            p.plan.cluster = 0;
-        }
-    }
     if (!p.plan.aligned && p.plan.cluster <= 1 && !dec_scratch(dev, g.stream, &scratch)) {
         // no scratch buffer to be had: whole tiles per CTA need none
         p.plan.ctas = p.plan.tiles < g.sm_count ? p.plan.tiles : g.sm_count;
@@ -2931,7 +2960,11 @@ extern "C" int hq_selftest_decode_plan(int64_t n, int64_t k, int sm_count, int f
     if (n < 1 || k < 128 || k % 128 != 0 || sm_count < 1) {
         return hq::fail(err, errlen, HQ_ERR_INVALID, "n >= 1, k a positive multiple of 128 and sm_count >= 1 expected");
     }
-    hq::DecPlan p = hq::dec_plan(int(n), k, sm_count, true, 16, force_split != 0, hq::decode_ring_bytes(16), true);
+    hq::DecClusterLimits nominal = {};
+    nominal.max_active[2] = 74;
+    nominal.max_active[4] = 36;
+    nominal.max_active[8] = 14;
+    hq::DecPlan p = hq::dec_plan(int(n), k, sm_count, true, 16, force_split != 0, hq::decode_ring_bytes(16), &nominal);
     if (force_split == 2) {
         // the general even deal: every CTA one contiguous run of units, whatever the tile boundaries
         const int64_t units = int64_t(p.tiles) * p.ksteps;

@@ -54,7 +54,7 @@ def test_matches_the_allocating_entry_point_twice_in_a_row(hq, monkeypatch, m, n
     # the cases that deal a tile to several CTAs through the scratch memory are the point of the
     # entry; the others check that it is the same kernel in every other respect
     if deal == "scratch":
-        monkeypatch.setenv("HALOPS_B200_DECODE", "nocluster")
+        monkeypatch.setenv("HALOPS_B200_DECODE", "split,nocluster")
     tile = hq.describe_tile(m, n, k)
     if deal.startswith("scratch"):
         assert "splitk=1" in tile and "cluster=1" in tile, tile
