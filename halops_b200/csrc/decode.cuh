@@ -209,9 +209,11 @@ __global__ void __launch_bounds__(kDecThreads, 1)
 gemm_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                    const __grid_constant__ CUtensorMap tm_o, const DecParams p) {
     using C = DecCfg<NACT>;
-    // the descriptors come from global memory: ask for them before anything else
-    if (threadIdx.x == 0) {
-        ptx::prefetch_tmap(&tm_w);
+    // the descriptors come from global memory: ask for them before anything else (each request
+    // holds its thread for a few hundred cycles, so the loader's thread asks only for the one it
+    // needs first)
+    if (threadIdx.x == 0) ptx::prefetch_tmap(&tm_w);
+    if (threadIdx.x == 64) {
         ptx::prefetch_tmap(&tm_x);
         ptx::prefetch_tmap(&tm_o);
     }

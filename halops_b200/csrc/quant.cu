@@ -93,6 +93,34 @@ __device__ __forceinline__ float2 mul2(float a, float b, float s) {
         : "f"(a), "f"(b), "f"(s));
     return r;
 }
+// (a * c, b * d) as one packed instruction
+__device__ __forceinline__ float2 mul2v(float2 v, float2 w) {
+    float2 r;
+    asm("{\n\t"
+        ".reg .b64 t, u;\n\t"
+        "mov.b64 t, {%2, %3};\n\t"
+        "mov.b64 u, {%4, %5};\n\t"
+        "mul.rn.f32x2 t, t, u;\n\t"
+        "mov.b64 {%0, %1}, t;\n\t"
+        "}"
+        : "=f"(r.x), "=f"(r.y)
+        : "f"(v.x), "f"(v.y), "f"(w.x), "f"(w.y));
+    return r;
+}
+// (a * a + c, b * b + d) as one packed instruction
+__device__ __forceinline__ float2 fma2_sq(float2 v, float2 acc) {
+    float2 r;
+    asm("{\n\t"
+        ".reg .b64 t, u;\n\t"
+        "mov.b64 t, {%2, %3};\n\t"
+        "mov.b64 u, {%4, %5};\n\t"
+        "fma.rn.f32x2 u, t, t, u;\n\t"
+        "mov.b64 {%0, %1}, u;\n\t"
+        "}"
+        : "=f"(r.x), "=f"(r.y)
+        : "f"(v.x), "f"(v.y), "f"(acc.x), "f"(acc.y));
+    return r;
+}
 // -0.0 -> +0.0, everything else unchanged.  (Written as two scalar adds: the
 // packed add.rn.f32x2 with a zero operand does not survive ptxas.)
 __device__ __forceinline__ float2 add_zero2(float2 v) {
@@ -428,22 +456,25 @@ rms_norm_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld,
     }
 
     uint4 raw[kPieces];
-    float sum_sq = 0.0f;
 #pragma unroll
     for (int p = 0; p < kPieces; ++p) {
         const int col = (p * threads + t) * 8;
         raw[p] = col < k ? ld_stream(x + row * ld + col) : make_uint4(0, 0, 0, 0);
     }
+    // the row as floats (kept for the second pass) and its sum of squares, two lanes of a
+    // packed accumulator that are added at the end
+    float2 xf[kPieces][4];
+    float2 acc2 = make_float2(0.0f, 0.0f);
 #pragma unroll
     for (int p = 0; p < kPieces; ++p) {
         const uint32_t xw[4] = {raw[p].x, raw[p].y, raw[p].z, raw[p].w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const float a = P::lo(xw[i]), b = P::hi(xw[i]);
-            sum_sq = fmaf(a, a, sum_sq);
-            sum_sq = fmaf(b, b, sum_sq);
+            xf[p][i] = make_float2(P::lo(xw[i]), P::hi(xw[i]));
+            acc2 = fma2_sq(xf[p][i], acc2);
         }
     }
+    float sum_sq = acc2.x + acc2.y;
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) sum_sq += __shfl_xor_sync(0xffffffffu, sum_sq, s);
     const int warps = threads >> 5;
@@ -454,18 +485,19 @@ rms_norm_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld,
         for (int i = 0; i < warps; ++i) sum_sq += warp_sums[i];
     }
     const float rrms = rsqrtf(sum_sq / float(k) + eps);
+    const float2 rrms2 = make_float2(rrms, rrms);
 
 #pragma unroll
     for (int p = 0; p < kPieces; ++p) {
         const int col = (p * threads + t) * 8;
         const bool active = col < k;
-        const uint32_t xw[4] = {raw[p].x, raw[p].y, raw[p].z, raw[p].w};
         const uint32_t gws[4] = {gw[p].x, gw[p].y, gw[p].z, gw[p].w};
         uint32_t yw[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const __nv_bfloat162 y = __float22bfloat162_rn(
-                make_float2(P::lo(xw[i]) * rrms * P::lo(gws[i]), P::hi(xw[i]) * rrms * P::hi(gws[i])));
+            // (x * rrms) * gamma, each product rounded to float32, as two packed multiplies
+            const float2 y2 = mul2v(mul2v(xf[p][i], rrms2), make_float2(P::lo(gws[i]), P::hi(gws[i])));
+            const __nv_bfloat162 y = __float22bfloat162_rn(y2);
             yw[i] = *reinterpret_cast<const uint32_t*>(&y);
         }
         uint32_t codes[4];
