@@ -480,6 +480,25 @@ def run_ours(args):
             gather_error = repr(ex)[:300]
             gather_ms = gather_alone_ms = gather_nccl_ms = nccl_alone_ms = None
 
+    # ---- the same with the all-gather inside the GEMM: its epilogue stores every tile into the
+    # peers' outputs (symmetric memory) as well as into its own
+    fused_ms = fused_error = None
+    if world > 1 and gather_error is None:
+        try:
+            def step_fused():
+                hq.group_wise_quant(x, MODE, True, True, xq, sfa)
+                return layer.gathered_fused(xq, sfa)
+
+            whole = step_fused()
+            staged = step_gather("nccl")
+            bitwise = bitwise and bool(torch.equal(whole, layer.gathered_as_matrix(staged)))
+            fused_ms = timed_ms(step_fused, reps, barrier)
+            assert hq.device_status(dev) == 0
+            del whole, staged
+        except Exception as ex:
+            fused_error = repr(ex)[:300]
+            fused_ms = None
+
     # ---- end to end through the public API with host buffers: every step copies its own
     # activation in from pinned memory and its own result out; consecutive steps overlap on
     # three streams (copy in / kernels / copy out) with two sets of device buffers
@@ -537,14 +556,14 @@ def run_ours(args):
     copy_pair = other.get("copy_engines", {})
     vals = [total_ms, gemm_ms, quant_ms, sus_ms, e2e_ms, gather_ms or 0.0, gather_alone_ms or 0.0, check_rel,
             gather_nccl_ms or 0.0, nccl_alone_ms or 0.0, copy_pair.get("ms_per_step", 0.0),
-            copy_pair.get("transfer_alone_ms", 0.0)]
+            copy_pair.get("transfer_alone_ms", 0.0), fused_ms or 0.0]
     times = torch.tensor(vals, device=dev, dtype=torch.float64)
     ok = torch.tensor([1 if (bitwise is None or bitwise) else 0], device=dev, dtype=torch.int32)
     if dist is not None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     (total_ms, gemm_ms, quant_ms, sus_ms, e2e_ms, gather_ms, gather_alone_ms, check_rel, gather_nccl_ms,
-     nccl_alone_ms, copy_ms_max, copy_alone_max) = times.tolist()
+     nccl_alone_ms, copy_ms_max, copy_alone_max, fused_ms_max) = times.tolist()
 
     flops = 2.0 * M5 * N5 * K5          # the whole job
     flops_rank = flops / world
@@ -620,6 +639,12 @@ def run_ours(args):
                                    "sms_left_to_nccl": ColumnParallelDenseGemm.default_comm_sms(world)},
                 "copy_engine_transport": ({"ms_per_step": copy_ms_max, "transfer_alone_ms": copy_alone_max}
                                           if copy_ms_max else None),
+                "fused_epilogue": ({"ms_per_step": fused_ms_max, "tflops": flops / (fused_ms_max * 1e-3) / 1e12,
+                                    "ratio_to_compute_alone": fused_ms_max / ms_per_step,
+                                    "nvlink_gbs_in_step": gathered_bytes / (fused_ms_max * 1e-3) / 1e9,
+                                    "how": "one kernel: the GEMM's epilogue stores each tile into every peer's "
+                                           "output with 16-byte stores over NVLink"}
+                                   if fused_ms_max else {"error": fused_error}),
                 "how": "GEMM of row block i+1 on the compute stream while block i travels on a second stream; "
                        "with the gather the configuration is bound by NVLink from 4 GPUs on",
             }

@@ -52,6 +52,9 @@ SIGNATURES = {
     "hq_sm_count": (c_int, [c_int]),
     "hq_device_status": (c_int, [c_int, c_void_p, ctypes.POINTER(ctypes.c_uint32), c_char_p, c_size_t]),
     "hq_selftest_bounded_wait": (c_int, [ctypes.c_uint32, c_int, c_void_p, c_char_p, c_size_t]),
+    "hq_dense_gemm_allgather": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_void_p), c_int, c_int,
+                                        c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, c_int, c_int, c_void_p,
+                                        c_char_p, c_size_t]),
     "hq_dense_gemm_small_m_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_i64, c_i64, c_i64,
                                               c_i64, c_i64, c_i64, c_int, c_int, c_int, c_int, c_void_p, c_char_p,
                                               c_size_t]),

@@ -1311,13 +1311,28 @@ __device__ __forceinline__ uint32_t instr_desc_pair(uint32_t sf_id) {
            (uint32_t(256 >> 4) << 24) | (sf_id << 29);
 }
 
-template <int BN, int KIND>
+// Column-parallel all-gather fused into the epilogue (kGather): besides its own output, a rank
+// stores every finished chunk of a tile into the same columns of its peers' outputs (symmetric
+// memory mapped over NVLink): the TMA store that writes the staged chunk to the local output
+// is repeated with a tensor map over each peer's matrix.  Every LOAD of the kernel (operands,
+// scales) is from this GPU's memory.
+template <bool kGather>
+struct GatherMaps {
+    int count;
+};
+template <>
+struct GatherMaps<true> {
+    CUtensorMap out[7];  // the peers' outputs, each map starting at this rank's first column
+    int count;
+};
+
+template <int BN, int KIND, bool kGather = false>
 __global__ void __launch_bounds__((Cfg2<BN, KIND>::kThreads), 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_d, const __grid_constant__ CUtensorMap tm_sfa,
                  const __grid_constant__ CUtensorMap tm_sfb, const float* __restrict__ alpha,
                  const __nv_bfloat16* __restrict__ bias, int epi_op, int k_tiles, int kq_dim, int tiles_m,
-                 int tiles_n) {
+                 int tiles_n, const __grid_constant__ GatherMaps<kGather> peers) {
     using C = Cfg2<BN, KIND>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -1628,6 +1643,38 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 }
                 uint32_t p[16];
                 epilogue_chunk(r, p, scale, bias != nullptr ? bias + n0 + c * kEpiChunk : nullptr, epi_op);
+                if constexpr (kGather) {
+                    // Two neighbouring chunks are staged as ONE box of 32 rows x 128 bytes (the warp's
+                    // two buffers, 128-byte swizzle) and stored together: rows of 128 bytes use
+                    // NVLink better than rows of 64 (measured on 4 GPUs).  Chunks come in ascending
+                    // or descending order, so chunk c's partner c ^ 1 is always the next or the previous one.
+                    const uint32_t buf = epi_base + ew * C::kEpiBufs * kEpiBufBytes;
+                    if ((ci & 1) == 0) {
+                        if (lane == 0) ptx::bulk_wait_read<0>();
+                        __syncwarp();
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t piece = uint32_t((c & 1) * 4 + j);
+                        const uint32_t dst = buf + lane * 128 + ((piece ^ (lane & 7)) << 4);
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(p[4 * j]),
+                                     "r"(p[4 * j + 1]), "r"(p[4 * j + 2]), "r"(p[4 * j + 3])
+                                     : "memory");
+                    }
+                    if ((ci & 1) != 0) {
+                        ptx::fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            const int col = n0 + (c & ~1) * kEpiChunk;
+                            ptx::tma_store_2d(&tm_d, buf, col, m0 + int(lane_base));
+                            for (int q = 0; q < peers.count; ++q) {
+                                ptx::tma_store_2d(&peers.out[q], buf, col, m0 + int(lane_base));
+                            }
+                            ptx::bulk_commit();
+                        }
+                    }
+                    continue;
+                }
                 const uint32_t buf = epi_base + (ew * C::kEpiBufs + (stores % C::kEpiBufs)) * kEpiBufBytes;
                 if (lane == 0) ptx::bulk_wait_read<C::kEpiBufs - 1>();
                 __syncwarp();
@@ -1647,7 +1694,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 ++stores;
             }
         }
-        if (lane == 0) ptx::bulk_wait_read<0>();
+        if constexpr (kGather) {
+            // the stores into the peers' memory have been performed, not only read from shared
+            // memory, before the kernel is seen as complete
+            if (lane == 0) {
+                ptx::bulk_wait<0>();
+                __threadfence_system();
+            }
+        } else {
+            if (lane == 0) ptx::bulk_wait_read<0>();
+        }
     }
 
     if (*abort != 0u) {
@@ -1827,12 +1883,13 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     return HQ_OK;
 }
 
-template <int BN, int KIND>
-int launch_pair(const GemmArgs& g, char* err, size_t errlen) {
+template <int BN, int KIND, bool kGather = false>
+int launch_pair(const GemmArgs& g, char* err, size_t errlen, __nv_bfloat16* const* gather = nullptr,
+                int gather_count = 0) {
     using C = Cfg2<BN, KIND>;
     static SmemOptIn opt_in;
     int dev = 0;
-    HQ_CUDA_TRY(opt_in.ensure(gemm_pair_kernel<BN, KIND>, C::kSmemBytes, &dev));
+    HQ_CUDA_TRY(opt_in.ensure(gemm_pair_kernel<BN, KIND, kGather>, C::kSmemBytes, &dev));
 
     const uint64_t atoms_a = uint64_t((g.m + 127) / 128) * uint64_t(g.kq_dim);
     const uint64_t atoms_b = uint64_t((g.n + 127) / 128) * uint64_t(g.kq_dim);
@@ -1842,8 +1899,10 @@ int launch_pair(const GemmArgs& g, char* err, size_t errlen) {
                      uint64_t(g.k_bytes), kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B) &&
         make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes), uint64_t(g.n),
                      uint64_t(g.k_bytes), kBKBytes, BN / 2, CU_TENSOR_MAP_SWIZZLE_128B) &&
+        // (the gathering kernel stores boxes of two chunks, see its epilogue)
         make_tmap_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out, uint64_t(g.n), uint64_t(g.m),
-                     uint64_t(g.ldo) * 2, kEpiChunk, 32, CU_TENSOR_MAP_SWIZZLE_64B) &&
+                     uint64_t(g.ldo) * 2, kGather ? 2 * kEpiChunk : kEpiChunk, 32,
+                     kGather ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B) &&
         // scale atoms as rows of 128 32-bit words
         make_tmap_2d(&tm_sfa, CU_TENSOR_MAP_DATA_TYPE_UINT32, g.sfa, 128, atoms_a, 512, 128, C::kSfKAtoms,
                      CU_TENSOR_MAP_SWIZZLE_NONE) &&
@@ -1872,14 +1931,24 @@ int launch_pair(const GemmArgs& g, char* err, size_t errlen) {
         occ.attrs = at;
         occ.numAttrs = 1;
         int n = 0;
-        HQ_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<BN, KIND>, &occ));
+        HQ_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<BN, KIND, kGather>, &occ));
         max_clusters[slot] = n > 0 ? n : 1;
     }
     const int clusters = min(min(g.sm_count / 2, max_clusters[slot]), tiles_m * tiles_n);
     const int k_tiles = int(g.k_bytes / kBKBytes);
-    HQ_CUDA_TRY(launch(gemm_pair_kernel<BN, KIND>, dim3(2 * clusters), dim3(C::kThreads), size_t(C::kSmemBytes),
+    GatherMaps<kGather> peers{};
+    if constexpr (kGather) {
+        for (int q = 0; q < gather_count; ++q) {
+            if (!make_tmap_2d(&peers.out[q], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, gather[q], uint64_t(g.n), uint64_t(g.m),
+                              uint64_t(g.ldo) * 2, 2 * kEpiChunk, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
+                return fail(err, errlen, HQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the output of a peer");
+            }
+        }
+        peers.count = gather_count;
+    }
+    HQ_CUDA_TRY(launch(gemm_pair_kernel<BN, KIND, kGather>, dim3(2 * clusters), dim3(C::kThreads), size_t(C::kSmemBytes),
                        g.stream, g.pdl, 2, tm_a, tm_b, tm_d, tm_sfa, tm_sfb, g.alpha, g.bias, g.epi_op, k_tiles, g.kq_dim, tiles_m,
-                       tiles_n));
+                       tiles_n, peers));
     return HQ_OK;
 }
 
@@ -2876,6 +2945,74 @@ extern "C" int hq_selftest_bounded_wait(uint32_t limit_us, int device, void* str
     HQ_CUDA_TRY(hq::launch(hq::wait_selftest_kernel, dim3(1), dim3(64), size_t(0), static_cast<cudaStream_t>(stream),
                            false, 1, uint64_t(limit_us) * 1000ull));
     return HQ_OK;
+}
+
+extern "C" int hq_dense_gemm_allgather(const void* a, const void* b, const void* sfa, const void* sfb,
+                                       void* const* outs, int world, int rank, int64_t m, int64_t n_local, int64_t k,
+                                       int64_t sfa_bytes, int64_t sfb_bytes, int64_t ldo, int sm_count, int use_pdl,
+                                       int device, void* stream, char* err, size_t errlen) {
+    using hq::fail;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || outs == nullptr) {
+        return fail(err, errlen, HQ_ERR_INVALID, "world must be 1..8 with 0 <= rank < world and one output per rank, got "
+                                                 "world=%d rank=%d", world, rank);
+    }
+    if (m < 1 || n_local < 1 || k < 1 || m > INT32_MAX || n_local * world > INT32_MAX || k > INT32_MAX) {
+        return fail(err, errlen, HQ_ERR_INVALID, "input must be a 2D tensor of shape [M, K]");
+    }
+    if (n_local % 256 != 0 || k % 128 != 0 || m <= 128) {
+        return fail(err, errlen, HQ_ERR_UNSUPPORTED,
+                    "the fused all-gather runs on the 256x256 2-CTA tile: N per rank must be a multiple of 256, K of "
+                    "128 and M > 128, got M=%lld N=%lld K=%lld", (long long)m, (long long)n_local, (long long)k);
+    }
+    const int64_t sf_k = k / 32;
+    if (sfa_bytes < hq_sf_rows(m) * sf_k || sfb_bytes < hq_sf_rows(n_local) * sf_k) {
+        return fail(err, errlen, HQ_ERR_INVALID, "sfa / sfb must hold whole 128-row SfAtoms");
+    }
+    if (ldo < n_local * world || ldo % 8 != 0) {
+        return fail(err, errlen, HQ_ERR_INVALID, "the outputs are [M, world * N] matrices: row stride %lld is too small "
+                                                 "or not a multiple of 8", (long long)ldo);
+    }
+    for (int r = 0; r < world; ++r) {
+        if (outs[r] == nullptr || !hq::aligned(outs[r], 16)) {
+            return fail(err, errlen, HQ_ERR_INVALID, "output %d is null or not 16-byte aligned", r);
+        }
+    }
+    if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || !hq::aligned(a, 16) || !hq::aligned(b, 16) ||
+        !hq::aligned(sfa, 16) || !hq::aligned(sfb, 16)) {
+        return fail(err, errlen, HQ_ERR_INVALID, "operands and scales must be non-null and 16-byte aligned");
+    }
+    const hq::DeviceGuard guard(device);
+    if (!guard.ok()) return fail(err, errlen, HQ_ERR_CUDA, "cannot select CUDA device %d", device);
+    const int sm_all = hq_sm_count(device);
+    const int sm = sm_count > 0 ? (sm_count < sm_all || sm_all == 0 ? sm_count : sm_all) : sm_all;
+    if (sm <= 0) return fail(err, errlen, HQ_ERR_CUDA, "cannot query the SM count of device %d", device);
+    hq::GemmArgs g;
+    g.a = a;
+    g.b = b;
+    g.sfa = static_cast<const uint8_t*>(sfa);
+    g.sfb = static_cast<const uint8_t*>(sfb);
+    g.alpha = nullptr;
+    g.bias = nullptr;
+    g.epi_op = HQ_EPILOGUE_IDENTITY;
+    g.situ = hq::SituParams{};
+    // this rank's own copy: columns [rank * n_local, (rank + 1) * n_local) of its [M, ldo] output
+    g.out = static_cast<__nv_bfloat16*>(outs[rank]) + int64_t(rank) * n_local;
+    g.ldo = ldo;
+    g.m = int(m);
+    g.n = int(n_local);
+    g.grp = hq::GroupParams{hq::kGroupDense, 1, 0, nullptr};
+    g.k_bytes = k;
+    g.kq_dim = int(sf_k / 4);
+    g.sm_count = sm;
+    g.pdl = use_pdl != 0;
+    g.direct_store = false;
+    g.stream = static_cast<cudaStream_t>(stream);
+    __nv_bfloat16* peers[8];
+    int count = 0;
+    for (int r = 0; r < world; ++r) {
+        if (r != rank) peers[count++] = static_cast<__nv_bfloat16*>(outs[r]) + int64_t(rank) * n_local;
+    }
+    return hq::launch_pair<256, 0, true>(g, err, errlen, peers, count);
 }
 
 extern "C" int hq_dense_gemm_small_m_noalloc(const void* a, const void* b, const void* sfa, const void* sfb, void* out,

@@ -92,6 +92,7 @@ class ColumnParallelDenseGemm:
         self._comm_stream = None
         self._symm = None   # ((shape, device), local staging, [views of every rank's staging])
         self._flag = None
+        self._symm_matrix = None   # ((M, device), local [M, N], every rank's view, their addresses)
 
     def set_alpha(self, alpha: torch.Tensor) -> None:
         """Per-tensor float32 ``[1]`` factor of the NVFP4 recipe."""
@@ -250,6 +251,63 @@ class ColumnParallelDenseGemm:
                 self._rendezvous_on(comm)
             cur.wait_stream(comm)
         return staging
+
+    # ------------------------------------------------------------------ all-gather inside the GEMM
+
+    def fused_supported(self, m: int) -> bool:
+        """Whether ``gathered_fused`` can run: MXFP8 on the 2-CTA 256 x 256 tile, at most 8 ranks."""
+        return (self.mode == "w8a8-mxfp8" and self.alpha is None and self.n_local % 256 == 0 and m > 128
+                and 1 <= self.world <= 8)
+
+    def _symmetric_matrix(self, m: int, device):
+        """The ``[M, N]`` output of ``gathered_fused`` in symmetric memory, with the device
+        addresses of every rank's copy as this process sees them.  Collective."""
+        key = (m, device)
+        if self._symm_matrix is not None and self._symm_matrix[0] == key:
+            return self._symm_matrix[1:]
+        import ctypes
+
+        shape = [m, self.world * self.n_local]
+        if self.world == 1:
+            local = torch.empty(shape, dtype=torch.bfloat16, device=device)
+            views = [local]
+        else:
+            import torch.distributed._symmetric_memory as symm
+
+            group = self.group if self.group is not None else self._dist.group.WORLD
+            local = symm.empty(shape, dtype=torch.bfloat16, device=device)
+            handle = symm.rendezvous(local, group)
+            views = [handle.get_buffer(r, shape, torch.bfloat16) for r in range(self.world)]
+            if self._flag is None:
+                self._flag = torch.zeros([1], dtype=torch.int32, device=device)
+        addresses = (ctypes.c_void_p * self.world)(*[v.data_ptr() for v in views])
+        self._symm_matrix = (key, local, views, addresses)
+        return local, views, addresses
+
+    def gathered_fused(self, xq: torch.Tensor, sfa: torch.Tensor, sm_count: int = -1) -> torch.Tensor:
+        """GEMM and all-gather in ONE kernel.  Every rank holds an ``[M, N]`` output in symmetric
+        memory; the GEMM's epilogue stores each finished tile into this rank's columns of its own
+        output (TMA stores) and, from the same registers, into the same columns of every peer's
+        output with plain 16-byte stores over NVLink, so the transfer of a tile runs while the
+        tensor cores work on the next one and no copy or collective kernel follows.  All loads
+        (operands, scales) are from this GPU's memory.  Two one-element NCCL all-reduces fence
+        the call on the current stream: before the kernel (no rank still reads the previous
+        result) and after it (every rank's stores are complete).  Returns this rank's ``[M, N]``
+        matrix, valid on the current stream; the next call overwrites it.  Collective."""
+        m, k = xq.shape
+        if not self.fused_supported(m):
+            raise RuntimeError("gathered_fused needs the MXFP8 recipe, a shard with a multiple of 256 rows, more "
+                               "than 128 activation rows and at most 8 ranks")
+        local, _views, addresses = self._symmetric_matrix(m, xq.device)
+        stream = torch.cuda.current_stream(xq.device)
+        if self.world > 1:
+            self._dist.all_reduce(self._flag, group=self.group)
+        _native.call("hq_dense_gemm_allgather", xq.data_ptr(), self.wq.data_ptr(), sfa.data_ptr(), self.sfb.data_ptr(),
+                     addresses, self.world, self.rank, m, self.n_local, k, sfa.numel(), self.sfb.numel(),
+                     local.stride(0), sm_count, 0, xq.device.index, stream.cuda_stream)
+        if self.world > 1:
+            self._dist.all_reduce(self._flag, group=self.group)
+        return local
 
     @staticmethod
     def gathered_as_matrix(staging: torch.Tensor) -> torch.Tensor:

@@ -306,6 +306,33 @@ int hq_selftest_bounded_wait(uint32_t limit_us, int device, void* stream,
                              char* err, size_t errlen);
 
 /*
+ * Column-parallel MXFP8 dense GEMM with the all-gather of the output fused into
+ * its epilogue.  The reference has no multi-GPU dense GEMM (its tensor-parallel
+ * tests combine single-GPU calls with framework collectives,
+ * tests/test_fused_all_reduce_mhc.py:181-218); this is the N-sharded mode of the
+ * benchmark's largest configuration in one kernel.
+ *   a, sfa          the replicated activation [m, k] e4m3 and its SfAtom scales
+ *   b, sfb          this rank's weight shard [n_local, k] and its scales
+ *   outs[world]     one [m, ldo] bf16 matrix per rank, ldo >= world * n_local;
+ *                   outs[rank] lives on this device, the others are the peers'
+ *                   matrices mapped into this process (symmetric memory)
+ * The kernel (2-CTA 256 x 256 tile) writes columns [rank * n_local, (rank + 1) *
+ * n_local) of EVERY matrix: its own through TMA stores, the peers' with plain
+ * 16-byte global stores over NVLink from the same registers, tile by tile, so
+ * the transfer overlaps the math.  Tensor maps and all loads cover this GPU's
+ * memory only.  The caller fences across ranks: nobody may still read a matrix
+ * when the first rank starts, and a rank may read its matrix once every rank's
+ * kernel has completed.  HQ_ERR_UNSUPPORTED unless n_local % 256 == 0,
+ * k % 128 == 0 and m > 128; world <= 8.
+ */
+int hq_dense_gemm_allgather(const void* a, const void* b, const void* sfa,
+                            const void* sfb, void* const* outs, int world,
+                            int rank, int64_t m, int64_t n_local, int64_t k,
+                            int64_t sfa_bytes, int64_t sfb_bytes, int64_t ldo,
+                            int sm_count, int use_pdl, int device, void* stream,
+                            char* err, size_t errlen);
+
+/*
  * MXFP8 dense GEMM for at most 32 activation rows that allocates nothing: no
  * cudaMalloc, no cudaFree, no allocating library call, on any call.  It has no
  * counterpart in the reference.  It is for callers that cannot have a library

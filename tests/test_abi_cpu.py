@@ -357,3 +357,25 @@ def test_product_never_imports_the_oracle():
         for f in files:
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 assert "oracle" not in open(os.path.join(dirpath, f)).read(), f
+
+
+def test_gemm_allgather_rules_without_a_device(native):
+    import ctypes
+
+    from halops_b200 import _native
+
+    def call(world, rank, m, n_local, k, ldo):
+        outs = (ctypes.c_void_p * 8)(*([256] * 8))
+        _native.call("hq_dense_gemm_allgather", 256, 256, 256, 256, outs, world, rank, m, n_local, k, 1 << 40, 1 << 40,
+                     ldo, -1, 0, 0, None)
+
+    with pytest.raises(RuntimeError, match="world must be"):
+        call(9, 0, 256, 256, 128, 256 * 9)
+    with pytest.raises(RuntimeError, match="world must be"):
+        call(2, 2, 256, 256, 128, 512)
+    with pytest.raises(RuntimeError, match="multiple of 256"):
+        call(2, 0, 256, 128, 128, 256)
+    with pytest.raises(RuntimeError, match="multiple of 256"):
+        call(2, 0, 128, 256, 128, 512)
+    with pytest.raises(RuntimeError, match="row stride"):
+        call(2, 0, 256, 256, 128, 256)

@@ -63,6 +63,16 @@ def _worker():
                     f"rank {rank} {mode} {transport}: block-wise gathered output differs (call {i})"
                 # the next call may only overwrite the buffers once every rank has read them
                 staged.zero_()
+        # the all-gather inside the GEMM's epilogue (stores into the peers' symmetric memory),
+        # twice in a row on the same outputs, with a ragged last row tile the second time round
+        if mode == "w8a8-mxfp8":
+            for rows_used, wanted in ((1024, want4), (1024, want4), (384, want)):
+                aq, sa = (x4q, sfa4) if rows_used == 1024 else (xq, sfa)
+                for i in range(2):
+                    full = layer.gathered_fused(aq, sa)
+                    assert torch.equal(full, wanted), \
+                        f"rank {rank}: output gathered by the GEMM's own stores differs ({rows_used} rows, call {i})"
+                    full.zero_()
         # ... or slice an already quantised weight (contiguous scale range)
         layer2 = ColumnParallelDenseGemm(shard_quantized_weight(wq, sfb, mode, world, rank), mode=mode)
         if alpha is not None:
