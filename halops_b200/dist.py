@@ -13,7 +13,9 @@ with the GEMM by working on blocks of rows: while block ``i`` travels on a secon
 stream, the GEMM computes block ``i + 1``.  On GPUs with peer access the blocks
 are pushed into the peers' buffers (symmetric memory) by the copy engines, which
 take no SM from the GEMM; otherwise NCCL moves them and the GEMM leaves it a few
-SMs.
+SMs.  ``gathered_fused`` does the gather inside the GEMM: the epilogue of the
+2-CTA MXFP8 kernel stores every finished tile into the peers' outputs as well
+as into its own, so no copy or collective follows the kernel.
 
 One process per GPU (``torch.distributed``); the kernels run on each rank's
 current stream.
@@ -53,6 +55,10 @@ def shard_quantized_weight(wq: torch.Tensor, sfb: torch.Tensor, mode: str, world
     flat = sfb.reshape(-1)
     sf = flat[start * kb_dim:(start + rows) * kb_dim].view(rows, kb_dim)
     return wq[start:start + rows], sf
+
+
+class SymmetricMemoryUnavailable(RuntimeError):
+    """The peers' buffers cannot be mapped (no peer access, or no symmetric memory in this torch)."""
 
 
 class ColumnParallelDenseGemm:
@@ -272,12 +278,15 @@ class ColumnParallelDenseGemm:
             local = torch.empty(shape, dtype=torch.bfloat16, device=device)
             views = [local]
         else:
-            import torch.distributed._symmetric_memory as symm
+            try:
+                import torch.distributed._symmetric_memory as symm
 
-            group = self.group if self.group is not None else self._dist.group.WORLD
-            local = symm.empty(shape, dtype=torch.bfloat16, device=device)
-            handle = symm.rendezvous(local, group)
-            views = [handle.get_buffer(r, shape, torch.bfloat16) for r in range(self.world)]
+                group = self.group if self.group is not None else self._dist.group.WORLD
+                local = symm.empty(shape, dtype=torch.bfloat16, device=device)
+                handle = symm.rendezvous(local, group)
+                views = [handle.get_buffer(r, shape, torch.bfloat16) for r in range(self.world)]
+            except Exception as ex:  # no peer access / no symmetric memory in this build
+                raise SymmetricMemoryUnavailable(str(ex)) from ex
             if self._flag is None:
                 self._flag = torch.zeros([1], dtype=torch.int32, device=device)
         addresses = (ctypes.c_void_p * self.world)(*[v.data_ptr() for v in views])
@@ -286,10 +295,10 @@ class ColumnParallelDenseGemm:
 
     def gathered_fused(self, xq: torch.Tensor, sfa: torch.Tensor, sm_count: int = -1) -> torch.Tensor:
         """GEMM and all-gather in ONE kernel.  Every rank holds an ``[M, N]`` output in symmetric
-        memory; the GEMM's epilogue stores each finished tile into this rank's columns of its own
-        output (TMA stores) and, from the same registers, into the same columns of every peer's
-        output with plain 16-byte stores over NVLink, so the transfer of a tile runs while the
-        tensor cores work on the next one and no copy or collective kernel follows.  All loads
+        memory; the GEMM's epilogue stages each finished piece of a tile in shared memory once and
+        stores it, with one TMA store per matrix, into this rank's columns of its own output and
+        of every peer's output (over NVLink), so the transfer of a tile runs while the tensor
+        cores work on the next one and no copy or collective kernel follows.  All loads
         (operands, scales) are from this GPU's memory.  Two one-element NCCL all-reduces fence
         the call on the current stream: before the kernel (no rank still reads the previous
         result) and after it (every rank's stores are complete).  Returns this rank's ``[M, N]``
@@ -324,6 +333,12 @@ class ColumnParallelDenseGemm:
     def __call__(self, x: torch.Tensor, gather: bool = False, overlap: bool = False) -> torch.Tensor:
         if gather and overlap:
             xq, sfa = self._quant(x, mode=self.mode)
+            if xq.is_cuda and self.world > 1 and self.fused_supported(xq.size(0)):
+                # (on 2, 4 and 8 B200 the GEMM that gathers in its epilogue gave the shortest step)
+                try:
+                    return self.gathered_fused(xq, sfa)
+                except SymmetricMemoryUnavailable:  # on every rank alike: the block-wise overlap it is
+                    pass
             return self.gathered_as_matrix(self.gathered(xq, sfa))
         out = self.local(x)
         return self.as_matrix(self.gather(out)) if gather else out

@@ -317,10 +317,11 @@ int hq_selftest_bounded_wait(uint32_t limit_us, int device, void* stream,
  *                   outs[rank] lives on this device, the others are the peers'
  *                   matrices mapped into this process (symmetric memory)
  * The kernel (2-CTA 256 x 256 tile) writes columns [rank * n_local, (rank + 1) *
- * n_local) of EVERY matrix: its own through TMA stores, the peers' with plain
- * 16-byte global stores over NVLink from the same registers, tile by tile, so
- * the transfer overlaps the math.  Tensor maps and all loads cover this GPU's
- * memory only.  The caller fences across ranks: nobody may still read a matrix
+ * n_local) of EVERY matrix: each staged 32 x 64 piece of a finished tile goes
+ * out by one TMA store per matrix (rows of 128 bytes; the peers' over NVLink),
+ * tile by tile, so the transfer overlaps the math.  Every load of the kernel
+ * (operands, scales) is from this GPU's memory; none uses cluster multicast.
+ * The caller fences across ranks: nobody may still read a matrix
  * when the first rank starts, and a rank may read its matrix once every rank's
  * kernel has completed.  HQ_ERR_UNSUPPORTED unless n_local % 256 == 0,
  * k % 128 == 0 and m > 128; world <= 8.
