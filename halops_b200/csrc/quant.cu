@@ -59,6 +59,23 @@ struct Pair<__nv_bfloat16> {
         asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));  // a NaN operand is ignored
         return r;
     }
+    static constexpr uint32_t kInfBits = 0x7f80u;  // magnitudes from here on: infinity, NaN
+    static __device__ __forceinline__ uint32_t abs2(uint32_t a) {
+        uint32_t r;
+        asm("abs.bf16x2 %0, %1;" : "=r"(r) : "r"(a));
+        return r;
+    }
+    // max(a, |b|) and max(a, b) that return NaN when an operand is NaN
+    static __device__ __forceinline__ uint32_t absmax2_nan(uint32_t a, uint32_t b) {
+        uint32_t r;
+        asm("{\n\t.reg .b32 t;\n\tabs.bf16x2 t, %2;\n\tmax.NaN.bf16x2 %0, %1, t;\n\t}" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
+    static __device__ __forceinline__ uint32_t max2_nan(uint32_t a, uint32_t b) {
+        uint32_t r;
+        asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
     static __device__ __forceinline__ float lo(uint32_t w) { return __uint_as_float(w << 16); }
     static __device__ __forceinline__ float hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 };
@@ -69,6 +86,22 @@ struct Pair<__half> {
     static __device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) {
         uint32_t r;
         asm("max.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
+    static constexpr uint32_t kInfBits = 0x7c00u;
+    static __device__ __forceinline__ uint32_t abs2(uint32_t a) {
+        uint32_t r;
+        asm("abs.f16x2 %0, %1;" : "=r"(r) : "r"(a));
+        return r;
+    }
+    static __device__ __forceinline__ uint32_t absmax2_nan(uint32_t a, uint32_t b) {
+        uint32_t r;
+        asm("{\n\t.reg .b32 t;\n\tabs.f16x2 t, %2;\n\tmax.NaN.f16x2 %0, %1, t;\n\t}" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
+    static __device__ __forceinline__ uint32_t max2_nan(uint32_t a, uint32_t b) {
+        uint32_t r;
+        asm("max.NaN.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
         return r;
     }
     static __device__ __forceinline__ float lo(uint32_t w) {
@@ -121,6 +154,23 @@ __device__ __forceinline__ float2 fma2_sq(float2 v, float2 acc) {
         : "f"(v.x), "f"(v.y), "f"(acc.x), "f"(acc.y));
     return r;
 }
+// (a * s + 0, b * s + 0) as one packed instruction: the product, with the -0.0 that a zero
+// factor gives turned into +0.0 (a product that underflows to zero keeps its sign: use it only
+// where s is large enough for that not to happen, as the NVFP4 reciprocal scales are)
+__device__ __forceinline__ float2 mul2_pos_zero(float a, float b, float s) {
+    float2 r;
+    asm("{\n\t"
+        ".reg .b64 t, u, z;\n\t"
+        "mov.b64 t, {%2, %3};\n\t"
+        "mov.b64 u, {%4, %4};\n\t"
+        "mov.b64 z, {%5, %5};\n\t"
+        "fma.rn.f32x2 t, t, u, z;\n\t"
+        "mov.b64 {%0, %1}, t;\n\t"
+        "}"
+        : "=f"(r.x), "=f"(r.y)
+        : "f"(a), "f"(b), "f"(s), "f"(0.0f));
+    return r;
+}
 // -0.0 -> +0.0, everything else unchanged.  (Written as two scalar adds: the
 // packed add.rn.f32x2 with a zero operand does not survive ptxas.)
 __device__ __forceinline__ float2 add_zero2(float2 v) {
@@ -171,6 +221,18 @@ __device__ __forceinline__ uint32_t e2m1x2_half_away(float2 v) {
     };
     return __nv_cvt_float2_to_fp4x2(make_float2(away(v.x), away(v.y)), __NV_E2M1, cudaRoundNearest);
 }
+// The same rounding for finite values, in three instructions: the lowest mantissa bit is set
+// before the conversion.  Every midpoint between two e2m1 values is a float whose lowest bit is
+// clear, so setting the bit moves a value that sits on a midpoint just past it, away from zero,
+// and moves no other value onto or across a midpoint (the neighbour one ulp below a midpoint
+// has the bit set already); round-to-nearest-even then gives round-half-away.  Zero becomes the
+// smallest subnormal and still converts to zero.  Not for infinities (the bit would make a NaN):
+// the caller's values are finite products of finite factors.
+__device__ __forceinline__ uint32_t e2m1x2_half_away_finite(float2 v) {
+    return __nv_cvt_float2_to_fp4x2(make_float2(__uint_as_float(__float_as_uint(v.x) | 1u),
+                                                __uint_as_float(__float_as_uint(v.y) | 1u)),
+                                    __NV_E2M1, cudaRoundNearest);
+}
 // Same for values that are exact products of a 16-bit float and a power of two
 // and have already been scaled by 1 + 2^-23: such a value is never within an
 // ulp below a midpoint, so plain round-to-nearest-even gives ties away.
@@ -182,27 +244,26 @@ __device__ __forceinline__ uint32_t e4m3x2(float x, float y) {
     return __nv_cvt_float2_to_fp8x2(make_float2(x, y), __NV_SATFINITE, __NV_E4M3);
 }
 
-// Scale byte and codes of the kEpl = 2 * kWords values one lane holds of a
-// quantisation group (packed two per word): 4 lanes share a 32-element group
-// and reduce its amax with two shuffles, NVFP4 gives a lane a whole 16-element
-// group.  codes[i] holds the two codes of word i: 16 bits (e4m3) or 8 bits
-// (e2m1).  Every lane of the warp must call it.
+// quantize_piece for a group that holds a NaN or an infinity (rare).  The
+// lanes that share the group call it together; other lanes of the warp may be elsewhere, so
+// the shuffles name only the group's lanes.
 template <typename T, int kMode>
-__device__ __forceinline__ uint32_t quantize_piece(
+__device__ __forceinline__ uint32_t quantize_piece_special(
     const uint32_t (&w)[(kMode == HQ_MODE_W4A4_NVFP4 ? 16 : 8) / 2],
     uint32_t (&codes)[(kMode == HQ_MODE_W4A4_NVFP4 ? 16 : 8) / 2]) {
     constexpr bool kNv = kMode == HQ_MODE_W4A4_NVFP4;
     constexpr bool kFp4 = kMode != HQ_MODE_W8A8_MXFP8;
     constexpr int kWords = (kNv ? 16 : 8) / 2;
     using P = Pair<T>;
+    const uint32_t group_lanes = kNv ? 0u : 0xfu << (threadIdx.x & 28u);
     // group amax on the packed 16-bit values (NaN operands are ignored, as fmaxf does)
     uint32_t mx = w[0] & 0x7fff7fffu;
 #pragma unroll
     for (int i = 1; i < kWords; ++i) mx = P::max2(mx, w[i] & 0x7fff7fffu);
     mx = P::max2(mx, __byte_perm(mx, 0, 0x1032));
     if constexpr (!kNv) {
-        mx = P::max2(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = P::max2(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        mx = P::max2(mx, __shfl_xor_sync(group_lanes, mx, 1));
+        mx = P::max2(mx, __shfl_xor_sync(group_lanes, mx, 2));
     }
     const float amax = fmaxf(P::lo(mx), kAmaxFloor);
 
@@ -215,7 +276,12 @@ __device__ __forceinline__ uint32_t quantize_piece(
         sf_byte = ue8m0_of_amax<0x00400000u, 2>(amax);
         inv = inv_pow2(sf_byte);
     } else {
-        const float s = fminf(fmaxf(__fdiv_rn(amax, kE2m1Max), 0.0f), kE4m3Max);
+        // amax / 6, correctly rounded: a product with 1/6 and one Newton correction of the quotient
+        // (checked against the division for every bf16 and fp16 amax and for the floor)
+        constexpr float kSixth = 1.0f / 6.0f;
+        const float q0 = __fmul_rn(amax, kSixth);
+        const float quot = __fmaf_rn(__fmaf_rn(-kE2m1Max, q0, amax), kSixth, q0);
+        const float s = fminf(quot, kE4m3Max);
         sf_byte = __nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3);
         // UE4M3 may round a tiny scale to 0: smallest positive code (2^-9)
         if (sf_byte == 0u) sf_byte = 1u;
@@ -239,9 +305,9 @@ __device__ __forceinline__ uint32_t quantize_piece(
             if constexpr (kMode == HQ_MODE_W8A8_MXFP8) {
                 codes[i] = e4m3x2(x.x, x.y);
             } else if constexpr (kMode == HQ_MODE_W4A4_MXFP4) {
-                codes[i] = e2m1x2_rne(add_zero2(x)) & 0xffu;
+                codes[i] = e2m1x2_rne(add_zero2(x));
             } else {
-                codes[i] = e2m1x2_half_away(add_zero2(x)) & 0xffu;
+                codes[i] = e2m1x2_half_away(add_zero2(x));
             }
         }
     } else {
@@ -253,11 +319,78 @@ __device__ __forceinline__ uint32_t quantize_piece(
             if constexpr (!kFp4) {
                 codes[i] = e4m3x2(a, b);
             } else {
-                codes[i] = e2m1x2_half_away(add_zero2(make_float2(a, b))) & 0xffu;
+                codes[i] = e2m1x2_half_away(add_zero2(make_float2(a, b)));
             }
         }
     }
 
+    return sf_byte;
+}
+
+// Scale byte and codes of the kEpl = 2 * kWords values one lane holds of a
+// quantisation group (packed two per word): 4 lanes share a 32-element group
+// and reduce its amax with two shuffles, NVFP4 gives a lane a whole 16-element
+// group.  codes[i] holds the two codes of word i: 16 bits (e4m3) or 8 bits
+// (e2m1).  Every lane of the warp must call it.
+//
+// The maximum of the magnitudes is taken with the NaN-propagating max, so one compare of
+// the result tells whether the group holds a NaN or an infinity.  Such groups go to
+// quantize_piece_special, which implements the reference's clamp (NaN -> -MAX, infinities
+// saturate) literally; every other group holds finite values only, whose scaled values
+// cannot overflow: no clamp, no NaN rule, and the reciprocal scale is never zero.
+template <typename T, int kMode>
+__device__ __forceinline__ uint32_t quantize_piece(
+    const uint32_t (&w)[(kMode == HQ_MODE_W4A4_NVFP4 ? 16 : 8) / 2],
+    uint32_t (&codes)[(kMode == HQ_MODE_W4A4_NVFP4 ? 16 : 8) / 2]) {
+    constexpr bool kNv = kMode == HQ_MODE_W4A4_NVFP4;
+    constexpr int kWords = (kNv ? 16 : 8) / 2;
+    using P = Pair<T>;
+    uint32_t mx = P::abs2(w[0]);
+#pragma unroll
+    for (int i = 1; i < kWords; ++i) mx = P::absmax2_nan(mx, w[i]);
+    mx = P::max2_nan(mx, __byte_perm(mx, 0, 0x1032));
+    if constexpr (!kNv) {
+        mx = P::max2_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = P::max2_nan(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    }
+    if ((mx & 0x7fffu) >= P::kInfBits) return quantize_piece_special<T, kMode>(w, codes);
+    const float amax = fmaxf(P::lo(mx), kAmaxFloor);
+
+    uint32_t sf_byte;
+    float inv;
+    if constexpr (kMode == HQ_MODE_W8A8_MXFP8) {
+        sf_byte = ue8m0_of_amax<0x00600000u, 8>(amax);
+        inv = inv_pow2(sf_byte);
+    } else if constexpr (kMode == HQ_MODE_W4A4_MXFP4) {
+        sf_byte = ue8m0_of_amax<0x00400000u, 2>(amax);
+        // (1 + 2^-23: see e2m1x2_rne)
+        inv = inv_pow2(sf_byte) * (1.0f + 1.1920929e-7f);
+    } else {
+        // amax / 6, correctly rounded: a product with 1/6 and one Newton correction of the quotient
+        // (checked against the division for every bf16 and fp16 amax and for the floor)
+        constexpr float kSixth = 1.0f / 6.0f;
+        const float q0 = __fmul_rn(amax, kSixth);
+        const float quot = __fmaf_rn(__fmaf_rn(-kE2m1Max, q0, amax), kSixth, q0);
+        sf_byte = __nv_cvt_float_to_fp8(fminf(quot, kE4m3Max), __NV_SATFINITE, __NV_E4M3);
+        // UE4M3 may round a tiny scale to 0: smallest positive code (2^-9)
+        if (sf_byte == 0u) sf_byte = 1u;
+        const float dec = __half2float(__half(__nv_cvt_fp8_to_halfraw(
+            static_cast<__nv_fp8_storage_t>(sf_byte), __NV_E4M3)));
+        inv = __frcp_rn(dec);
+    }
+
+#pragma unroll
+    for (int i = 0; i < kWords; ++i) {
+        if constexpr (kMode == HQ_MODE_W8A8_MXFP8) {
+            const float2 x = mul2(P::lo(w[i]), P::hi(w[i]), inv);
+            codes[i] = e4m3x2(x.x, x.y);
+        } else if constexpr (kMode == HQ_MODE_W4A4_MXFP4) {
+            // (a product that underflows to -0.0 must come out as +0.0 too: multiply, then add zero)
+            codes[i] = e2m1x2_rne(add_zero2(mul2(P::lo(w[i]), P::hi(w[i]), inv)));
+        } else {
+            codes[i] = e2m1x2_half_away_finite(mul2_pos_zero(P::lo(w[i]), P::hi(w[i]), inv));
+        }
+    }
     return sf_byte;
 }
 
@@ -317,8 +450,9 @@ __device__ __forceinline__ void quantize_segment(const T* __restrict__ in_row,
             uint32_t q[kWords / 4];
 #pragma unroll
             for (int h = 0; h < kWords / 4; ++h) {
-                q[h] = codes[4 * h] | (codes[4 * h + 1] << 8) | (codes[4 * h + 2] << 16) |
-                       (codes[4 * h + 3] << 24);
+                // byte 0 of four code words -> one word
+                q[h] = __byte_perm(__byte_perm(codes[4 * h], codes[4 * h + 1], 0x0040),
+                                   __byte_perm(codes[4 * h + 2], codes[4 * h + 3], 0x0040), 0x5410);
             }
             if (active) {
                 uint8_t* const dst = q_row + (col0 >> 1) + lane * (kEpl / 2);
