@@ -805,7 +805,7 @@ def run_sweep(args):
             "quant_b_frac_of_hbm": round(n * k * q_bpe / qb["us"] / 1e3 / peaks["hbm_gbs"], 3),
             "quant_incl_tflops": round(flops / (gemm_us + qa["us"] + qb["us"]) / 1e6, 1),
         }), flush=True)
-    if only:
+    if only and only != "next":
         return
     run_sweep_next_rows(tm, dev, peaks)
 
@@ -957,7 +957,8 @@ def main():
                     help="run only warm-up and the timed steps (for profiler captures)")
     ap.add_argument("--sweep", action="store_true",
                     help="time every benchmark configuration (GEMM only / quantizer only, cold L2) instead")
-    ap.add_argument("--only", default=None, help="with --sweep: only the dense rows whose label contains this")
+    ap.add_argument("--only", default=None, help="with --sweep: only the dense rows whose label contains this; 'next' = only the rows "
+                         "beyond the dense path (rms_norm_quant, epilogues, grouped, low latency)")
     ap.add_argument("--shape", default=None, metavar="MODE,M,N,K",
                     help="time one dense GEMM shape (GEMM only, cold L2) instead, e.g. w8a8-mxfp8,16,24576,1536")
     args = ap.parse_args()
