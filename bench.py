@@ -915,7 +915,8 @@ def run_sweep_low_latency(tm, dev, peaks):
 
 
 def run_shape(args):
-    """One dense GEMM shape, GEMM only: MODE,M,N,K.  Prints one JSON line (cold-L2 median);
+    """One dense GEMM shape, GEMM only: MODE,M,N,K (or rms,M,0,K: rms_norm_quant alone).  Prints one JSON
+    line (cold-L2 median);
     with --kernels-only just 3 warm-up and 3 measured launches, for profiler captures."""
     import halops_b200 as hq
 
@@ -924,6 +925,22 @@ def run_shape(args):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     g = torch.Generator(device=dev).manual_seed(2026)
+    if mode == "rms":  # rms,M,0,K: rms_norm_quant of an [M, K] activation
+        x = (torch.randn([m, k], generator=g, device=dev) * 3).to(torch.bfloat16)
+        w = (torch.rand([k], generator=g, device=dev) + 0.5).to(torch.bfloat16)
+        fn = lambda: hq.rms_norm_quant(x, w, 1e-6, True, False)  # noqa: E731
+        if args.kernels_only:
+            flush = torch.empty([256 << 20], dtype=torch.uint8, device=dev)
+            for _ in range(6):
+                flush.zero_()
+                fn()
+            torch.cuda.synchronize()
+            print(json.dumps({"shape": args.shape, "kernels_only": True}), flush=True)
+            return
+        r = Timers(dev).row(fn)
+        print(json.dumps({"shape": args.shape, "rms_norm_quant": r,
+                          "gbs": round((m * k * 3.03125 + k * 2) / r["us"] / 1e3, 1)}), flush=True)
+        return
     a = torch.randn([m, k], generator=g, device=dev).to(torch.bfloat16)
     b = (torch.randn([n, k], generator=g, device=dev) * 0.02).to(torch.bfloat16)
     aq, sfa = hq.group_wise_quant(a, mode=mode)
