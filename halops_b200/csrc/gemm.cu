@@ -1311,6 +1311,123 @@ __device__ __forceinline__ uint32_t instr_desc_pair(uint32_t sf_id) {
            (uint32_t(256 >> 4) << 24) | (sf_id << 29);
 }
 
+// What one persistent-loop iteration of the 2-CTA kernel works on: a 256-row tile of the
+// stacked A rows against BN rows of one weight.
+struct PairWork {
+    int a_row0;     // first of the tile's 256 stacked A rows (a multiple of 256)
+    int b_row0;     // first of the BN weight rows in the stacked weights
+    int row_lo;     // tile rows [row_lo, row_hi) belong to this item; the others are padding,
+    int row_hi;     //   belong to another expert, or lie beyond M
+    int out_row0;   // output row of tile row 0
+    int out_col0;   // first output column
+    int bias_col0;  // first bias element
+};
+
+// The grouped kinds on the 2-CTA tile (kGrouped; dense otherwise).  Batches and masked experts
+// take it when their row count is a multiple of 256, so that no tile holds rows of two of
+// them; an item is (expert, 256-row tile that holds valid rows of it, column tile).  The
+// contiguous layout takes it when M is a multiple of 256: a tile whose four 64-row quarters
+// belong to several experts is worked once per run of equal experts, each pass storing its own
+// rows (the rule of the single-CTA kernel, with 256-row tiles).  The roles of the kernel walk
+// the same sequence of items, each with its own copy of this iterator.
+template <int BN, bool kGrouped>
+struct PairWorkIter {
+    GroupParams g;
+    int M, N, tiles_m, tiles_n;
+    int tile, stride;
+    int pass = 0;        // contiguous: run of the current tile to work next
+    int walk_group = 0;  // batch / masked: group of the last item and the number of
+    int walk_base = 0;   //   (group, row tile) pairs before it
+
+    __device__ PairWorkIter(const GroupParams& grp, int m, int n, int tm, int tn, int first, int step)
+        : g(grp), M(m), N(n), tiles_m(tm), tiles_n(tn), tile(first), stride(step) {}
+
+    __device__ bool next(PairWork& w) {
+        if (!kGrouped || g.kind == kGroupContiguous) {
+            if (tile >= tiles_m * tiles_n) return false;
+            const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+            w.a_row0 = tc.m * 256;
+            w.out_row0 = w.a_row0;
+            w.out_col0 = tc.n * BN;
+            w.row_lo = 0;
+            w.row_hi = min(256, M - w.a_row0);
+            int group = 0;
+            bool last = true;
+            if constexpr (kGrouped) {
+                int e[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int row = w.a_row0 + 64 * q;
+                    e[q] = row < M ? min(max(__ldg(g.table + row), 0), g.count - 1) : e[q > 0 ? q - 1 : 0];
+                }
+                int start = 0, run = 0, cur = e[0];
+                bool found = false;
+                group = e[0];
+#pragma unroll
+                for (int q = 1; q <= 4; ++q) {
+                    const bool ends = q == 4 || e[q & 3] != e[q - 1];  // the run [start, q) of quarters ends here
+                    if (!found && ends) {
+                        if (run == pass) {
+                            w.row_lo = 64 * start;
+                            w.row_hi = min(64 * q, M - w.a_row0);
+                            group = cur;
+                            last = q == 4;
+                            found = true;
+                        } else {
+                            ++run;
+                            start = q;
+                            cur = e[q & 3];
+                        }
+                    }
+                }
+                pass = last ? 0 : pass + 1;
+            }
+            w.b_row0 = group * N + tc.n * BN;
+            w.bias_col0 = w.b_row0;
+            if (last) tile += stride;
+            return true;
+        }
+        // batch / masked
+        const int pair = tile / tiles_n;
+        const int nt = tile - pair * tiles_n;
+        int first, valid;
+        for (;;) {
+            if (walk_group >= g.count) return false;
+            first = walk_group * g.rows;
+            valid = g.kind == kGroupMasked ? min(max(__ldg(g.table + walk_group), 0), g.rows) : g.rows;
+            const int cnt = (valid + 255) / 256;
+            if (pair < walk_base + cnt) break;
+            walk_base += cnt;
+            ++walk_group;
+        }
+        const int rt = pair - walk_base;
+        w.a_row0 = first + rt * 256;
+        w.row_lo = 0;
+        w.row_hi = min(256, valid - rt * 256);
+        w.b_row0 = walk_group * N + nt * BN;
+        w.bias_col0 = w.b_row0;
+        if (g.kind == kGroupBatch) {
+            w.out_row0 = w.a_row0 - first;
+            w.out_col0 = w.b_row0;
+        } else {
+            w.out_row0 = w.a_row0;
+            w.out_col0 = nt * BN;
+        }
+        tile += stride;
+        return true;
+    }
+};
+
+// What the grouped 2-CTA kernel needs beyond the tensor maps: the groups, and the output for
+// the rows it stores from registers (tiles that are only partly this item's).
+struct PairGroupArgs {
+    GroupParams grp;
+    __nv_bfloat16* out;
+    int64_t ldo;
+    int m;  // stacked A rows
+    int n;  // columns per weight
+};
+
 // Column-parallel all-gather fused into the epilogue (kGather): besides its own output, a rank
 // stores every finished chunk of a tile into the same columns of its peers' outputs (symmetric
 // memory mapped over NVLink): the TMA store that writes the staged chunk to the local output
@@ -1326,14 +1443,15 @@ struct GatherMaps<true> {
     int count;
 };
 
-template <int BN, int KIND, bool kGather = false>
+template <int BN, int KIND, bool kGather = false, bool kGrouped = false>
 __global__ void __launch_bounds__((Cfg2<BN, KIND>::kThreads), 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_d, const __grid_constant__ CUtensorMap tm_sfa,
                  const __grid_constant__ CUtensorMap tm_sfb, const float* __restrict__ alpha,
                  const __nv_bfloat16* __restrict__ bias, int epi_op, int k_tiles, int kq_dim, int tiles_m,
-                 int tiles_n, const __grid_constant__ GatherMaps<kGather> peers) {
+                 int tiles_n, const __grid_constant__ GatherMaps<kGather> peers, const PairGroupArgs ga) {
     using C = Cfg2<BN, KIND>;
+    using Iter = PairWorkIter<BN, kGrouped>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* const smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
@@ -1352,7 +1470,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const bool leader = rank == 0;
     const int cluster_id = blockIdx.x >> 1;
     const int num_clusters = gridDim.x >> 1;
-    const int num_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
@@ -1389,17 +1506,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
     ptx::pdl_wait();
 
-    const int my_tiles = cluster_id < num_tiles ? (num_tiles - cluster_id + num_clusters - 1) / num_clusters : 0;
-    const uint32_t total_its = uint32_t(my_tiles) * uint32_t(k_tiles);
     if (warp == 0) {
         // ------------------------------------------------------------ box loader (both CTAs)
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
-                const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
-                const int m0 = tc.m * 256 + int(rank) * kBM;
-                const int n0 = tc.n * BN + int(rank) * (BN / 2);
+            Iter walk(ga.grp, ga.m, ga.n, tiles_m, tiles_n, cluster_id, num_clusters);
+            PairWork wk;
+            while (ok && walk.next(wk)) {
+                const int m0 = wk.a_row0 + int(rank) * kBM;
+                const int n0 = wk.b_row0 + int(rank) * (BN / 2);
                 for (int kt = 0; kt < k_tiles; ++kt, ++it) {
                     const uint32_t s = it % C::kStages;
                     ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ((it / C::kStages) & 1u) ^ 1u, abort,
@@ -1428,10 +1544,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
-                const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
-                const int sfa_atom_row = (tc.m * 2 + int(rank)) * kq_dim;
-                const int sfb_atom_row = (tc.n * BN / 128) * kq_dim;
+            Iter walk(ga.grp, ga.m, ga.n, tiles_m, tiles_n, cluster_id, num_clusters);
+            PairWork wk;
+            while (ok && walk.next(wk)) {
+                const int sfa_atom_row = (wk.a_row0 / 128 + int(rank)) * kq_dim;
+                const int sfb_atom_row = (wk.b_row0 / 128) * kq_dim;
                 for (int kt = 0; kt < k_tiles; ++kt, ++it) {
                     const uint32_t s = it % C::kStages;
                     ok = wait_bar(ptx::smem_u32(&bars->empty[s]), ((it / C::kStages) & 1u) ^ 1u, abort,
@@ -1455,7 +1572,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         if (leader && lane == 0) {
             const int cw = warp - 7;
             bool ok = true;
-            for (uint32_t it = 0; ok && it < total_its; ++it) {
+            Iter walk(ga.grp, ga.m, ga.n, tiles_m, tiles_n, cluster_id, num_clusters);
+            PairWork wk;
+            uint32_t total_its = 0;
+            for (uint32_t it = 0; ok; ++it) {
+                if (it == total_its) {  // the k-tiles of the next item
+                    if (!walk.next(wk)) break;
+                    total_its += uint32_t(k_tiles);
+                }
                 const uint32_t s = it % C::kStages;
                 ok = wait_bar(ptx::smem_u32(&bars->full[s]), (it / C::kStages) & 1u, abort, kStatusProducer);
                 if (!ok) break;
@@ -1495,7 +1619,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             uint32_t it = 0;
             uint32_t t = 0;
             bool ok = true;
-            for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++t) {
+            Iter walk(ga.grp, ga.m, ga.n, tiles_m, tiles_n, cluster_id, num_clusters);
+            PairWork wk;
+            for (; ok && walk.next(wk); ++t) {
                 const uint32_t as = t & 1u;
                 const uint32_t aph = (t >> 1) & 1u;
                 const uint32_t acc = tmem + as * C::kAccStride;
@@ -1582,10 +1708,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         uint32_t t = 0;
         uint32_t stores = 0;
         bool ok = true;
-        for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters, ++t) {
-            const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
-            const int m0 = tc.m * 256 + int(rank) * kBM;
-            const int n0 = tc.n * BN;
+        Iter walk(ga.grp, ga.m, ga.n, tiles_m, tiles_n, cluster_id, num_clusters);
+        PairWork wk;
+        for (; ok && walk.next(wk); ++t) {
+            const int m0 = wk.out_row0 + int(rank) * kBM;
+            const int n0 = wk.out_col0;
+            // rows of this CTA's half of the tile that belong to the item
+            const int half_lo = min(max(wk.row_lo - int(rank) * kBM, 0), kBM);
+            const int half_hi = min(max(wk.row_hi - int(rank) * kBM, 0), kBM);
+            // (a dense tile that sticks out beyond M is clipped by the TMA store; the grouped kinds
+            // come here with whole tiles inside M only)
+            const bool partial = kGrouped && (half_lo != 0 || half_hi != kBM);
             const uint32_t as = t & 1u;
             const uint32_t aph = (t >> 1) & 1u;
             ok = wait_bar(ptx::smem_u32(&bars->acc_full[as]), aph, abort, kStatusEpilogue);
@@ -1642,7 +1775,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     }
                 }
                 uint32_t p[16];
-                epilogue_chunk(r, p, scale, bias != nullptr ? bias + n0 + c * kEpiChunk : nullptr, epi_op);
+                epilogue_chunk(r, p, scale, bias != nullptr ? bias + wk.bias_col0 + c * kEpiChunk : nullptr, epi_op);
+                if constexpr (kGrouped) {
+                    if (partial) {
+                        // only some rows of this half belong to the item: each thread stores its
+                        // own row's 32 columns from registers, or nothing
+                        const int r_half = int(lane_base) + lane;
+                        if (r_half >= half_lo && r_half < half_hi) {
+                            uint4* const dst = reinterpret_cast<uint4*>(ga.out + int64_t(m0 + r_half) * ga.ldo + n0 +
+                                                                        c * kEpiChunk);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                dst[j] = make_uint4(p[4 * j], p[4 * j + 1], p[4 * j + 2], p[4 * j + 3]);
+                            }
+                        }
+                        continue;
+                    }
+                }
                 if constexpr (kGather) {
                     // Two neighbouring chunks are staged as ONE box of 32 rows x 128 bytes (the warp's
                     // two buffers, 128-byte swizzle) and stored together: rows of 128 bytes use
@@ -1883,24 +2032,29 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     return HQ_OK;
 }
 
-template <int BN, int KIND, bool kGather = false>
+template <int BN, int KIND, bool kGather = false, bool kGrouped = false>
 int launch_pair(const GemmArgs& g, char* err, size_t errlen, __nv_bfloat16* const* gather = nullptr,
                 int gather_count = 0) {
     using C = Cfg2<BN, KIND>;
     static SmemOptIn opt_in;
     int dev = 0;
-    HQ_CUDA_TRY(opt_in.ensure(gemm_pair_kernel<BN, KIND, kGather>, C::kSmemBytes, &dev));
+    HQ_CUDA_TRY(opt_in.ensure(gemm_pair_kernel<BN, KIND, kGather, kGrouped>, C::kSmemBytes, &dev));
+    // the grouped kinds: weights (and their scales) of all groups are stacked; a batch writes
+    // [rows, count * N]
+    const int64_t weights = kGrouped ? g.grp.count : 1;
+    const int64_t out_rows = kGrouped && g.grp.kind == kGroupBatch ? g.grp.rows : g.m;
+    const int64_t out_cols = kGrouped && g.grp.kind == kGroupBatch ? weights * g.n : g.n;
 
     const uint64_t atoms_a = uint64_t((g.m + 127) / 128) * uint64_t(g.kq_dim);
-    const uint64_t atoms_b = uint64_t((g.n + 127) / 128) * uint64_t(g.kq_dim);
+    const uint64_t atoms_b = uint64_t(weights) * uint64_t((g.n + 127) / 128) * uint64_t(g.kq_dim);
     CUtensorMap tm_a, tm_b, tm_d, tm_sfa, tm_sfb;
     const bool maps_ok =
         make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.a, uint64_t(g.k_bytes), uint64_t(g.m),
                      uint64_t(g.k_bytes), kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B) &&
-        make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes), uint64_t(g.n),
+        make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes), uint64_t(weights * g.n),
                      uint64_t(g.k_bytes), kBKBytes, BN / 2, CU_TENSOR_MAP_SWIZZLE_128B) &&
         // (the gathering kernel stores boxes of two chunks, see its epilogue)
-        make_tmap_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out, uint64_t(g.n), uint64_t(g.m),
+        make_tmap_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out, uint64_t(out_cols), uint64_t(out_rows),
                      uint64_t(g.ldo) * 2, kGather ? 2 * kEpiChunk : kEpiChunk, 32,
                      kGather ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B) &&
         // scale atoms as rows of 128 32-bit words
@@ -1931,7 +2085,7 @@ int launch_pair(const GemmArgs& g, char* err, size_t errlen, __nv_bfloat16* cons
         occ.attrs = at;
         occ.numAttrs = 1;
         int n = 0;
-        HQ_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<BN, KIND, kGather>, &occ));
+        HQ_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<BN, KIND, kGather, kGrouped>, &occ));
         max_clusters[slot] = n > 0 ? n : 1;
     }
     const int clusters = min(min(g.sm_count / 2, max_clusters[slot]), tiles_m * tiles_n);
@@ -1946,9 +2100,10 @@ int launch_pair(const GemmArgs& g, char* err, size_t errlen, __nv_bfloat16* cons
         }
         peers.count = gather_count;
     }
-    HQ_CUDA_TRY(launch(gemm_pair_kernel<BN, KIND, kGather>, dim3(2 * clusters), dim3(C::kThreads), size_t(C::kSmemBytes),
-                       g.stream, g.pdl, 2, tm_a, tm_b, tm_d, tm_sfa, tm_sfb, g.alpha, g.bias, g.epi_op, k_tiles, g.kq_dim, tiles_m,
-                       tiles_n, peers));
+    const PairGroupArgs ga{kGrouped ? g.grp : GroupParams{kGroupDense, 1, 0, nullptr}, g.out, g.ldo, g.m, g.n};
+    HQ_CUDA_TRY(launch(gemm_pair_kernel<BN, KIND, kGather, kGrouped>, dim3(2 * clusters), dim3(C::kThreads),
+                       size_t(C::kSmemBytes), g.stream, g.pdl, 2, tm_a, tm_b, tm_d, tm_sfa, tm_sfb, g.alpha, g.bias,
+                       g.epi_op, k_tiles, g.kq_dim, tiles_m, tiles_n, peers, ga));
     return HQ_OK;
 }
 
@@ -2555,13 +2710,17 @@ const char* group_kind_name(int kind) {
 // multiples of 64 rows, the finest granularity of the reference's tiles
 // (csrc/kernel/gemm/gemm_dispatch.cuh:65-100).
 TilePick pick_tile_grouped(int kind, int64_t count, int64_t rows, int64_t total_m, int64_t n, int64_t k, int mode,
-                           int sm_count) {
+                           int sm_count, bool plain_epilogue = true) {
     if (count < 1 || rows < 1) return {0, false};
     if (kind == kGroupMasked && rows % 64 != 0) return {0, false};
     if (kind == kGroupContiguous && total_m % 64 != 0) return {0, false};
     const int64_t pad = kind != kGroupContiguous && rows % kBM != 0 ? (count - 1) * kBM : 0;
     TilePick pick = pick_tile(total_m + pad, n, k, mode, sm_count);
-    pick.pair = false;  // a forced or modelled pair choice falls back to the same width
+    // The 2-CTA tile: MXFP8 with a plain epilogue, and no 256-row tile may hold rows of two
+    // batches or expert slots (the contiguous layout is worked per run of experts, see
+    // PairWorkIter).  Otherwise a forced or modelled pair choice falls back to the same width.
+    const bool whole_tiles = kind == kGroupContiguous ? total_m % 256 == 0 : rows % 256 == 0;
+    if (!(mode == HQ_MODE_W8A8_MXFP8 && plain_epilogue && whole_tiles)) pick.pair = false;
     return pick;
 }
 
@@ -2657,7 +2816,8 @@ int grouped_gemm_impl(int kind, const void* a, const void* b, const void* sfa, c
                     "operands, scales and output must be 16-byte aligned and the output row stride a "
                     "multiple of 8 elements");
     }
-    const TilePick pick = pick_tile_grouped(kind, count, rows, total_m, n, k, mode, sm);
+    const TilePick pick = pick_tile_grouped(kind, count, rows, total_m, n, k, mode, sm,
+                                            epilogue == HQ_EPILOGUE_IDENTITY && !quant_epi);
 
     GemmArgs g;
     g.a = a;
@@ -2688,6 +2848,10 @@ int grouped_gemm_impl(int kind, const void* a, const void* b, const void* sfa, c
         default:                                               \
             return launch_tile<64, KIND>(g, err, errlen);      \
     }
+    if (pick.pair) {
+        return pick.bn == 256 ? launch_pair<256, 0, false, true>(g, err, errlen)
+                              : launch_pair<128, 0, false, true>(g, err, errlen);
+    }
     if (mode == HQ_MODE_W8A8_MXFP8) {
         HQ_DISPATCH(0)
     } else if (w4a8) {
@@ -2715,10 +2879,11 @@ extern "C" int hq_describe_group_tile(int kind, int64_t count, int64_t rows, int
     const hq::TilePick pick = hq::pick_tile_grouped(kind, count, rows, total_m, n, k, mode, sm > 0 ? sm : 148);
     if (pick.bn == 0) return hq::no_group_tile(buf, buflen, kind, mode, rows, total_m, n, k);
     if (buf != nullptr && buflen > 0) {
-        snprintf(buf, buflen, "[gemm] mode=%s kind=%s groups=%lld m=%lld grid_m=%lld n=%lld k=%lld sm=%d -> %dx%d/%d pair=0",
+        // (the Identity epilogue is assumed)
+        snprintf(buf, buflen, "[gemm] mode=%s kind=%s groups=%lld m=%lld grid_m=%lld n=%lld k=%lld sm=%d -> %dx%d/%d pair=%d",
                  hq::group_kind_name(kind), hq::mode_name(mode), (long long)count, (long long)rows,
-                 (long long)total_m, (long long)n, (long long)k, sm, hq::kBM, pick.bn,
-                 mode == HQ_MODE_W8A8_MXFP8 ? 128 : 256);
+                 (long long)total_m, (long long)n, (long long)k, sm, pick.pair ? 256 : hq::kBM, pick.bn,
+                 mode == HQ_MODE_W8A8_MXFP8 ? 128 : 256, pick.pair ? 1 : 0);
     }
     return HQ_OK;
 }

@@ -91,6 +91,23 @@ def test_fp4(hq, mode, k, b, m, n):
     _compare(out, xq, wq, sfa, sfb, mode, alpha=alpha)
 
 
+@pytest.mark.parametrize("tile", ["pair256", "pair128"])
+@pytest.mark.parametrize("b,m,n,k,add_bias", [(3, 512, 512, 256, True), (2, 256, 256, 128, False),
+                                              (4, 1024, 256, 384, False)], ids=lambda v: str(v))
+def test_2cta_tile(hq, monkeypatch, tile, b, m, n, k, add_bias):
+    """Batches of a multiple of 256 rows run on the 2-CTA tile, with the same bits as the single-CTA tiles."""
+    xq, wq, sfa, sfb = _inputs(hq, b, m, n, k, "w8a8-mxfp8", seed=5)
+    bias = None
+    if add_bias:
+        bias = torch.rand([b, n], generator=torch.Generator().manual_seed(9)).to(torch.bfloat16).cuda()
+    monkeypatch.setenv("HALOPS_B200_TILE", tile)
+    assert "pair=1" in hq.describe_group_tile("batch", b, m, n, k)
+    out = _run(hq, xq, wq, sfa, sfb, "w8a8-mxfp8", bias=bias)
+    _compare(out, xq, wq, sfa, sfb, "w8a8-mxfp8", bias=bias)
+    monkeypatch.setenv("HALOPS_B200_TILE", "128")
+    assert torch.equal(out, _run(hq, xq, wq, sfa, sfb, "w8a8-mxfp8", bias=bias))
+
+
 @pytest.mark.parametrize("tile", ["256", "128", "64"])
 def test_every_tile_width(hq, monkeypatch, tile):
     """Each single-CTA tile width walks the batches the same way."""

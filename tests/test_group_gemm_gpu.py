@@ -107,6 +107,46 @@ def test_masked_fp4(hq, mode, k, max_m, experts, n, masked):
     _masked_case(hq, max_m, experts, n, k, mode, masked, check_rows=1024)
 
 
+@pytest.mark.parametrize("tile", ["pair256", "pair128"])
+@pytest.mark.parametrize("max_m,experts,n,k,masked,add_bias", [
+    (256, 3, 512, 128, [256, 129, 5], False),
+    (512, 4, 512, 256, [512, 300, 0, 257], True),
+    (256, 5, 256, 384, [0, 256, 1, 128, 255], False),
+    (1024, 6, 1024, 512, None, False),
+], ids=lambda v: str(v) if not isinstance(v, list) else "m" + "-".join(map(str, v)))
+def test_masked_mxfp8_on_the_2cta_tile(hq, monkeypatch, tile, max_m, experts, n, k, masked, add_bias):
+    """Slots of a multiple of 256 rows run on the 2-CTA tile: full and partly filled 256-row tiles,
+    empty slots, a half of a tile without valid rows; rows past masked_m stay untouched."""
+    monkeypatch.setenv("HALOPS_B200_TILE", tile)
+    assert "pair=1" in hq.describe_group_tile("masked", experts, max_m, n, k)
+    if masked is None:
+        masked = [max_m] * experts
+    a = _masked_case(hq, max_m, experts, n, k, "w8a8-mxfp8", masked, add_bias, check_rows=1024)
+    # the same bits as the single-CTA tiles (every kernel sums the k-tiles in order)
+    monkeypatch.setenv("HALOPS_B200_TILE", "128")
+    b = _masked_case(hq, max_m, experts, n, k, "w8a8-mxfp8", masked, add_bias, check_rows=1024)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("tile", ["pair256", "pair128"])
+@pytest.mark.parametrize("counts,n,k,add_bias", [
+    ([256, 256], 512, 256, False),
+    ([64, 192, 128, 64, 64], 256, 128, True),          # two and three runs of experts in a 256-row tile
+    ([64] * 8, 256, 256, False),                       # four experts per tile
+    ([0, 128, 0, 384, 256], 256, 256, True),           # experts without rows, a run across two tiles
+    ([256] * 16, 1024, 512, False),
+], ids=lambda v: str(v) if not isinstance(v, list) else "runs" + "-".join(map(str, v)))
+def test_contiguous_mxfp8_on_the_2cta_tile(hq, monkeypatch, tile, counts, n, k, add_bias):
+    monkeypatch.setenv("HALOPS_B200_TILE", tile)
+    m = int(sum(counts))
+    assert m % 256 == 0
+    assert "pair=1" in hq.describe_group_tile("contiguous", len(counts), m // len(counts), n, k, total_m=m)
+    a = _contiguous_case(hq, counts, n, k, "w8a8-mxfp8", add_bias, check_rows=1024)
+    monkeypatch.setenv("HALOPS_B200_TILE", "128")
+    b = _contiguous_case(hq, counts, n, k, "w8a8-mxfp8", add_bias, check_rows=1024)
+    assert torch.equal(a, b)
+
+
 def test_masked_determinism_and_sm_count(hq):
     xq, wq, sfa, sfb = _inputs(hq, 6 * 128, 6, 256, 256, "w8a8-mxfp8", seed=2)
     masked = torch.tensor([128, 5, 0, 77, 128, 64], dtype=torch.int32).cuda()
