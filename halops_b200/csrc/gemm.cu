@@ -1263,11 +1263,15 @@ struct Cfg2 {
     static_assert(BN == 128 || BN == 256, "pair tile widths built");
     static constexpr int kABytes = kBM * kBKBytes;
     static constexpr int kBBytes = (BN / 2) * kBKBytes;
-    static constexpr int kSfKAtoms = KIND == 0 ? 1 : (KIND == 1 ? 4 : 2);
+    static constexpr bool kFp8Kind = KIND == 0 || KIND == 3;  // mxf8f6f4: e4m3 x e4m3, or e4m3 x packed e2m1
+    static constexpr int kSfKAtoms = kFp8Kind ? 1 : (KIND == 1 ? 4 : 2);
     static constexpr int kNAtoms = BN / 128;
     static constexpr int kSfaBytes = kSfKAtoms * 512;
     static constexpr int kSfbBytes = kNAtoms * kSfaBytes;
     static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+    // bytes a stage reads from global memory: packed e2m1 weights (KIND 3) are spread to one byte
+    // per value by the copy, and the barrier counts what was read
+    static constexpr int kStageTxBytes = kStageBytes - (KIND == 3 ? kBBytes / 2 : 0);
     static constexpr int kEpiBufs = 2;
     static constexpr int kEpiBytes = kEpiWarps * kEpiBufs * kEpiBufBytes;
     static constexpr int kBarBytes = 1024;
@@ -1282,9 +1286,9 @@ struct Cfg2 {
     // cycles on them; the MMAs alone take 512.  A set is free again once the MMAs that
     // read it have completed, so with 4 sets the copies run two k-tiles ahead.
     static constexpr int kSfCols = kSfKAtoms * 4 * (1 + kNAtoms);
-    static constexpr int kSfSets = BN < 256 ? 4 : (KIND == 0 ? 4 : (KIND == 2 ? 3 : 2));
+    static constexpr int kSfSets = BN < 256 ? 4 : (kFp8Kind ? 4 : (KIND == 2 ? 3 : 2));
     // warps: 0 box loader, 1 MMA issuer, 2-5 epilogue, 6 scale loader, 7.. scale copies
-    static constexpr int kCpWarps = KIND == 0 ? 1 : (KIND == 1 ? 3 : 2);
+    static constexpr int kCpWarps = kFp8Kind ? 1 : (KIND == 1 ? 3 : 2);
     // Two threads (warp 1 and the last warp) issue the MMAs of alternate k-tiles: issuing
     // 4 MMAs and the commit that releases the stage keeps one thread busy for longer
     // than the 512 cycles the MMAs run.  After its MMAs a thread
@@ -1305,9 +1309,11 @@ struct Cfg2 {
 
 template <int BN, int KIND>
 __device__ __forceinline__ uint32_t instr_desc_pair(uint32_t sf_id) {
-    constexpr uint32_t fmt = KIND == 0 ? 0u : 1u;
+    // (the fields and format codes of instr_desc; M = 256 across the pair)
+    constexpr uint32_t fmt_a = (KIND == 0 || KIND == 3) ? 0u : 1u;
+    constexpr uint32_t fmt_b = KIND == 0 ? 0u : (KIND == 3 ? 5u : 1u);
     constexpr uint32_t scale_fmt = KIND == 1 ? 0u : 1u;
-    return (sf_id << 4) | (fmt << 7) | (fmt << 10) | (uint32_t(BN >> 3) << 17) | (scale_fmt << 23) |
+    return (sf_id << 4) | (fmt_a << 7) | (fmt_b << 10) | (uint32_t(BN >> 3) << 17) | (scale_fmt << 23) |
            (uint32_t(256 >> 4) << 24) | (sf_id << 29);
 }
 
@@ -1532,7 +1538,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     // Bytes of all four loader threads of the pair are counted on the leader's
                     // barrier; only this thread registers them (the count may go negative in
                     // between).
-                    if (leader) ptx::mbar_arrive_expect_tx(ptx::smem_u32(&bars->full[s]), 2 * C::kStageBytes);
+                    if (leader) ptx::mbar_arrive_expect_tx(ptx::smem_u32(&bars->full[s]), 2 * C::kStageTxBytes);
                     ptx::tma_load_2d_pair(a_base + s * C::kABytes, &tm_a, kt * kBKBytes, m0, full);
                     ptx::tma_load_2d_pair(b_base + s * C::kBBytes, &tm_b, kt * kBKBytes, n0, full);
                 }
@@ -1668,7 +1674,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         uint32_t atom, sf_id;
-                        if constexpr (KIND == 0) {
+                        if constexpr (KIND == 0 || KIND == 3) {
                             atom = 0;
                             sf_id = k;
                         } else if constexpr (KIND == 1) {
@@ -2051,8 +2057,13 @@ int launch_pair(const GemmArgs& g, char* err, size_t errlen, __nv_bfloat16* cons
     const bool maps_ok =
         make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.a, uint64_t(g.k_bytes), uint64_t(g.m),
                      uint64_t(g.k_bytes), kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B) &&
-        make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes), uint64_t(weights * g.n),
-                     uint64_t(g.k_bytes), kBKBytes, BN / 2, CU_TENSOR_MAP_SWIZZLE_128B) &&
+        // (KIND 3: packed e2m1 weights, spread to one byte per value by the copy; see launch_tile)
+        (KIND == 3 ? make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, g.b, uint64_t(g.k_bytes),
+                                  uint64_t(weights * g.n), uint64_t(g.k_bytes / 2), kBKBytes, BN / 2,
+                                  CU_TENSOR_MAP_SWIZZLE_128B)
+                   : make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, g.b, uint64_t(g.k_bytes),
+                                  uint64_t(weights * g.n), uint64_t(g.k_bytes), kBKBytes, BN / 2,
+                                  CU_TENSOR_MAP_SWIZZLE_128B)) &&
         // (the gathering kernel stores boxes of two chunks, see its epilogue)
         make_tmap_2d(&tm_d, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, g.out, uint64_t(out_cols), uint64_t(out_rows),
                      uint64_t(g.ldo) * 2, kGather ? 2 * kEpiChunk : kEpiChunk, 32,
@@ -2716,11 +2727,12 @@ TilePick pick_tile_grouped(int kind, int64_t count, int64_t rows, int64_t total_
     if (kind == kGroupContiguous && total_m % 64 != 0) return {0, false};
     const int64_t pad = kind != kGroupContiguous && rows % kBM != 0 ? (count - 1) * kBM : 0;
     TilePick pick = pick_tile(total_m + pad, n, k, mode, sm_count);
-    // The 2-CTA tile: MXFP8 with a plain epilogue, and no 256-row tile may hold rows of two
+    // The 2-CTA tile: MXFP8 (or e4m3 x MXFP4) with a plain epilogue, and no 256-row tile may hold rows of two
     // batches or expert slots (the contiguous layout is worked per run of experts, see
     // PairWorkIter).  Otherwise a forced or modelled pair choice falls back to the same width.
     const bool whole_tiles = kind == kGroupContiguous ? total_m % 256 == 0 : rows % 256 == 0;
-    if (!(mode == HQ_MODE_W8A8_MXFP8 && plain_epilogue && whole_tiles)) pick.pair = false;
+    const bool fp8_kind = mode == HQ_MODE_W8A8_MXFP8 || (mode == HQ_MODE_W4A8_MXFP4 && kind != kGroupBatch);
+    if (!(fp8_kind && plain_epilogue && whole_tiles)) pick.pair = false;
     return pick;
 }
 
@@ -2847,6 +2859,10 @@ int grouped_gemm_impl(int kind, const void* a, const void* b, const void* sfa, c
             return launch_tile<128, KIND>(g, err, errlen);     \
         default:                                               \
             return launch_tile<64, KIND>(g, err, errlen);      \
+    }
+    if (pick.pair && w4a8) {
+        return pick.bn == 256 ? launch_pair<256, 3, false, true>(g, err, errlen)
+                              : launch_pair<128, 3, false, true>(g, err, errlen);
     }
     if (pick.pair) {
         return pick.bn == 256 ? launch_pair<256, 0, false, true>(g, err, errlen)

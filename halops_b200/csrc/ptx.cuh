@@ -279,7 +279,7 @@ __device__ __forceinline__ void tc_mma_block_scaled(uint32_t d, uint64_t adesc, 
             HQ_MMA_ASM(".cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::2X");
         }
     } else {
-        if constexpr (kKind == 0) {
+        if constexpr (kKind == 0 || kKind == 3) {
             HQ_MMA_ASM(".cta_group::2.kind::mxf8f6f4.block_scale");
         } else if constexpr (kKind == 1) {
             HQ_MMA_ASM(".cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X");

@@ -383,6 +383,42 @@ def test_contiguous_w4a8(hq, counts, n, k):
     _compare(out, ref, np.arange(ids.size), "w4a4-mxfp4", None)
 
 
+@pytest.mark.parametrize("tile", ["pair256", "pair128"])
+def test_w4a8_on_the_2cta_tile(hq, monkeypatch, tile):
+    """FP8 activations x MXFP4 weights on the 2-CTA tile (slots / M of a multiple of 256 rows): against the
+    oracle and bit for bit against the single-CTA tile."""
+    def masked_run():
+        max_m, experts, n, k, masked = 256, 3, 512, 1024, [256, 100, 7]
+        xq, wq, sfa, sfb = _inputs_w4a8(hq, experts * max_m, experts, n, k)
+        out = torch.full([experts * max_m, n], 3.0, dtype=torch.bfloat16, device="cuda")
+        hq.group_masked_gemm(xq, wq, sfa, sfb, torch.tensor(masked, dtype=torch.int32).cuda(), out, None, None, max_m,
+                             -1, "w4a8-mxfp4")
+        ids = np.full(experts * max_m, -1, dtype=np.int64)
+        for e, cnt in enumerate(masked):
+            ids[e * max_m:e * max_m + cnt] = e
+        return out, (xq, wq, sfa, sfb), ids
+
+    def contiguous_run():
+        counts, n, k = [64, 192, 256, 128, 128], 512, 1024
+        ids = _spans(counts)
+        xq, wq, sfa, sfb = _inputs_w4a8(hq, ids.size, len(counts), n, k, seed=3)
+        out = torch.full([ids.size, n], float("nan"), dtype=torch.bfloat16, device="cuda")
+        hq.group_contiguous_gemm(xq, wq, sfa, sfb, torch.from_numpy(ids).cuda(), out, None, None, -1, "w4a8-mxfp4")
+        return out, (xq, wq, sfa, sfb), ids.astype(np.int64)
+
+    for run, kind, args in ((masked_run, "masked", (3, 256, 512, 1024)), (contiguous_run, "contiguous", (5, 153, 512, 1024))):
+        monkeypatch.setenv("HALOPS_B200_TILE", tile)
+        assert "pair=1" in hq.describe_group_tile(kind, *args, mode="w4a8-mxfp4", total_m=768)
+        out, ops, ids = run()
+        assert hq.device_status() == 0
+        ref = oracle.group_gemm_ref(*ops, ids, "w4a8-mxfp4")
+        _compare(out, ref, np.nonzero(ids >= 0)[0], "w4a4-mxfp4", None)
+        if kind == "masked":
+            assert torch.all(out.cpu()[torch.from_numpy(np.nonzero(ids < 0)[0])] == 3.0)
+        monkeypatch.setenv("HALOPS_B200_TILE", "128")
+        assert torch.equal(out, run()[0])
+
+
 def test_w4a8_rules(hq):
     """tests/test_group_masked_gemm.py:727-768."""
     experts, max_m, n, k = 2, 128, 256, 256
