@@ -320,7 +320,7 @@ int hq_selftest_bounded_wait(uint32_t limit_us, int device, void* stream,
  * n_local) of EVERY matrix: each staged 32 x 64 piece of a finished tile goes
  * out by one TMA store per matrix (rows of 128 bytes; the peers' over NVLink),
  * tile by tile, so the transfer overlaps the math.  Every load of the kernel
- * (operands, scales) is from this GPU's memory; none uses cluster multicast.
+ * (operands, scales) is from this GPU's memory.
  * The caller fences across ranks: nobody may still read a matrix
  * when the first rank starts, and a rank may read its matrix once every rank's
  * kernel has completed.  HQ_ERR_UNSUPPORTED unless n_local % 256 == 0,
