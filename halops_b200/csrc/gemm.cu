@@ -1949,6 +1949,7 @@ struct GemmArgs {
     int kq_dim;
     int sm_count;
     bool pdl;
+    bool early_weights = false;  // with pdl: b and sfb may be read before the preceding kernel completes
     bool direct_store;
     cudaStream_t stream;
 };
@@ -2264,6 +2265,7 @@ int launch_decode(const GemmArgs& g, char* err, size_t errlen) {
         return fail(err, errlen, HQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the GEMM operands");
     }
     p.sfw = g.sfb;
+    p.early_weights = g.pdl && g.early_weights ? 1 : 0;
     p.sfx = g.sfa;
     p.scratch = scratch.partials;
     p.counters = scratch.counters;
@@ -2350,6 +2352,7 @@ int launch_decode_noalloc(const GemmArgs& g, const DecPlan& plan, char* err, siz
         return fail(err, errlen, HQ_ERR_CUDA, "cuTensorMapEncodeTiled failed for the GEMM operands");
     }
     p.sfw = g.sfb;
+    p.early_weights = g.pdl && g.early_weights ? 1 : 0;
     p.sfx = g.sfa;
     p.scratch = scratch.partials;
     p.counters = scratch.counters;
@@ -2617,6 +2620,7 @@ int dense_gemm_impl(const void* a, const void* b, const void* sfa, const void* s
     g.kq_dim = int(sf_k / 4);
     g.sm_count = sm;
     g.pdl = use_pdl != 0;
+    g.early_weights = use_pdl == 2;
     {
         // test switch, read on every call: store every tile from registers
         const char* e = getenv("HALOPS_B200_EPILOGUE");

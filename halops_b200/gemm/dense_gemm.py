@@ -76,7 +76,10 @@ def dense_gemm(
             ``w4a4-mxfp4``, ignored for ``w8a8-mxfp8``.
         sm_count: SMs to use (-1: all).
         mode: ``"w8a8-mxfp8"``, ``"w4a4-mxfp4"`` or ``"w4a4-nvfp4"``.
-        use_pdl: launch with programmatic stream serialisation.
+        use_pdl: launch with programmatic stream serialisation.  ``2`` (not in the reference) adds the
+            promise that ``weight`` and ``sfb`` are not written by the kernel that precedes this call on
+            the stream; the small-M kernel then streams the weight of its first stages while that kernel
+            is still finishing (chains of decode GEMMs).
         bias: optional [N] bfloat16 vector, ``w8a8-mxfp8`` only, M a multiple of 256
             (the reference's rule).
         epilogue: what happens to ``y = alpha * input @ weight^T + bias`` before it is stored.
@@ -204,5 +207,5 @@ def dense_gemm(
         "hq_dense_gemm",
         input.data_ptr(), weight.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), output.data_ptr(), bias_ptr, alpha_ptr,
         m, n, k, sfa.numel(), sfb.numel(), output.stride(0) if m > 0 else max(n, 8),
-        _native.MODE_IDS[mode], int(epilogue), int(sm_count), int(bool(use_pdl)), dev, stream,
+        _native.MODE_IDS[mode], int(epilogue), int(sm_count), 2 if use_pdl == 2 else int(bool(use_pdl)), dev, stream,
     )

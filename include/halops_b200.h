@@ -119,6 +119,15 @@ int hq_rms_norm_quant(const void* input, int64_t ld_elems, const void* weight,
  *   alpha device pointer to one float: required for nvfp4, must be NULL for
  *         mxfp4, ignored for mxfp8 (csrc/kernel/gemm/dense_gemm.cu:126-164)
  *   sm_count <= 0 uses every SM of the device
+ *   use_pdl  0: plain launch.  1: programmatic stream serialisation, as the
+ *         reference's use_pdl: the kernel's set-up overlaps the tail of the
+ *         preceding kernel and nothing is read before that kernel is complete.
+ *         2 (no counterpart in the reference): the same, and the caller
+ *         vouches that `b` and `sfb` are not written by the preceding kernel
+ *         (a weight that was quantised at load time); the small-M kernel (MXFP8,
+ *         M <= 64) then asks for the weight of its first stages before it
+ *         waits for the preceding kernel, so a chain of decode GEMMs streams
+ *         its weights back to back.  Other kernels treat 2 as 1.
  * Rows of A past M are never read into the result and rows of out past M are
  * never written.
  */

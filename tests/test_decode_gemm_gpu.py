@@ -211,3 +211,33 @@ def test_one_row_of_64_wide_tiles_with_two_issuers(hq, monkeypatch, m, n, k, env
     sig = _run(hq, aq, bq, sfa, sfb, epilogue=hq.EpilogueOp.Sigmoid)
     ref = torch.sigmoid(oracle.dequantize(aq, sfa, "w8a8-mxfp8") @ oracle.dequantize(bq, sfb, "w8a8-mxfp8").T)
     torch.testing.assert_close(sig.float().cpu(), ref, rtol=2e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("m,n,k,deal", [(8, 7168, 2048, ""), (64, 4096, 8192, ""), (16, 1024, 8192, "split,nocluster"),
+                                        (1, 24576, 1536, ""), (32, 2048, 4096, "split")], ids=lambda v: str(v))
+def test_chain_with_early_weight_loads(hq, monkeypatch, m, n, k, deal):
+    """use_pdl=2: the weight of the first stages is asked for before the preceding kernel is known to be
+    complete.  A chain of GEMMs on different weights, each reading the activation that a kernel just
+    before it wrote, gives the bits of the plain launches."""
+    monkeypatch.setenv("HALOPS_B200_DECODE", deal)
+    g = torch.Generator().manual_seed(77 + m)
+    layers = 6
+    xs = [torch.randn([m, k], generator=g).to(torch.bfloat16).cuda() for _ in range(layers)]
+    ws = [hq.group_wise_quant((torch.randn([n, k], generator=g) * 0.05).to(torch.bfloat16).cuda()) for _ in range(layers)]
+    outs = {}
+    xq = [torch.empty([m, k], dtype=torch.float8_e4m3fn, device="cuda") for _ in range(layers)]
+    sfa = [torch.empty([128, k // 32], dtype=torch.uint8, device="cuda") for _ in range(layers)]
+    for use_pdl in (0, 1, 2):
+        res = [torch.full([m, n], 9.0, dtype=torch.bfloat16, device="cuda") for _ in range(layers)]
+        torch.cuda.synchronize()
+        for _ in range(3):  # a few rounds: the scratch memory and the tile counters are reused
+            for i in range(layers):
+                # only this library's kernels on the stream: the quantizer writes the activation that the
+                # GEMM right behind it reads, and the next quantizer follows that GEMM
+                hq.group_wise_quant(xs[i], "w8a8-mxfp8", True, bool(use_pdl), xq[i], sfa[i])
+                hq.dense_gemm(xq[i], ws[i][0], sfa[i], ws[i][1], res[i], None, None, -1, "w8a8-mxfp8", use_pdl)
+        torch.cuda.synchronize()
+        assert hq.device_status() == 0
+        outs[use_pdl] = res
+    for i in range(layers):
+        assert torch.equal(outs[0][i], outs[1][i]) and torch.equal(outs[0][i], outs[2][i]), f"GEMM {i} of the chain differs"
