@@ -85,6 +85,11 @@ def _worker(rank, world, port, ret):
         staged = layer.gathered(x2q, sfa2, blocks=8)
         ok = ok and list(staged.shape) == [2, world, 256, rows]
         ok = ok and bool(torch.equal(layer.gathered_as_matrix(staged), oracle.dense_gemm_ref(x2q, wq, sfa2, sfb, "w8a8-mxfp8")))
+        # the GEMM that gathers in its epilogue applies to this shard from 129 rows on, but only on a
+        # GPU: here the overlapped call takes the block-wise path and gives the same matrix
+        ok = ok and layer.fused_supported(512) and not layer.fused_supported(64)
+        ok = ok and bool(torch.equal(layer(x2, gather=True, overlap=True),
+                                     oracle.dense_gemm_ref(x2q, wq, sfa2, sfb, "w8a8-mxfp8")))
         ret[rank] = ok
     finally:
         dist.destroy_process_group()
