@@ -10,6 +10,7 @@ import threading
 _LIB_PATH = os.environ.get("HALOPS_B200_LIB") or os.path.join(
     os.path.dirname(os.path.abspath(__file__)), "lib", "libhalops_b200.so")
 _lock = threading.Lock()
+_tls = threading.local()
 _lib = None
 
 MODE_IDS = {"w8a8-mxfp8": 0, "w4a4-mxfp4": 1, "w4a4-nvfp4": 2}
@@ -90,7 +91,21 @@ def lib() -> ctypes.CDLL:
 def call(name: str, *args) -> None:
     """Calls an entry point whose last two parameters are (err, errlen) and
     raises RuntimeError with the library's message on a non-zero return."""
-    err = ctypes.create_string_buffer(512)
-    rc = getattr(lib(), name)(*args, err, len(err))
+    err = getattr(_tls, "err", None)
+    if err is None:
+        err = _tls.err = ctypes.create_string_buffer(512)  # one per thread: entry points are re-entrant
+    rc = getattr(lib(), name)(*args, err, 512)
     if rc != 0:
         raise RuntimeError(err.value.decode("utf-8", "replace") or f"{name} failed with code {rc}")
+
+
+def current_stream(device) -> int:
+    """Handle of torch's current CUDA stream on ``device`` (a ``torch.device`` with an index).
+    ``torch.cuda.current_stream`` builds a Stream object for this, which costs the host several
+    microseconds per call; torch's raw getter does not."""
+    import torch
+
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is not None and device.index is not None:
+        return raw(device.index)
+    return torch.cuda.current_stream(device).cuda_stream

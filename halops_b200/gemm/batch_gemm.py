@@ -137,7 +137,7 @@ def batch_gemm(
             input.data_ptr(), weight.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), output.data_ptr(),
             output_sf.data_ptr(), gate_ptr, gate_ld, bias_ptr, batches, m, n, k, sfa.numel(), sfb.numel(),
             output.stride(0), output_sf.numel(), int(epilogue), int(sm_count), int(bool(use_pdl)),
-            input.device.index, torch.cuda.current_stream(input.device).cuda_stream,
+            input.device.index, _native.current_stream(input.device),
         )
         return
     _check(output_sf is None and gate is None, "output_sf and gate belong to the quantising epilogues")
@@ -167,5 +167,5 @@ def batch_gemm(
         input.data_ptr(), weight.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), output.data_ptr(), bias_ptr, alpha_ptr,
         batches, m, n, k, sfa.numel(), sfb.numel(), output.stride(0),
         _native.MODE_IDS[mode], int(epilogue), int(sm_count), int(bool(use_pdl)), input.device.index,
-        torch.cuda.current_stream(input.device).cuda_stream,
+        _native.current_stream(input.device),
     )

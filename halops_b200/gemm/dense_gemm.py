@@ -43,6 +43,10 @@ def interleave_gate_up(t: torch.Tensor) -> torch.Tensor:
     return blocks.transpose(0, 1).reshape(t.shape)
 
 
+# dense shapes that hq_describe_tile has accepted (the check does not depend on the device)
+_LEGAL_SHAPES: set = set()
+
+
 def _check(cond: bool, msg: str) -> None:
     if not cond:
         raise RuntimeError(msg)
@@ -97,70 +101,62 @@ def dense_gemm(
         output_sf: SfAtom scales of the quantised output ([ceil(M/128)*128, N/64] uint8).
         situ_beta / situ_linear_beta: gate and up soft-caps.
     """
-    _check(
-        mode in _native.MODE_IDS,
-        f"Unsupported mode: {mode}. Expected 'w8a8-mxfp8', 'w4a4-mxfp4' or 'w4a4-nvfp4'.",
-    )
-    _check(input.dim() == 2, "input must be a 2D tensor of shape [M, K]")
-    _check(weight.dim() == 2, "weight must be a 2D tensor of shape [N, K]")
-    _check(output.dim() == 2, "output must be a 2D tensor of shape [M, N]")
+    # (the messages are only built when a check fails: this function runs once per GEMM of a
+    # decode step, where the host's time per call is what the step costs)
+    if mode not in _native.MODE_IDS:
+        raise RuntimeError(f"Unsupported mode: {mode}. Expected 'w8a8-mxfp8', 'w4a4-mxfp4' or 'w4a4-nvfp4'.")
+    if input.dim() != 2:
+        raise RuntimeError("input must be a 2D tensor of shape [M, K]")
+    if weight.dim() != 2:
+        raise RuntimeError("weight must be a 2D tensor of shape [N, K]")
+    if output.dim() != 2:
+        raise RuntimeError("output must be a 2D tensor of shape [M, N]")
     epilogue = EpilogueOp(int(epilogue))
-    m, n = input.size(0), weight.size(0)
+    m, in_k = input.shape
+    n, w_k = weight.shape
+    out_m, out_cols = output.shape
     out_n = n // 2 if epilogue == EpilogueOp.SituQuant else n
-    _check(
-        output.size(0) == m and output.size(1) == out_n,
-        f"output shape must be [{m}, {out_n}], got [{output.size(0)}, {output.size(1)}]",
-    )
+    if out_m != m or out_cols != out_n:
+        raise RuntimeError(f"output shape must be [{m}, {out_n}], got [{out_m}, {out_cols}]")
     m_sf = (m + 127) // 128 * 128
     fp8 = mode == "w8a8-mxfp8"
     if fp8:
-        k = weight.size(1)
-        _check(input.size(1) == k, f"input K must match weight K, got input K={input.size(1)}, weight K={k}")
-        _check(sfb.dtype == torch.uint8,
-               "sfb must be the uint8 SfAtom weight scale that group_wise_quant returns")
+        k = w_k
+        if in_k != k:
+            raise RuntimeError(f"input K must match weight K, got input K={in_k}, weight K={k}")
+        if sfb.dtype != torch.uint8:
+            raise RuntimeError("sfb must be the uint8 SfAtom weight scale that group_wise_quant returns")
         sf_k = k // 32
-        _check(
-            sfa.is_contiguous() and sfa.numel() >= m_sf * sf_k,
-            f"sfa must hold whole 128-row SfAtoms: expected at least {m_sf * sf_k} elements "
-            f"({m_sf} x {sf_k}) for M={m}, got {sfa.numel()}",
-        )
-        if bias is not None and epilogue != EpilogueOp.SituQuant:
-            _check(
-                m % 256 == 0,
-                "the bias tile has no per-row store predicate yet, so M must be a multiple of 256 "
-                f"when bias is given, got {m}",
-            )
+        if not (sfa.is_contiguous() and sfa.numel() >= m_sf * sf_k):
+            raise RuntimeError(f"sfa must hold whole 128-row SfAtoms: expected at least {m_sf * sf_k} elements "
+                               f"({m_sf} x {sf_k}) for M={m}, got {sfa.numel()}")
+        if bias is not None and epilogue != EpilogueOp.SituQuant and m % 256 != 0:
+            raise RuntimeError("the bias tile has no per-row store predicate yet, so M must be a multiple of 256 "
+                               f"when bias is given, got {m}")
     else:
-        k = weight.size(1) * 2
-        _check(
-            input.size(1) == weight.size(1),
-            f"packed input K/2 must match packed weight K/2, got input K/2={input.size(1)}, "
-            f"weight K/2={weight.size(1)}",
-        )
-        _check(bias is None, "W4A4 mode does not support bias yet.")
+        k = w_k * 2
+        if in_k != w_k:
+            raise RuntimeError(f"packed input K/2 must match packed weight K/2, got input K/2={in_k}, "
+                               f"weight K/2={w_k}")
+        if bias is not None:
+            raise RuntimeError("W4A4 mode does not support bias yet.")
         mxfp4 = mode == "w4a4-mxfp4"
-        _check(
-            not mxfp4 or alpha is None,
-            "'w4a4-mxfp4' does not take alpha; the global scaling factor is only used by 'w4a4-nvfp4'.",
-        )
+        if mxfp4 and alpha is not None:
+            raise RuntimeError(
+                "'w4a4-mxfp4' does not take alpha; the global scaling factor is only used by 'w4a4-nvfp4'.")
         sf_k = k // (32 if mxfp4 else 16)
-        _check(
-            sfa.size(-1) == sf_k and sfb.size(-1) == sf_k,
-            "W4A4 scale-factor shape does not match mode "
-            + ("'w4a4-mxfp4' (UE8M0 per 32)" if mxfp4 else "'w4a4-nvfp4' (UE4M3 per 16)")
-            + f" requires SF K = {sf_k}, got sfa K={sfa.size(-1)} and sfb K={sfb.size(-1)}.",
-        )
-        _check(
-            sfa.is_contiguous() and sfa.numel() >= m_sf * sf_k,
-            f"sfa must hold whole 128-row SfAtoms: expected at least {m_sf * sf_k} elements "
-            f"({m_sf} x {sf_k}) for M={m}, got {sfa.numel()}",
-        )
-        if not mxfp4:
-            _check(alpha is not None, "W4A4-nvfp4 mode requires alpha input (per-batch scaling).")
-    _check(
-        epilogue in (EpilogueOp.Identity, EpilogueOp.Sigmoid) or (epilogue == EpilogueOp.SituQuant and fp8),
-        f"Unsupported epilogue {int(epilogue)} for {mode}",
-    )
+        if sfa.size(-1) != sf_k or sfb.size(-1) != sf_k:
+            raise RuntimeError(
+                "W4A4 scale-factor shape does not match mode "
+                + ("'w4a4-mxfp4' (UE8M0 per 32)" if mxfp4 else "'w4a4-nvfp4' (UE4M3 per 16)")
+                + f" requires SF K = {sf_k}, got sfa K={sfa.size(-1)} and sfb K={sfb.size(-1)}.")
+        if not (sfa.is_contiguous() and sfa.numel() >= m_sf * sf_k):
+            raise RuntimeError(f"sfa must hold whole 128-row SfAtoms: expected at least {m_sf * sf_k} elements "
+                               f"({m_sf} x {sf_k}) for M={m}, got {sfa.numel()}")
+        if not mxfp4 and alpha is None:
+            raise RuntimeError("W4A4-nvfp4 mode requires alpha input (per-batch scaling).")
+    if not (epilogue in (EpilogueOp.Identity, EpilogueOp.Sigmoid) or (epilogue == EpilogueOp.SituQuant and fp8)):
+        raise RuntimeError(f"Unsupported epilogue {int(epilogue)} for {mode}")
     bias_ptr = None
     if bias is not None:
         _check(bias.dtype == torch.bfloat16 and bias.dim() == 1 and bias.numel() == n and bias.is_contiguous(),
@@ -184,16 +180,18 @@ def dense_gemm(
             input.data_ptr(), weight.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), output.data_ptr(),
             output_sf.data_ptr(), bias_ptr, m, n, k, sfa.numel(), sfb.numel(), output_sf.numel(),
             float(situ_beta), 0.0 if situ_linear_beta is None else float(situ_linear_beta), int(sm_count),
-            int(bool(use_pdl)), input.device.index, torch.cuda.current_stream(input.device).cuda_stream,
+            int(bool(use_pdl)), input.device.index, _native.current_stream(input.device),
         )
         return
     _check(output.dtype == torch.bfloat16, "output must be a bfloat16 tensor")
     _check(input.is_contiguous() and weight.is_contiguous() and sfb.is_contiguous(),
            "input, weight and sfb must be contiguous")
     _check(output.stride(1) == 1, "output rows must be contiguous")
-    if m > 0 and n > 0:
+    if m > 0 and n > 0 and (m, n, k, mode) not in _LEGAL_SHAPES:
         # shape legality ("No dense ... tile") is reported before anything touches a device
         _native.call("hq_describe_tile", m, n, k, _native.MODE_IDS[mode], 148, -1)
+        if len(_LEGAL_SHAPES) < 4096:
+            _LEGAL_SHAPES.add((m, n, k, mode))
     alpha_ptr = None
     if alpha is not None and not fp8:
         _check(alpha.is_cuda and alpha.dtype == torch.float32 and alpha.numel() >= 1,
@@ -202,7 +200,7 @@ def dense_gemm(
     for name, t in (("input", input), ("weight", weight), ("sfa", sfa), ("sfb", sfb), ("output", output)):
         _check(t.is_cuda, f"{name} must be a CUDA tensor (this library has no CPU path)")
     dev = input.device.index
-    stream = torch.cuda.current_stream(input.device).cuda_stream
+    stream = _native.current_stream(input.device)
     _native.call(
         "hq_dense_gemm",
         input.data_ptr(), weight.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), output.data_ptr(), bias_ptr, alpha_ptr,

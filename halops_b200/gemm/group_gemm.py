@@ -145,7 +145,7 @@ def group_masked_gemm(
         input.data_ptr(), weight.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), masked_m.data_ptr(), output.data_ptr(),
         bias_ptr, alpha_ptr, num_experts, max_m_per_expert, n, k, sfa.numel(), sfb.numel(), output.stride(0),
         _MODE_IDS[mode], int(sm_count), 1, input.device.index,
-        torch.cuda.current_stream(input.device).cuda_stream,
+        _native.current_stream(input.device),
     )
 
 
@@ -204,5 +204,5 @@ def group_contiguous_gemm(
         input.data_ptr(), weight.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), expert_ids.data_ptr(),
         output.data_ptr(), bias_ptr, alpha_ptr, num_experts, m, n, k, sfa.numel(), sfb.numel(), output.stride(0),
         _MODE_IDS[mode], int(sm_count), 1, input.device.index,
-        torch.cuda.current_stream(input.device).cuda_stream,
+        _native.current_stream(input.device),
     )

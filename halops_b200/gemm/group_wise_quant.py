@@ -47,49 +47,40 @@ def group_wise_quant(
         ``(output_quant, output_sf)``: [m, k] float8_e4m3fn or [m, k/2] uint8,
         and [ceil(m/128)*128 or m, k / group] uint8.
     """
-    _check(input.dim() == 2, "input must be a 2D tensor of shape [m, k]")
-    _check(input.dtype in _DTYPE_IDS, "input dtype must be bfloat16 or float16")
-    _check(
-        input.stride(1) == 1 and (input.stride(0) * 2) % 16 == 0 and input.data_ptr() % 16 == 0,
-        "input rows must be contiguous and 16-byte aligned",
-    )
-    _check(
-        mode in _native.MODE_IDS,
-        f"Unsupported quantization mode: {mode}. Expected 'w8a8-mxfp8', 'w4a4-mxfp4' or 'w4a4-nvfp4'.",
-    )
+    # (the messages are only built when a check fails: this runs once per activation of a decode step)
+    if input.dim() != 2:
+        raise RuntimeError("input must be a 2D tensor of shape [m, k]")
+    if input.dtype not in _DTYPE_IDS:
+        raise RuntimeError("input dtype must be bfloat16 or float16")
+    if not (input.stride(1) == 1 and (input.stride(0) * 2) % 16 == 0 and input.data_ptr() % 16 == 0):
+        raise RuntimeError("input rows must be contiguous and 16-byte aligned")
+    if mode not in _native.MODE_IDS:
+        raise RuntimeError(
+            f"Unsupported quantization mode: {mode}. Expected 'w8a8-mxfp8', 'w4a4-mxfp4' or 'w4a4-nvfp4'.")
     group = _native.GROUP_SIZE[mode]
     m, k = input.shape
     kb_dim = k // group
-    _check(
-        k % group == 0,
-        f"k must be divisible by the quantization group size ({group}) for mode {mode}, got k={k}",
-    )
-    if use_swizzle:
-        _check(
-            kb_dim % 4 == 0,
-            f"scale kb_dim must be divisible by 4 for CUTLASS SfAtom layout, got {kb_dim}",
-        )
+    if k % group != 0:
+        raise RuntimeError(f"k must be divisible by the quantization group size ({group}) for mode {mode}, got k={k}")
+    if use_swizzle and kb_dim % 4 != 0:
+        raise RuntimeError(f"scale kb_dim must be divisible by 4 for CUTLASS SfAtom layout, got {kb_dim}")
     m_sf = (m + 127) // 128 * 128 if use_swizzle else m
     fp4 = mode != "w8a8-mxfp8"
     quant_dtype = torch.uint8 if fp4 else torch.float8_e4m3fn
     quant_k = k // 2 if fp4 else k
     if output_quant is None:
         output_quant = torch.empty([m, quant_k], dtype=quant_dtype, device=input.device)
+    elif not (output_quant.is_contiguous() and output_quant.dtype == quant_dtype
+              and output_quant.numel() == m * quant_k and output_quant.device == input.device):
+        raise RuntimeError(f"output_quant must be a contiguous [{m}, {quant_k}] tensor of the mode's dtype")
     if output_sf is None:
         output_sf = torch.empty([m_sf, kb_dim], dtype=torch.uint8, device=input.device)
-    _check(
-        output_quant.is_contiguous() and output_quant.dtype == quant_dtype
-        and output_quant.numel() == m * quant_k and output_quant.device == input.device,
-        f"output_quant must be a contiguous [{m}, {quant_k}] tensor of the mode's dtype",
-    )
-    _check(
-        output_sf.is_contiguous() and output_sf.dtype == torch.uint8
-        and output_sf.numel() == m_sf * kb_dim and output_sf.device == input.device,
-        f"output_sf must be a contiguous uint8 tensor of {m_sf} x {kb_dim} elements",
-    )
+    elif not (output_sf.is_contiguous() and output_sf.dtype == torch.uint8
+              and output_sf.numel() == m_sf * kb_dim and output_sf.device == input.device):
+        raise RuntimeError(f"output_sf must be a contiguous uint8 tensor of {m_sf} x {kb_dim} elements")
     _check(input.is_cuda, "input must be a CUDA tensor (this library has no CPU path)")
     dev = input.device.index
-    stream = torch.cuda.current_stream(input.device).cuda_stream
+    stream = _native.current_stream(input.device)
     _native.call(
         "hq_group_wise_quant",
         input.data_ptr(), input.stride(0), _DTYPE_IDS[input.dtype], m, k, _native.MODE_IDS[mode],

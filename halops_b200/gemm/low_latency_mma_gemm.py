@@ -122,5 +122,5 @@ def low_latency_mma_gemm(
         0 if sfa2 is None else sfa2.stride(0), 0 if sfb2 is None else sfb2.stride(0),
         output.stride(0) if m > 0 else max(n, 8), 0 if output2 is None else output2.stride(0),
         int(bool(use_sigmoid)), int(sm_count), int(bool(use_pdl)), input.device.index,
-        torch.cuda.current_stream(input.device).cuda_stream,
+        _native.current_stream(input.device),
     )

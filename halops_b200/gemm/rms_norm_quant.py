@@ -63,6 +63,6 @@ def rms_norm_quant(
         "hq_rms_norm_quant",
         input.data_ptr(), input.stride(0), weight.data_ptr(), float(eps), m, k, int(bool(use_swizzle)),
         int(bool(use_pdl)), q.data_ptr(), sf.data_ptr(), input.device.index,
-        torch.cuda.current_stream(input.device).cuda_stream,
+        _native.current_stream(input.device),
     )
     return q, sf
