@@ -15,9 +15,10 @@ from .. import _native
 __all__ = ["low_latency_mma_gemm"]
 
 
-def _check(cond: bool, msg: str) -> None:
+def _check(cond: bool, msg) -> None:
+    """``msg``: the text, or a callable that builds it (only called when the check fails)."""
     if not cond:
-        raise RuntimeError(msg)
+        raise RuntimeError(msg() if callable(msg) else msg)
 
 
 def _scale_ok(scale: torch.Tensor, rows: int) -> bool:
@@ -71,24 +72,24 @@ def low_latency_mma_gemm(
     n2 = weight2.size(0) if output2 is not None else 0
     k1 = weight.size(1)
     k = k1 + (weight2.size(1) if input2 is not None else 0)
-    _check(m <= 16, f"low_latency_mma_gemm supports M <= 16, got M={m}")
+    _check(m <= 16, lambda: f"low_latency_mma_gemm supports M <= 16, got M={m}")
     _check(n % 8 == 0 and n2 % 8 == 0,
-           f"low_latency_mma_gemm weight rows must be divisible by 8, got {n} and {n2}")
-    _check(k % 256 == 0, f"low_latency_mma_gemm K must be divisible by 256, got K={k}")
+           lambda: f"low_latency_mma_gemm weight rows must be divisible by 8, got {n} and {n2}")
+    _check(k % 256 == 0, lambda: f"low_latency_mma_gemm K must be divisible by 256, got K={k}")
     _check(input2 is None or input.size(1) % 512 == 0,
-           f"concat-K K1 must be a multiple of 512, got K1={input.size(1)}")
+           lambda: f"concat-K K1 must be a multiple of 512, got K1={input.size(1)}")
     _check(
         _scale_ok(sfa, m) and _scale_ok(sfb, n) and (sfa2 is None or _scale_ok(sfa2, m))
         and (sfb2 is None or _scale_ok(sfb2, weight2.size(0))),
-        "sfa / sfb / sfa2 / sfb2 must be plain row-major [rows, K / 32] scales "
+        lambda: "sfa / sfb / sfa2 / sfb2 must be plain row-major [rows, K / 32] scales "
         "(group_wise_quant(..., use_swizzle=False)) with a row stride that is a multiple of 16 bytes; got sfa "
         f"{list(sfa.shape)} strides {list(sfa.stride())}, sfb {list(sfb.shape)} strides {list(sfb.stride())}",
     )
     _check(not use_sigmoid or weight2 is None, "low_latency_mma_gemm use_sigmoid does not support input2 or output2")
     _check(input.size(1) == k1 and sfa.size(1) == k1 // 32 and sfb.size(1) == k1 // 32,
-           f"input K must match weight K, got input K={input.size(1)}, weight K={k1}")
+           lambda: f"input K must match weight K, got input K={input.size(1)}, weight K={k1}")
     _check(output.size(0) == m and output.size(1) == n and output.dtype == torch.bfloat16 and output.stride(1) == 1,
-           f"output must be a bfloat16 [{m}, {n}] tensor with contiguous rows")
+           lambda: f"output must be a bfloat16 [{m}, {n}] tensor with contiguous rows")
     tensors = [("input", input), ("weight", weight), ("sfa", sfa), ("sfb", sfb), ("output", output)]
     if input2 is not None:
         _check(input2.dim() == 2 and input2.size(0) == m and weight2.dim() == 2 and weight2.size(0) == n
@@ -101,15 +102,15 @@ def low_latency_mma_gemm(
                "weight2 [N2, K1] and sfb2 [N2, K1 / 32] must match input's K")
         _check(output2.dim() == 2 and output2.size(0) == m and output2.size(1) == n2
                and output2.dtype == torch.bfloat16 and output2.stride(1) == 1,
-               f"output2 must be a bfloat16 [{m}, {n2}] tensor with contiguous rows")
+               lambda: f"output2 must be a bfloat16 [{m}, {n2}] tensor with contiguous rows")
         tensors += [("output2", output2)]
     if weight2 is not None:
         tensors += [("weight2", weight2), ("sfb2", sfb2)]
     for name, t in tensors:
-        _check(t.is_cuda, f"{name} must be a CUDA tensor (this library has no CPU path)")
+        _check(t.is_cuda, lambda: f"{name} must be a CUDA tensor (this library has no CPU path)")
     for name, t in tensors:
         if name in ("input", "weight", "input2", "weight2"):
-            _check(t.is_contiguous(), f"{name} must be contiguous")
+            _check(t.is_contiguous(), lambda: f"{name} must be contiguous")
 
     def ptr(t):
         return None if t is None else t.data_ptr()

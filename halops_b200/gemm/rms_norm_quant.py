@@ -50,7 +50,8 @@ def rms_norm_quant(
         input.stride(1) == 1 and (input.stride(0) * 2) % 16 == 0 and input.data_ptr() % 16 == 0,
         "input rows must be contiguous and 16-byte aligned",
     )
-    _check(k % 128 == 0 and 0 < k <= 8192, f"K must be a multiple of 128 and at most 8192, got {k}")
+    if not (k % 128 == 0 and 0 < k <= 8192):
+        raise RuntimeError(f"K must be a multiple of 128 and at most 8192, got {k}")
     _check(
         weight.dim() == 1 and weight.size(0) == k and weight.dtype == torch.bfloat16 and weight.is_contiguous(),
         "weight must be a contiguous bfloat16 [K] tensor",
