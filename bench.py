@@ -915,10 +915,33 @@ def run_sweep_low_latency(tm, dev, peaks):
     assert hq.device_status(dev) == 0
 
 
+def _graph_time_us(chain):
+    """Median time of one replay of `chain` captured into a CUDA graph (programmatic launches become
+    programmatic edges).  One call from Python costs the host about 10 us, more than a decode kernel runs."""
+    for _ in range(3):
+        chain()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        chain()
+    graph.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(20):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e) * 1e3)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
 def run_sweep_decode_chain(dev, peaks):
-    """Decode GEMMs back to back in a CUDA graph, every one on its own weight (the set is larger than L2):
-    time per GEMM with plain launches, with programmatic launches, and with programmatic launches that
-    may read the weight early (use_pdl = 0, 1, 2)."""
+    """Decode GEMMs back to back in a CUDA graph, every one on its own weight (the set is larger than L2),
+    alone and with the activation's quantizer before every GEMM: time per GEMM with plain launches, with
+    programmatic launches, and with programmatic launches that may read the weight early (use_pdl = 0, 1, 2)."""
     import halops_b200 as hq
 
     for m, n, k, layers in ((8, 7168, 2048, 16), (8, 24576, 1536, 8), (64, 7168, 2048, 16)):
@@ -928,37 +951,26 @@ def run_sweep_decode_chain(dev, peaks):
         ws = [hq.group_wise_quant((torch.randn([n, k], generator=g, device=dev) * 0.05).to(torch.bfloat16))
               for _ in range(layers)]
         outs = [torch.empty([m, n], dtype=torch.bfloat16, device=dev) for _ in range(layers)]
-        row = {"config": "decode chain", "m": m, "n": n, "k": k, "gemms": layers,
-               "weights_mb": round(layers * n * k * (1 + 1 / 32) / 1e6, 1)}
-        for use_pdl in (0, 1, 2):
-            def chain():
-                for i in range(layers):
-                    hq.dense_gemm(xq, ws[i][0], sfa, ws[i][1], outs[i], None, None, -1, MODE, use_pdl)
+        xqs = [torch.empty_like(xq) for _ in range(layers)]
+        sfas = [torch.empty_like(sfa) for _ in range(layers)]
+        for with_quant in (False, True):
+            row = {"config": "decode chain" + (", quantizer before every GEMM" if with_quant else ""),
+                   "m": m, "n": n, "k": k, "gemms": layers,
+                   "weights_mb": round(layers * n * k * (1 + 1 / 32) / 1e6, 1)}
+            for use_pdl in (0, 1, 2):
+                def chain():
+                    for i in range(layers):
+                        if with_quant:
+                            hq.group_wise_quant(x, MODE, True, use_pdl != 0, xqs[i], sfas[i])
+                            hq.dense_gemm(xqs[i], ws[i][0], sfas[i], ws[i][1], outs[i], None, None, -1, MODE, use_pdl)
+                        else:
+                            hq.dense_gemm(xq, ws[i][0], sfa, ws[i][1], outs[i], None, None, -1, MODE, use_pdl)
 
-            for _ in range(3):
-                chain()
-            torch.cuda.synchronize()
-            # one call from Python costs the host about 20 us, more than the kernel runs: the chain is
-            # captured into a CUDA graph (programmatic launches become programmatic edges) and replayed
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                chain()
-            graph.replay()
-            torch.cuda.synchronize()
-            ts = []
-            for _ in range(20):
-                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                s.record()
-                graph.replay()
-                e.record()
-                torch.cuda.synchronize()
-                ts.append(s.elapsed_time(e) * 1e3 / layers)
-            ts.sort()
-            us = ts[len(ts) // 2]
-            row[f"us_per_gemm_pdl{use_pdl}"] = round(us, 2)
-            row[f"frac_of_hbm_pdl{use_pdl}"] = round(n * k * (1 + 1 / 32) / us / 1e3 / peaks["hbm_gbs"], 3)
-        assert hq.device_status(dev) == 0
-        print(json.dumps(row), flush=True)
+                us = _graph_time_us(chain) / layers
+                row[f"us_per_gemm_pdl{use_pdl}"] = round(us, 2)
+                row[f"frac_of_hbm_pdl{use_pdl}"] = round(n * k * (1 + 1 / 32) / us / 1e3 / peaks["hbm_gbs"], 3)
+            assert hq.device_status(dev) == 0
+            print(json.dumps(row), flush=True)
 
 
 def run_shape(args):

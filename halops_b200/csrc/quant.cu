@@ -507,9 +507,12 @@ group_wise_quant_kernel(const T* __restrict__ input, int64_t ld,
     }
 
     // The first global access is below: with a programmatic launch the index
-    // math above overlaps the tail of the producing kernel.
-    pdl_wait();
+    // math above overlaps the tail of the producing kernel.  The kernel behind this one may
+    // start its own set-up at once (it still waits for this whole grid before it reads
+    // anything): a decode GEMM then has its prologue, and with early weight loads its first
+    // stages, behind it when the few CTAs of an activation's quantizer are done.
     pdl_launch_dependents();
+    pdl_wait();
 
     if (row >= rows_total) return;
 
@@ -575,8 +578,8 @@ rms_norm_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t ld,
         gw[p] = col < k ? __ldg(reinterpret_cast<const uint4*>(gamma + col)) : make_uint4(0, 0, 0, 0);
     }
 
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
 
     if (row >= m) {  // padding rows of the last SfAtom (swizzled layout only)
         if constexpr (kSwizzle) {
