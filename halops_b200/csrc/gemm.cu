@@ -437,7 +437,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     // Two MMA issuers with an accumulator each (64-wide dense tiles, plain epilogues): the k-tiles
     // of a tile are summed as (even ones) + (odd ones), deterministically, but not in the k order
     // of the other tiles.
-    const bool dual = BN == 64 && !kSplitK && dual_issue != 0;
+    const bool dual = BN == 64 && !kSplitK && dual_issue == 1;
+    // dual_issue == 2: two issuers as well, but into ONE accumulator and in k order, as in the
+    // 2-CTA kernel: the threads take alternate k-iterations and hand each other the turn (tcgen05
+    // fences around an mbarrier arrival), so the MMAs reach the tensor core in the order one thread
+    // would issue them and the bits do not change.  What it buys is issue time: 4 MMAs and the
+    // commit that releases the stage keep one thread busy for longer than a narrow tile's MMAs run.
+    const bool ordered = !kSplitK && dual_issue == 2;
     static_assert(!kSplitK || (BN == 64 && 2 * C::kABytes == kBM * BN * 4 && C::kStages >= 6), "split-K buffer");
     // stages of the ring; with split-K the last two A stages hold the partial sums received
     constexpr uint32_t kRing = kSplitK ? C::kStages - 2 : C::kStages;
@@ -471,7 +477,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);
         }
         for (int s = 0; s < 2; ++s) {
-            ptx::mbar_init(ptx::smem_u32(&bars->acc_full[s]), dual ? 2 : 1);  // one commit per MMA issuer
+            ptx::mbar_init(ptx::smem_u32(&bars->acc_full[s]), (dual || ordered) ? 2 : 1);  // one commit per MMA issuer
+            ptx::mbar_init(ptx::smem_u32(&bars->turn[s]), 1);
             ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[s]), kEpiWarps);
             ptx::mbar_init(ptx::smem_u32(&bars->overlap_free[s]), kEpiWarps);
         }
@@ -542,7 +549,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     } else if (warp == 1 || warp == 10) {
         // ------------------------------------------------------------ MMA issuer(s)
         const int me = warp == 1 ? 0 : 1;
-        if (lane == 0 && (me == 0 || dual)) {
+        if (lane == 0 && (me == 0 || dual || ordered)) {
             uint32_t it = 0;
             uint32_t t = 0;
             bool ok = true;
@@ -562,12 +569,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     if (!ok) break;
                 }
                 ptx::tc_fence_after();
-                const uint32_t acc = tmem + (me == 0 ? as * C::kAccStride : C::kDualCol + as * BN);
+                const uint32_t acc = tmem + ((me == 0 || ordered) ? as * C::kAccStride : C::kDualCol + as * BN);
                 // a 64-wide tile uses half of a 128-row scale atom
                 const uint32_t sfb_shift = BN == 64 ? uint32_t(wk.sfb_shift) : 0u;
                 bool issued = false;
                 for (int kt = k_begin; kt < k_end; ++kt, ++it) {
                     if (dual && ((kt - k_begin) & 1) != me) continue;
+                    if (ordered && int(it & 1u) != me) continue;
                     const uint32_t s = it % kRing;
                     const uint32_t ph = (it / kRing) & 1u;
                     // the scales of this k-tile are in their set (the scale warps waited for the
@@ -575,6 +583,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     ok = wait_bar(ptx::smem_u32(&bars->sf_ready[it % C::kSfSets]), (it / C::kSfSets) & 1u, abort,
                                   kStatusMma) &&
                          wait_bar(ptx::smem_u32(&bars->full[s]), ph, abort, kStatusMma);
+                    // (in-order pair of issuers) the other thread has issued the MMAs of the previous k-iteration
+                    if (ok && ordered && it > 0u) {
+                        ok = wait_bar(ptx::smem_u32(&bars->turn[me]), ((it - 1u) >> 1) & 1u, abort, kStatusMma);
+                    }
                     if (!ok) break;
                     ptx::tc_fence_after();
                     const uint32_t set = tmem + (it % C::kSfSets) * C::kSfCols;
@@ -598,9 +610,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             acc, adesc + uint64_t(k * 2), bdesc + uint64_t(k * 2),
                             instr_desc<BN, KIND>(sf_id), set + C::kSfaCol + atom * 4,
                             set + C::kSfbCol + atom * C::kNAtoms * 4 + sfb_shift,
-                            (issued || k > 0) ? 1u : 0u);
+                            (ordered ? (kt > k_begin || k > 0) : (issued || k > 0)) ? 1u : 0u);
                     }
                     issued = true;
+                    if (ordered) {
+                        // hand the turn over before the (slow) commit
+                        ptx::tc_fence_before();
+                        ptx::mbar_arrive(ptx::smem_u32(&bars->turn[me ^ 1]));
+                    }
                     // stage s may be refilled once these MMAs have read it
                     ptx::tc_commit(ptx::smem_u32(&bars->empty[s]));
                 }
@@ -2026,13 +2043,19 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
         }
     }
     // One row of 64-wide dense tiles with a plain epilogue (65 to 128 activation rows, or fewer
-    // when the small-M kernel is not taken): two MMA issuers (see the kernel).  Problems with
-    // several rows of tiles keep one issuer, so that every tile shape sums the k-tiles of an
-    // output element in the same order and gives the same bits.
-    const int dual = BN == 64 && g.grp.kind == kGroupDense && tiles_m == 1 && k_tiles >= 2 &&
-                             (g.epi_op == HQ_EPILOGUE_IDENTITY || g.epi_op == HQ_EPILOGUE_SIGMOID)
-                         ? 1
-                         : 0;
+    // when the small-M kernel is not taken): two MMA issuers with an accumulator each (see the
+    // kernel).  Problems with several rows of tiles never take that mode, so that every tile
+    // shape sums the k-tiles of an output element in the same order and gives the same bits.
+    int dual = BN == 64 && g.grp.kind == kGroupDense && tiles_m == 1 && k_tiles >= 2 &&
+                       (g.epi_op == HQ_EPILOGUE_IDENTITY || g.epi_op == HQ_EPILOGUE_SIGMOID)
+                   ? 1
+                   : 0;
+    // Everything else: two issuers in k order (same bits as one issuer; the dense and the
+    // grouped kinds alike).  HALOPS_B200_ISSUERS=1 keeps one issuer (read on every call).
+    if (dual == 0 && k_tiles >= 2) {
+        const char* e = getenv("HALOPS_B200_ISSUERS");
+        if (e == nullptr || e[0] != '1') dual = 2;
+    }
     HQ_CUDA_TRY(launch(gemm_kernel<BN, KIND>, dim3(grid), dim3(kThreads), size_t(C::kSmemBytes), g.stream,
                        g.pdl, 1, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.bias, g.epi_op, g.out, g.ldo, g.m, g.n, k_tiles,
                        g.kq_dim, tiles_m, tiles_n, a_rows, g.direct_store ? 1 : 0, dual, g.grp, g.situ));
