@@ -2451,7 +2451,9 @@ TilePick pick_tile(int64_t m, int64_t n, int64_t k, int mode, int sm_count) {
     // k-tiles plus a fixed number of k-tile times for fill, drain and the hand-over to the
     // next tile.  128x256: 0.46 us per k-tile + 2 (425 / 109.5 / 199 us); 256x256 pair:
     // 0.404 + 3.2 (380 / 99.5 / 173 us); 128x128 0.35 (650 us); 256x128 pair 0.348 (633 us);
-    // 128x64 is extrapolated.  The FP4 kinds stay on single-CTA tiles: the pair measured no
+    // 128x64 is extrapolated.  (These fits were made with one MMA issuer in the single-CTA kernel;
+    // its second, in-order issuer shortens the narrow and the FP4 tiles more than the choices made
+    // here depend on.)  The FP4 kinds stay on single-CTA tiles: the pair measured no
     // faster there (126 against 113 us on 4096 x 14336 x 4096 with the same scale path).
     struct Cand {
         int bn;
