@@ -443,7 +443,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     // fences around an mbarrier arrival), so the MMAs reach the tensor core in the order one thread
     // would issue them and the bits do not change.  What it buys is issue time: 4 MMAs and the
     // commit that releases the stage keep one thread busy for longer than a narrow tile's MMAs run.
-    const bool ordered = !kSplitK && dual_issue == 2;
+    const bool ordered = dual_issue == 2;
     static_assert(!kSplitK || (BN == 64 && 2 * C::kABytes == kBM * BN * 4 && C::kStages >= 6), "split-K buffer");
     // stages of the ring; with split-K the last two A stages hold the partial sums received
     constexpr uint32_t kRing = kSplitK ? C::kStages - 2 : C::kStages;
@@ -1980,6 +1980,13 @@ bool split_k_chosen(int group_kind, int tiles_m, int tiles_n, int k_tiles, int s
            (epi_op == HQ_EPILOGUE_IDENTITY || epi_op == HQ_EPILOGUE_SIGMOID);
 }
 
+// 2: the single-CTA kernel issues its MMAs from two threads in k order (see the kernel);
+// 0 with HALOPS_B200_ISSUERS=1 (read on every call)
+int issuers_in_order() {
+    const char* e = getenv("HALOPS_B200_ISSUERS");
+    return e != nullptr && e[0] == '1' ? 0 : 2;
+}
+
 template <int BN, int KIND>
 int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
     using C = Cfg<BN, KIND>;
@@ -2038,7 +2045,7 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
             HQ_CUDA_TRY(launch(gemm_kernel<BN, KIND, true>, dim3(2 * tiles_n), dim3(kThreads), size_t(C::kSmemBytes),
                                g.stream, g.pdl, 2, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.bias, g.epi_op, g.out,
                                g.ldo, g.m, g.n, k_tiles, g.kq_dim, tiles_m, tiles_n, a_rows,
-                               g.direct_store ? 1 : 0, 0, g.grp, g.situ));
+                               g.direct_store ? 1 : 0, issuers_in_order(), g.grp, g.situ));
             return HQ_OK;
         }
     }
@@ -2052,10 +2059,7 @@ int launch_tile(const GemmArgs& g, char* err, size_t errlen) {
                    : 0;
     // Everything else: two issuers in k order (same bits as one issuer; the dense and the
     // grouped kinds alike).  HALOPS_B200_ISSUERS=1 keeps one issuer (read on every call).
-    if (dual == 0 && k_tiles >= 2) {
-        const char* e = getenv("HALOPS_B200_ISSUERS");
-        if (e == nullptr || e[0] != '1') dual = 2;
-    }
+    if (dual == 0 && k_tiles >= 2) dual = issuers_in_order();
     HQ_CUDA_TRY(launch(gemm_kernel<BN, KIND>, dim3(grid), dim3(kThreads), size_t(C::kSmemBytes), g.stream,
                        g.pdl, 1, tm_a, tm_b, tm_d, g.sfa, g.sfb, g.alpha, g.bias, g.epi_op, g.out, g.ldo, g.m, g.n, k_tiles,
                        g.kq_dim, tiles_m, tiles_n, a_rows, g.direct_store ? 1 : 0, dual, g.grp, g.situ));
